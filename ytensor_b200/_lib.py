@@ -1,0 +1,74 @@
+"""ctypes binding of libytensor_cuda.so (the C ABI declared in include/ytcuda.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libytensor_cuda.so"
+
+OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, TIMEOUT, NOT_IMPLEMENTED = range(6)
+F32, BF16, F16 = 0, 1, 2
+
+_i, _i64, _f, _vp, _u64 = C.c_int, C.c_int64, C.c_float, C.c_void_p, C.c_uint64
+
+# name -> (restype, argtypes); one entry per declaration in include/ytcuda.h
+SIGNATURES = {
+    "ytcuda_last_error_string": (C.c_char_p, []),
+    "ytcuda_malloc": (_i, [C.POINTER(_vp), _u64]),
+    "ytcuda_free": (_i, [_vp]),
+    "ytcuda_host_alloc": (_i, [C.POINTER(_vp), _u64]),
+    "ytcuda_host_free": (_i, [_vp]),
+    "ytcuda_memcpy_h2d": (_i, [_vp, _vp, _u64, _vp]),
+    "ytcuda_memcpy_d2h": (_i, [_vp, _vp, _u64, _vp]),
+    "ytcuda_stream_sync": (_i, [_vp]),
+    "ytcuda_device_status": (_i, [_vp]),
+    "ytcuda_launch_count": (_u64, []),
+    "ytcuda_gemm": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4 + [_vp]),
+    "ytcuda_gemm_set_path": (_i, [_i]),
+    "ytcuda_gemm_host": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4),
+}
+
+
+class YtCudaError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"ytcuda status {status}: {msg}")
+        self.status = status
+
+
+class YtCudaInvalidArgument(YtCudaError, ValueError):
+    """Mirrors std::invalid_argument thrown by the reference's API layer."""
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m ytensor_b200.build` "
+                "(there is no CPU fallback)")
+        L = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().ytcuda_last_error_string().decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    if status == OK:
+        return
+    msg = last_error()
+    if status in (INVALID_ARG, UNSUPPORTED):
+        raise YtCudaInvalidArgument(status, msg)
+    raise YtCudaError(status, msg)

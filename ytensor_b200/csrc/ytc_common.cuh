@@ -1,0 +1,185 @@
+// Shared host/device helpers of the YTensor CUDA backend: status codes, dtype
+// tags, the reference's scalar conversion rules and small launch utilities.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/ytcuda.h"
+
+namespace ytk {
+
+// ---- scalar conversions that follow the reference's own types ---------------
+// yt::bfloat16(float) (reference include/types/bfloat16.hpp:78-80): adds half an
+// ulp only when the kept LSB is 1, then truncates. No NaN/Inf special case.
+__host__ __device__ __forceinline__ uint16_t f32_to_bf16_bits_ref(float x) {
+#ifdef __CUDA_ARCH__
+  uint32_t u = __float_as_uint(x);
+#else
+  uint32_t u;
+  memcpy(&u, &x, 4);
+#endif
+  return static_cast<uint16_t>((u + ((u & 0x00010000u) >> 1)) >> 16);
+}
+__host__ __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {
+  uint32_t u = static_cast<uint32_t>(b) << 16;
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(u);
+#else
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+#endif
+}
+
+// yt::float16 = FloatSpec<1,5,10>, float -> half (reference
+// include/types/float_spec.hpp:435-491): fp32 zero/subnormal -> signed zero; Inf -> Inf;
+// NaN -> exponent all ones with mantissa 1; a result whose biased half exponent would be
+// <= 0 is flushed to signed zero BEFORE rounding; otherwise round-to-nearest-even on the
+// 13 dropped bits with carry into the exponent and overflow to infinity.
+__host__ __device__ __forceinline__ uint16_t f32_to_f16_bits_ref(float x) {
+#ifdef __CUDA_ARCH__
+  uint32_t bits = __float_as_uint(x);
+#else
+  uint32_t bits;
+  memcpy(&bits, &x, 4);
+#endif
+  const uint32_t s = bits >> 31, e = (bits >> 23) & 0xFFu, m = bits & 0x7FFFFFu;
+  uint32_t ne = 0, nm = 0;
+  if (e == 0) {
+  } else if (e == 0xFFu) {
+    ne = 31;
+    nm = m ? 1u : 0u;
+  } else {
+    const int re = static_cast<int>(e) - 127 + 15;
+    if (re <= 0) {
+    } else if (re >= 31) {
+      ne = 31;
+    } else {
+      ne = static_cast<uint32_t>(re);
+      nm = m >> 13;
+      const uint32_t rem = m & 0x1FFFu;
+      if (rem > 0x1000u || (rem == 0x1000u && (nm & 1u))) {
+        ++nm;
+        if (nm >= 1024u) {
+          nm = 0;
+          ++ne;
+          if (ne >= 31u) ne = 31u;
+        }
+      }
+    }
+  }
+  return static_cast<uint16_t>((s << 15) | (ne << 10) | nm);
+}
+// half -> float of the same type (reference include/types/float_spec.hpp:299-371, toFloat32).
+// Normal numbers widen exactly; Inf stays Inf; NaN becomes 0x7F800001 with the sign kept.
+// A subnormal encoding (exponent 0, mantissa m != 0) is normalised by the reference with the
+// exponent set to 1 - shift, where shift is the number of left shifts that bring the leading
+// one to mantissa bit 9: the value read is twice m * 2^-24. That is followed here bit for bit.
+__host__ __device__ __forceinline__ float f16_bits_to_f32_ref(uint16_t h) {
+  const uint32_t s = (h >> 15) & 1u, e = (h >> 10) & 0x1Fu;
+  uint32_t m = h & 0x3FFu;
+  uint32_t out;
+  if (e == 0) {
+    if (m == 0) {
+      out = s << 31;
+    } else {
+      uint32_t shift = 0;
+      while ((m & 0x200u) == 0 && shift < 10) {
+        m <<= 1;
+        ++shift;
+      }
+      m = (m << 1) & 0x3FFu;
+      out = (s << 31) | ((113u - shift) << 23) | (m << 13);
+    }
+  } else if (e == 31u) {
+    out = (s << 31) | 0x7F800000u | (m ? 1u : 0u);
+  } else {
+    out = (s << 31) | ((e + 112u) << 23) | (m << 13);
+  }
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(out);
+#else
+  float f;
+  memcpy(&f, &out, 4);
+  return f;
+#endif
+}
+
+template <int DT>
+struct DType;
+template <>
+struct DType<YTC_F32> {
+  using storage = float;
+  __device__ static __forceinline__ float load(const void* p, int64_t i) { return static_cast<const float*>(p)[i]; }
+  __device__ static __forceinline__ void store(void* p, int64_t i, float v) { static_cast<float*>(p)[i] = v; }
+};
+template <>
+struct DType<YTC_BF16> {
+  using storage = uint16_t;
+  __device__ static __forceinline__ float load(const void* p, int64_t i) {
+    return bf16_bits_to_f32(static_cast<const uint16_t*>(p)[i]);
+  }
+  __device__ static __forceinline__ void store(void* p, int64_t i, float v) {
+    static_cast<uint16_t*>(p)[i] = f32_to_bf16_bits_ref(v);
+  }
+};
+template <>
+struct DType<YTC_F16> {
+  using storage = uint16_t;
+  __device__ static __forceinline__ float load(const void* p, int64_t i) {
+    return f16_bits_to_f32_ref(static_cast<const uint16_t*>(p)[i]);
+  }
+  __device__ static __forceinline__ void store(void* p, int64_t i, float v) {
+    static_cast<uint16_t*>(p)[i] = f32_to_f16_bits_ref(v);
+  }
+};
+
+__host__ __device__ __forceinline__ int dtype_size(int dt) { return dt == YTC_F32 ? 4 : 2; }
+
+__device__ __forceinline__ float load_as_f32(const void* p, int64_t i, int dt) {
+  if (dt == YTC_F32) return DType<YTC_F32>::load(p, i);
+  if (dt == YTC_BF16) return DType<YTC_BF16>::load(p, i);
+  return DType<YTC_F16>::load(p, i);
+}
+__device__ __forceinline__ void store_from_f32(void* p, int64_t i, float v, int dt) {
+  if (dt == YTC_F32) DType<YTC_F32>::store(p, i, v);
+  else if (dt == YTC_BF16) DType<YTC_BF16>::store(p, i, v);
+  else DType<YTC_F16>::store(p, i, v);
+}
+
+// ---- host-side plumbing -------------------------------------------------------
+// Counts kernel launches of this library (reported by ytcuda_launch_count).
+void count_launch(uint64_t n = 1);
+void set_last_error(const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+int sm_count();
+// Device word that kernels with bounded waits write a status into (0 = fine).
+int* device_status_word();
+// Reads and clears the device status word (synchronises the stream).
+int read_device_status(cudaStream_t st);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup, so that
+// the library has no link-time dependency on libcuda.
+int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      CUtensorMapSwizzle swz);
+
+#define YTC_REQUIRE(cond, ...)        \
+  do {                                \
+    if (!(cond)) {                    \
+      ytk::set_last_error(__VA_ARGS__); \
+      return YTC_INVALID_ARG;         \
+    }                                 \
+  } while (0)
+
+#define YTC_CUDA(expr)                               \
+  do {                                               \
+    int _s = ytk::check_cuda((expr), #expr);         \
+    if (_s != YTC_OK) return _s;                     \
+  } while (0)
+
+}  // namespace ytk
