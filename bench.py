@@ -1,0 +1,296 @@
+#!/usr/bin/env python
+"""Benchmark of the headline hot path: bf16 batched GEMM [64,2048,4096] x [4096,4096] with fp32
+accumulation and bf16 output (the second configuration of BASELINE.json), through the C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one pass of the GEMM over one batch of 64 matrices. With N > 1 (launched by
+torch.distributed.run, one rank per GPU) every rank multiplies its own 64-matrix shard of a
+64*N batch: batch items are independent, there is no collective on the data path, and the value
+is the whole job's TFLOP/s (weak scaling). Prints ONE JSON line on rank 0.
+
+`--impl reference` times the reference's own CPU implementation (oracle/_ref when it is built,
+else the plain-C oracle port) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+BATCH, M, K, N = 64, 2048, 4096, 4096
+FLOPS_PER_STEP = 2.0 * BATCH * M * K * N          # 4 398 046 511 104
+WORKLOAD = "configs[1]: bf16 batched GEMM A[64,2048,4096] . B[4096,4096], fp32 accumulate, bf16 out"
+
+
+def make_config(world: int) -> dict:
+    return {"workload": WORKLOAD, "global_batch": BATCH * world, "m": M, "k": K, "n": N,
+            "parallelism": f"batch-sharded x{world}, no collective",
+            "l2": "inputs larger than L2 (A is 1.07 GB per step), no flush needed"}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------- reference arm
+def reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+
+    kind = "reference" if O.ref_available() else "port"
+    cores = os.cpu_count() or 1
+    if kind == "reference":
+        os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+        os.environ.setdefault("OMP_PROC_BIND", "close")
+        be = O.ref(threads=cores)
+        cores = be.threads()
+    else:
+        be = O.port()
+    rng = np.random.default_rng(1)
+    items = 1  # batch items per step: a bounded sample of the 64-item workload
+    a = be.f32_to_bf16(rng.standard_normal((items, M, K)).astype(np.float32))
+    b = be.f32_to_bf16((rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32))
+    for _ in range(min(args.warmup, 1)):
+        be.matmul_16(a, b, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        be.matmul_16(a, b, 1)
+    dt = (time.perf_counter() - t0) / args.steps
+    tfl = 2.0 * items * M * K * N / dt / 1e12
+    sample = (f"{items} of {BATCH} batch items per step (widen bf16->f32, YTensor<float>::matmul AVX2, narrow with "
+              f"yt::bfloat16), {args.steps} steps, scaled by FLOPs")
+    print(json.dumps({
+        "impl": "reference", "metric": "bf16_gemm_tflops", "value": tfl, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * (BATCH / items),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 compute on bf16 storage",
+        "data": "synthetic", "config": make_config(args.gpus),
+        "cpu_baseline": {"value": tfl, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": tfl, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def cpu_baseline(budget_s: float = 12.0) -> dict:
+    """Times the reference CPU path on a bounded sample (rank 0, N = 1 only)."""
+    import numpy as np
+    from oracle import oracle as O
+
+    kind = "reference" if O.ref_available() else "port"
+    cores = os.cpu_count() or 1
+    be = O.ref(threads=cores) if kind == "reference" else O.port()
+    if kind == "reference":
+        cores = be.threads()
+    rng = np.random.default_rng(1)
+    a = be.f32_to_bf16(rng.standard_normal((1, M, K)).astype(np.float32))
+    b = be.f32_to_bf16((rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32))
+    be.matmul_16(a[:, :256], b, 1)  # warm the thread pool
+    t0 = time.perf_counter()
+    be.matmul_16(a, b, 1)
+    one = time.perf_counter() - t0
+    reps = max(1, min(8, int(budget_s / max(one, 1e-3)) - 1))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        be.matmul_16(a, b, 1)
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 2.0 * M * K * N / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+            "sample": f"1 of {BATCH} batch items (2048x4096x4096), best-effort mean of {reps} runs, scaled by FLOPs"}
+
+
+# --------------------------------------------------------------------------------------- device arm
+def device_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from ytensor_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the device backend has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = _lib.lib()
+    dev = torch.device("cuda", local)
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    # plumbing only: torch provides device memory and the synthetic draw; the GEMM is ytcuda_gemm
+    a = torch.randn(BATCH, M, K, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    b = (torch.randn(K, N, device=dev, generator=g, dtype=torch.float32) / K ** 0.5).to(torch.bfloat16)
+    c = torch.empty(BATCH, M, N, device=dev, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        _lib.check(L.ytcuda_gemm(_lib.BF16, _lib.BF16, a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, 1.0, 0.0,
+                                 K, 1, N, 1, N, 1, BATCH, M * K, 0, M * N, stream))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.ytcuda_launch_count()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    evs[0].record()
+    for i in range(args.steps):
+        step()
+        evs[i + 1].record()
+    barrier()
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per_launch_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    launches = L.ytcuda_launch_count() - launches0
+    _lib.check(L.ytcuda_device_status(None))
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end: host buffers through ytcuda_gemm_host (H2D of A and B, D2H of C every step)
+    e2e_steps = max(2, min(args.steps, 5))
+    ha = torch.empty(BATCH, M, K, dtype=torch.bfloat16, pin_memory=True)
+    hb = torch.empty(K, N, dtype=torch.bfloat16, pin_memory=True)
+    hc = torch.empty(BATCH, M, N, dtype=torch.bfloat16, pin_memory=True)
+    ha.copy_(a)
+    hb.copy_(b)
+
+    def host_step():
+        _lib.check(L.ytcuda_gemm_host(_lib.BF16, _lib.BF16, ha.data_ptr(), hb.data_ptr(), hc.data_ptr(), M, N, K, 1.0,
+                                      0.0, K, 1, N, 1, N, 1, BATCH, M * K, 0, M * N))
+
+    host_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    same = bool(torch.equal(hc[BATCH - 1], c[BATCH - 1].cpu()))
+    e2e = {"value": FLOPS_PER_STEP * world / e2e_s / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": (ha.numel() + hb.numel()) * 2, "d2h_bytes_per_step": hc.numel() * 2,
+           "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "matches_device_result": same,
+           "api": "ytcuda_gemm_host (pinned host buffers)"}
+
+    if rank == 0:
+        peaks = measured_peaks()
+        avg_launch_ms = statistics.mean(per_launch_ms)
+        achieved = FLOPS_PER_STEP / (avg_launch_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                    "kernel": "gemm_tc_kernel<256>", "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
+                    "frac_of_sustained_peak": (achieved / peaks["bf16_tflops_sustained"]
+                                               if peaks.get("bf16_tflops_sustained") else None),
+                    "algorithmic_flops_per_launch": FLOPS_PER_STEP}
+        out = {
+            "metric": "bf16_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": make_config(world),
+            "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        device_arm(args)
+
+
+if __name__ == "__main__":
+    main()

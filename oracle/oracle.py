@@ -1,0 +1,292 @@
+"""TEST INFRASTRUCTURE: numpy front-end of the CPU oracle.
+
+Two back-ends with the same call surface:
+  * `port`  - oracle/libyt_oracle.so, the plain-C restatement in yt_oracle.c (always available
+              after `make -C oracle liboracle`);
+  * `ref`   - oracle/_ref/libyt_ref.so, the unmodified reference compiled behind ref_shim.cpp
+              (available where it was built from the reference sources).
+Only tests, the smoke check and the benchmark's CPU-baseline legs may import this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+PORT_LIB = HERE / "libyt_oracle.so"
+REF_LIB = HERE / "_ref" / "libyt_ref.so"
+
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+
+
+def build_port() -> Path:
+    subprocess.run(["make", "-s", "-C", str(HERE), "liboracle"], check=True)
+    return PORT_LIB
+
+
+def build_ref() -> Path | None:
+    subprocess.run(["make", "-s", "-C", str(HERE), "ref"], check=True)
+    return REF_LIB if REF_LIB.exists() else None
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ints(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _opt(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class _Backend:
+    prefix = ""
+
+    def __init__(self, path: Path):
+        self.lib = C.CDLL(str(path))
+
+    def _fn(self, name):
+        return getattr(self.lib, self.prefix + name)
+
+    # ---- casts -------------------------------------------------------------------------
+    def f32_to_bf16(self, x):
+        x = _f32(x)
+        y = np.empty(x.shape, np.uint16)
+        self._fn("f32_to_bf16")(_opt(x), _opt(y), C.c_int64(x.size))
+        return y
+
+    def bf16_to_f32(self, x):
+        x = np.ascontiguousarray(x, np.uint16)
+        y = np.empty(x.shape, np.float32)
+        self._fn("bf16_to_f32")(_opt(x), _opt(y), C.c_int64(x.size))
+        return y
+
+    def f32_to_f16(self, x):
+        x = _f32(x)
+        y = np.empty(x.shape, np.uint16)
+        self._fn("f32_to_f16")(_opt(x), _opt(y), C.c_int64(x.size))
+        return y
+
+    def f16_to_f32(self, x):
+        x = np.ascontiguousarray(x, np.uint16)
+        y = np.empty(x.shape, np.float32)
+        self._fn("f16_to_f32")(_opt(x), _opt(y), C.c_int64(x.size))
+        return y
+
+    # ---- N-d ops -----------------------------------------------------------------------
+    def softmax(self, x, axes):
+        x = _f32(x)
+        y = np.empty_like(x)
+        axes = _ints(np.atleast_1d(axes))
+        rc = self._fn("softmax_f32")(_opt(x), _opt(y), _opt(_ints(x.shape)), x.ndim, _opt(axes), axes.size)
+        assert rc == 0, rc
+        return y
+
+    def rmsnorm(self, x, w, axes, eps):
+        x, w = _f32(x), _f32(w)
+        y = np.empty_like(x)
+        axes = _ints(np.atleast_1d(axes))
+        rc = self._fn("rmsnorm_f32")(_opt(x), _opt(w), _opt(y), _opt(_ints(x.shape)), x.ndim, _opt(axes), axes.size,
+                                     C.c_float(eps))
+        assert rc == 0, rc
+        return y
+
+    def layernorm(self, x, gamma, beta, axes, eps):
+        x = _f32(x)
+        g = None if gamma is None else _f32(gamma)
+        b = None if beta is None else _f32(beta)
+        y = np.empty_like(x)
+        axes = _ints(np.atleast_1d(axes))
+        rc = self._fn("layernorm_f32")(_opt(x), _opt(g), _opt(b), _opt(y), _opt(_ints(x.shape)), x.ndim, _opt(axes),
+                                       axes.size, C.c_float(eps))
+        assert rc == 0, rc
+        return y
+
+    def reduce(self, x, axes, op):
+        """op: 'sum' | 'mean' | 'max'. Returns keep-dim result (and int32 indices for max)."""
+        x = _f32(x)
+        axes = _ints(np.atleast_1d(axes))
+        ks = list(x.shape)
+        for a in axes:
+            ks[int(a) % x.ndim] = 1
+        y = np.empty(ks, np.float32)
+        idx = np.zeros(ks, np.int32)
+        code = {"sum": 0, "mean": 1, "max": 2}[op]
+        rc = self._fn("reduce_f32")(_opt(x), _opt(y), _opt(idx), _opt(_ints(x.shape)), x.ndim, _opt(axes), axes.size,
+                                    code)
+        assert rc == 0, rc
+        return (y, idx) if op == "max" else y
+
+    def binary(self, a, b, op):
+        a, b = _f32(a), _f32(b)
+        nd = max(a.ndim, b.ndim)
+        a = a.reshape((1,) * (nd - a.ndim) + a.shape)
+        b = b.reshape((1,) * (nd - b.ndim) + b.shape)
+        out = np.empty(np.broadcast_shapes(a.shape, b.shape), np.float32)
+        code = {"add": 0, "sub": 1, "mul": 2, "div": 3}[op]
+        rc = self._fn("binary_f32")(_opt(a), _opt(_ints(a.shape)), _opt(b), _opt(_ints(b.shape)), nd, _opt(out), code)
+        assert rc == 0, rc
+        return out
+
+    def swish(self, x):
+        x = _f32(x)
+        y = np.empty_like(x)
+        self._fn("swish_f32")(_opt(x), _opt(y), C.c_int64(x.size))
+        return y
+
+    def chain(self, x, w, r, eps=1e-6):
+        x, w, r = _f32(x), _f32(w), _f32(r)
+        B, L, H = x.shape
+        out = np.empty(x.shape, np.uint16)
+        rc = self._fn("chain_f32")(_opt(x), _opt(w), _opt(r), _opt(out), B, L, H, int(r.shape[0] == B),
+                                   C.c_float(eps))
+        assert rc == 0, rc
+        return out
+
+    def sdpa(self, q, k, v, scale=0.0, mask=None, causal=False, bias=None, **kw):
+        """q [b,kvh,g,ql,d], k [b,kvh,kl,d], v [b,kvh,kl,dv] -> [b,kvh,g,ql,dv]."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        b, kvh, g, ql, d = q.shape
+        kl, dv = k.shape[2], v.shape[3]
+        out = np.empty((b, kvh, g, ql, dv), np.float32)
+        kind, m = 0, None
+        if mask is not None:
+            kind, m = 1, np.ascontiguousarray(mask, np.uint8)
+        elif causal:
+            kind = 2
+        bs = None if bias is None else _f32(bias)
+        rc = self._sdpa(q, k, v, out, b, kvh, g, ql, kl, d, dv, scale, kind, m, bs, **kw)
+        assert rc == 0, rc
+        return out
+
+
+class PortOracle(_Backend):
+    prefix = "yto_"
+
+    def __init__(self):
+        if not PORT_LIB.exists():
+            build_port()
+        super().__init__(PORT_LIB)
+
+    def matmul(self, a, b):
+        """a [batch,m,k] (or [m,k]) . b [k,n] or [batch,k,n], fp32."""
+        a, b = _f32(a), _f32(b)
+        a3 = a.reshape((-1,) + a.shape[-2:])
+        batch, m, k = a3.shape
+        n = b.shape[-1]
+        bb = int(b.ndim == 3)
+        c = np.empty((batch, m, n), np.float32)
+        self.lib.yto_matmul_f32(_opt(a3), _opt(b), _opt(c), batch, m, n, k, bb)
+        return c.reshape(a.shape[:-1] + (n,))
+
+    def matmul_16(self, a_bits, b_bits, dtype):
+        """bf16 (dtype=1) / fp16 (dtype=2) storage, fp32 compute; uint16 bit patterns in and out."""
+        a = np.ascontiguousarray(a_bits, np.uint16)
+        b = np.ascontiguousarray(b_bits, np.uint16)
+        a3 = a.reshape((-1,) + a.shape[-2:])
+        batch, m, k = a3.shape
+        n = b.shape[-1]
+        c = np.empty((batch, m, n), np.uint16)
+        self.lib.yto_matmul_16(_opt(a3), _opt(b), _opt(c), batch, m, n, k, int(b.ndim == 3), dtype)
+        return c.reshape(a.shape[:-1] + (n,))
+
+    def sgemm(self, A, B, Cin, alpha, beta):
+        """Strided form on numpy views: returns alpha*A@B + beta*Cin (fp32)."""
+        A, B = np.asarray(A, np.float32), np.asarray(B, np.float32)
+        out = np.array(Cin, np.float32, copy=True, order="C")
+        m, k = A.shape
+        n = B.shape[1]
+        es = 4
+        self.lib.yto_sgemm(C.c_void_p(A.ctypes.data), C.c_void_p(B.ctypes.data), _opt(out), m, n, k, C.c_float(alpha),
+                           C.c_float(beta), C.c_int64(A.strides[0] // es), C.c_int64(A.strides[1] // es),
+                           C.c_int64(B.strides[0] // es), C.c_int64(B.strides[1] // es), C.c_int64(n), C.c_int64(1))
+        return out
+
+    def _sdpa(self, q, k, v, out, b, kvh, g, ql, kl, d, dv, scale, kind, m, bs):
+        return self.lib.yto_sdpa_f32(_opt(q), _opt(k), _opt(v), _opt(out), b, kvh, g, ql, kl, d, dv, C.c_float(scale),
+                                     kind, _opt(m), _opt(bs))
+
+
+class RefOracle(_Backend):
+    prefix = "ytref_"
+
+    def __init__(self, threads: int = 0):
+        if not REF_LIB.exists():
+            raise FileNotFoundError(f"{REF_LIB} is not built (needs the reference sources)")
+        super().__init__(REF_LIB)
+        self.lib.ytref_set_threads(threads)
+        self.lib.ytref_qwen3_create.restype = C.c_void_p
+
+    def threads(self) -> int:
+        return self.lib.ytref_get_threads()
+
+    def matmul(self, a, b, backend=2):
+        a, b = _f32(a), _f32(b)
+        a3 = a.reshape((-1,) + a.shape[-2:])
+        batch, m, k = a3.shape
+        n = b.shape[-1]
+        c = np.empty((batch, m, n), np.float32)
+        rc = self.lib.ytref_matmul_f32(_opt(a3), _opt(b), _opt(c), batch, m, n, k, int(b.ndim == 3), backend)
+        assert rc == 0, rc
+        return c.reshape(a.shape[:-1] + (n,))
+
+    def matmul_16(self, a_bits, b_bits, dtype):
+        """The recipe for 16-bit storage: widen, YTensor<float>::matmul, narrow with the type's constructor."""
+        widen = self.bf16_to_f32 if dtype == 1 else self.f16_to_f32
+        narrow = self.f32_to_bf16 if dtype == 1 else self.f32_to_f16
+        return narrow(self.matmul(widen(a_bits), widen(b_bits)))
+
+    def linear(self, x, w, bias=None):
+        x, w = _f32(x), _f32(w)
+        rows, k = x.shape
+        n = w.shape[0]
+        y = np.empty((rows, n), np.float32)
+        bs = None if bias is None else _f32(bias)
+        rc = self.lib.ytref_linear_f32(_opt(x), _opt(w), _opt(bs), _opt(y), rows, n, k)
+        assert rc == 0, rc
+        return y
+
+    def sgemm(self, A, B, Cin, alpha, beta):
+        A, B = np.asarray(A, np.float32), np.asarray(B, np.float32)
+        out = np.array(Cin, np.float32, copy=True, order="C")
+        m, k = A.shape
+        n = B.shape[1]
+        es = 4
+        self.lib.ytref_sgemm_strided(C.c_void_p(A.ctypes.data), C.c_void_p(B.ctypes.data), _opt(out), m, n, k,
+                                     C.c_float(alpha), C.c_float(beta), C.c_int64(A.strides[0] // es),
+                                     C.c_int64(A.strides[1] // es), C.c_int64(B.strides[0] // es),
+                                     C.c_int64(B.strides[1] // es), C.c_int64(n), C.c_int64(1))
+        return out
+
+    def _sdpa(self, q, k, v, out, b, kvh, g, ql, kl, d, dv, scale, kind, m, bs, backend=1):
+        return self.lib.ytref_sdpa_f32(_opt(q), _opt(k), _opt(v), _opt(out), b, kvh, g, ql, kl, d, dv, C.c_float(scale),
+                                       kind, _opt(m), _opt(bs), backend)
+
+
+_port = None
+_ref = None
+
+
+def port() -> PortOracle:
+    global _port
+    if _port is None:
+        _port = PortOracle()
+    return _port
+
+
+def ref_available() -> bool:
+    return REF_LIB.exists()
+
+
+def ref(threads: int = 0) -> RefOracle:
+    global _ref
+    if _ref is None:
+        _ref = RefOracle(threads)
+    return _ref
