@@ -166,6 +166,43 @@ def cpu_baseline(budget_s: float = 12.0) -> dict:
 
 
 # --------------------------------------------------------------------------------------- device arm
+def end_to_end(args, L, a, b, c, world, dev, barrier):
+    """Host buffers through ytcuda_gemm_host: H2D of A and B and D2H of C inside every timed step."""
+    import torch
+    import torch.distributed as dist
+
+    from ytensor_b200 import _lib
+
+    e2e_steps = max(2, min(args.steps, 5))
+    ha = torch.empty(BATCH, M, K, dtype=torch.bfloat16, pin_memory=True)
+    hb = torch.empty(K, N, dtype=torch.bfloat16, pin_memory=True)
+    hc = torch.empty(BATCH, M, N, dtype=torch.bfloat16, pin_memory=True)
+    ha.copy_(a)
+    hb.copy_(b)
+
+    def host_step():
+        _lib.check(L.ytcuda_gemm_host(_lib.BF16, _lib.BF16, ha.data_ptr(), hb.data_ptr(), hc.data_ptr(), M, N, K, 1.0,
+                                      0.0, K, 1, N, 1, N, 1, BATCH, M * K, 0, M * N))
+
+    host_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    same = bool(torch.equal(hc[BATCH - 1], c[BATCH - 1].cpu()))
+    e2e = {"value": FLOPS_PER_STEP * world / e2e_s / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": (ha.numel() + hb.numel()) * 2, "d2h_bytes_per_step": hc.numel() * 2,
+           "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "matches_device_result": same,
+           "api": "ytcuda_gemm_host (pinned host buffers)"}
+    return e2e
+
+
 def device_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -225,34 +262,9 @@ def device_arm(args) -> None:
     ms_per_step = total_ms / args.steps
     value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
 
-    # ---- end to end: host buffers through ytcuda_gemm_host (H2D of A and B, D2H of C every step)
-    e2e_steps = max(2, min(args.steps, 5))
-    ha = torch.empty(BATCH, M, K, dtype=torch.bfloat16, pin_memory=True)
-    hb = torch.empty(K, N, dtype=torch.bfloat16, pin_memory=True)
-    hc = torch.empty(BATCH, M, N, dtype=torch.bfloat16, pin_memory=True)
-    ha.copy_(a)
-    hb.copy_(b)
-
-    def host_step():
-        _lib.check(L.ytcuda_gemm_host(_lib.BF16, _lib.BF16, ha.data_ptr(), hb.data_ptr(), hc.data_ptr(), M, N, K, 1.0,
-                                      0.0, K, 1, N, 1, N, 1, BATCH, M * K, 0, M * N))
-
-    host_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        host_step()
-    barrier()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
-    same = bool(torch.equal(hc[BATCH - 1], c[BATCH - 1].cpu()))
-    e2e = {"value": FLOPS_PER_STEP * world / e2e_s / 1e12, "unit": "TFLOP/s",
-           "h2d_bytes_per_step": (ha.numel() + hb.numel()) * 2, "d2h_bytes_per_step": hc.numel() * 2,
-           "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "matches_device_result": same,
-           "api": "ytcuda_gemm_host (pinned host buffers)"}
+    e2e = None
+    if not args.no_e2e:
+        e2e = end_to_end(args, L, a, b, c, world, dev, barrier)
 
     if rank == 0:
         peaks = measured_peaks()
@@ -279,13 +291,21 @@ def device_arm(args) -> None:
 
 
 def main() -> None:
+    global BATCH, FLOPS_PER_STEP, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures only)")
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="batch items per step; anything but 64 is a profiling case, not a bench line")
     args = ap.parse_args()
+    if args.batch != BATCH:
+        BATCH = args.batch
+        FLOPS_PER_STEP = 2.0 * BATCH * M * K * N
+        WORKLOAD = f"PROFILING CASE (batch {BATCH}, not configs[1]): bf16 GEMM A[{BATCH},2048,4096] . B[4096,4096]"
     if args.impl == "reference":
         reference_arm(args)
     else:

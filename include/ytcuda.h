@@ -67,6 +67,13 @@ int ytcuda_gemm(int dtype_in, int dtype_out, const void* A, const void* B, void*
  * YTensor::matmul (include/ytensor_math.hpp:70-73); process-wide, meant for tests. */
 int ytcuda_gemm_set_path(int path);
 
+/* Tuning knobs of the tcgen05 kernel. a_prefetch_kblocks: how many 64-wide k-blocks an L2 prefetch of the
+ * streamed A operand runs ahead of the shared-memory ring (0 = off, the default: it measured slower).
+ * split_loads: fetch K-major operand tiles as 64-row TMA boxes instead of one tall box (default 0).
+ * The counterpart of the reference's runtime blocking globals g_gemm_mc/kc/nc and their setters
+ * (include/kernel/avx2/gemm_utils.hpp:59-77). */
+int ytcuda_gemm_set_tuning(int a_prefetch_kblocks, int split_loads);
+
 /* Same computation with HOST buffers (pinned or pageable): copies A and B to the device,
  * multiplies, copies C back, and returns when C is complete. Batch items are pipelined so
  * that copies overlap the multiplication. This is what a YTensor that lives in host memory
@@ -74,6 +81,71 @@ int ytcuda_gemm_set_path(int path);
 int ytcuda_gemm_host(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
                      float alpha, float beta, int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc,
                      int64_t csc, int64_t batch, int64_t bsa, int64_t bsb, int64_t bsc);
+
+/* ---------------------------------------------------------------- reductions over axes
+ * All N-d entry points take `ndim` (1..8) extents and ELEMENT strides; `axes` lists the reduced axes
+ * (negative values count from the end). The reduced elements of one output position are walked
+ * as an odometer over the axes in the order listed, as the reference does. Trailing contiguous
+ * axes take the single-pass register kernel; any other axes / strides take the generic kernel. */
+
+/* y = softmax(x) jointly over `axes`. Replaces yt::function::softmax / softmax_
+ * (include/function/activation.hpp:30-39, src/function/activation.inl:130-409). */
+int ytcuda_softmax(int dt_in, int dt_out, const void* x, void* y, const int64_t* shape, const int64_t* xstrides,
+                   const int64_t* ystrides, int ndim, const int* axes, int naxes, void* stream);
+
+/* y = x / sqrt(mean_axes(x*x) + eps) * weight. `weight` (may be NULL) is contiguous over the reduced dims in
+ * ascending axis order. Replaces yt::function::rmsNorm / rmsNorm_ (include/function/normalization.hpp:55-88,
+ * src/function/normalization.inl:33-54,88-101,234-277). */
+int ytcuda_rmsnorm(int dt_in, int dt_out, int dt_w, const void* x, const void* weight, void* y, const int64_t* shape,
+                   const int64_t* xstrides, const int64_t* ystrides, int ndim, const int* axes, int naxes, float eps,
+                   void* stream);
+
+/* y = (x - mean) / sqrt(var + eps) * gamma + beta (gamma and beta both NULL for the plain form).
+ * Replaces yt::function::layerNorm / layerNorm_ (include/function/normalization.hpp:8-53,
+ * src/function/normalization.inl:3-30,159-230). */
+int ytcuda_layernorm(int dt_in, int dt_out, int dt_w, const void* x, const void* gamma, const void* beta, void* y,
+                     const int64_t* shape, const int64_t* xstrides, const int64_t* ystrides, int ndim, const int* axes,
+                     int naxes, float eps, void* stream);
+
+/* op 0 = sum, 1 = mean, 2 = max. y is contiguous with size-1 dims on the reduced axes; for max, `index`
+ * (may be NULL) receives the position of the FIRST maximum in the odometer walk. Replaces YTensor::sum / mean /
+ * max (include/ytensor_math.hpp:105-121, src/ytensor_math.inl:414-692). */
+int ytcuda_reduce(int op, int dt_in, int dt_out, const void* x, void* y, int32_t* index, const int64_t* shape,
+                  const int64_t* xstrides, int ndim, const int* axes, int naxes, void* stream);
+
+/* Fused memory-bound chain: out = cast(softmax(rmsNorm(x, weight, -1, eps) + residual, -1)).
+ * x [batch, rows, hidden] fp32 contiguous; residual [batch, rows, hidden] (residual_batched != 0) or
+ * [1, rows, hidden] broadcast over batch; one read of x and of the residual, one write of out.
+ * Replaces the sequence rmsNorm -> operator+= -> softmax_ -> copy_ (src/function/normalization.inl:234-277,
+ * src/ytensor_math.inl:35-49, src/function/activation.inl:376-409, src/ytensor_base.inl:257-430). */
+int ytcuda_rmsnorm_add_softmax_cast(int dt_out, const float* x, const float* weight, const float* residual, void* out,
+                                    int64_t batch, int64_t rows, int hidden, int residual_batched, float eps,
+                                    void* stream);
+
+/* ---------------------------------------------------------------- elementwise
+ * out = a (op) b with broadcasting expressed as zero strides; op 0 add, 1 sub, 2 mul, 3 div. `out` may alias
+ * `a` (the in-place operators). Replaces the operator macros over yt::kernel::broadcast / broadcastInplace
+ * (src/ytensor_math.inl:22-124, src/kernel/broadcast.inl:167-469). */
+int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const void* b, void* out, int ndim,
+                  const int64_t* shape, const int64_t* astrides, const int64_t* bstrides, const int64_t* ostrides,
+                  void* stream);
+
+/* y = f(x): op 0 copy, 1 swish (x * stable sigmoid(x)), 2 x * param, 3 x + param. Replaces
+ * yt::function::swish_ (src/function/activation.inl:631-647) and scalar broadcastInplace calls. */
+int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
+                 const int64_t* xstrides, const int64_t* ystrides, float param, void* stream);
+
+/* Strided dtype conversion with the reference's own rounding: yt::bfloat16(float) adds half an ulp only when
+ * the kept LSB is 1 (include/types/bfloat16.hpp:78-80); yt::float16 rounds to nearest even and flushes results
+ * below the smallest normal to zero (include/types/float_spec.hpp:435-491). Bit-exact with the reference.
+ * Replaces YTensorBase::copy_ / cast (src/ytensor_base.inl:257-430, include/ytensor_base.hpp:399-404). */
+int ytcuda_cast(int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape, const int64_t* xstrides,
+                const int64_t* ystrides, void* stream);
+
+/* out[r, i] = swish(gate_up[r, i]) * gate_up[r, inter + i], i < inter: the gate / up halves of the fused
+ * projection (example/qwen3/src/qwen3.cpp:193-200: swish_ on one slice, then *= the other slice). */
+int ytcuda_swiglu(int dt_in, int dt_out, const void* gate_up, void* out, int64_t rows, int inter, int64_t gu_row_stride,
+                  int64_t out_row_stride, void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,7 +28,17 @@ SIGNATURES = {
     "ytcuda_launch_count": (_u64, []),
     "ytcuda_gemm": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4 + [_vp]),
     "ytcuda_gemm_set_path": (_i, [_i]),
+    "ytcuda_gemm_set_tuning": (_i, [_i, _i]),
     "ytcuda_gemm_host": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4),
+    "ytcuda_softmax": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "ytcuda_rmsnorm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp]),
+    "ytcuda_layernorm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp]),
+    "ytcuda_reduce": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "ytcuda_rmsnorm_add_softmax_cast": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _f, _vp]),
+    "ytcuda_binary": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "ytcuda_unary": (_i, [_i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp]),
+    "ytcuda_cast": (_i, [_i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
+    "ytcuda_swiglu": (_i, [_i, _i, _vp, _vp, _i64, _i, _i64, _i64, _vp]),
 }
 
 

@@ -7,6 +7,9 @@ function calls the C ABI of libytensor_cuda.so; nothing here computes with torch
 """
 from __future__ import annotations
 
+import builtins
+import ctypes as C
+
 import torch
 
 from . import _lib
@@ -78,7 +81,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *,
     av, bv, ov = _batch_view(ae), _batch_view(be), _batch_view(out)
     L = lib()
     if av is not None and bv is not None and ov is not None:
-        batch = max(av[0], bv[0], ov[0])
+        batch = builtins.max(av[0], bv[0], ov[0])
         check(L.ytcuda_gemm(_dt(ae), _dt(out), ae.data_ptr(), be.data_ptr(), out.data_ptr(), m, n, k, alpha, beta,
                             ae.stride(-2), ae.stride(-1), be.stride(-2), be.stride(-1), out.stride(-2),
                             out.stride(-1), batch, av[1], bv[1], ov[1], _stream()))
@@ -93,6 +96,227 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     """x . weight^T (+ bias), weight [out_features, in_features] (reference src/function/ops.inl:84-105)."""
     y = matmul(x, weight.transpose(-1, -2))
     if bias is not None:
-        from .api import add_  # noqa: F401  (defined with the elementwise ops)
         add_(y, bias)
     return y
+
+
+# ------------------------------------------------------------------ N-d helpers
+def _i64(vals):
+    return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+def _i32(vals):
+    return (C.c_int * len(vals))(*[int(v) for v in vals])
+
+
+def _axes(axes) -> list[int]:
+    return [int(axes)] if isinstance(axes, int) else [int(a) for a in axes]
+
+
+def _nd(t: torch.Tensor):
+    if t.dim() == 0:
+        t = t.reshape(1)
+    return t, _i64(t.shape), _i64(t.stride())
+
+
+# ------------------------------------------------------------------ softmax / norms
+def softmax(x: torch.Tensor, axes=-1, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Softmax jointly over `axes` (reference yt::function::softmax, src/function/activation.inl:336-375)."""
+    _require_cuda(x, out)
+    y = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
+    ax = _axes(axes)
+    xx, shape, xs = _nd(x)
+    check(lib().ytcuda_softmax(_dt(x), _dt(y), x.data_ptr(), y.data_ptr(), shape, xs, _i64(y.stride() or (1,)),
+                               xx.dim(), _i32(ax), len(ax), _stream()))
+    return y
+
+
+def softmax_(x: torch.Tensor, axes=-1) -> torch.Tensor:
+    """In-place form (reference yt::function::softmax_, src/function/activation.inl:376-409)."""
+    return softmax(x, axes, out=x)
+
+
+def rmsNorm(x: torch.Tensor, weight: torch.Tensor | None, axes=-1, eps: float = 1e-5,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight (reference yt::function::rmsNorm, src/function/normalization.inl:234-277).
+    `weight` has one dim per axis; a shape mismatch raises like the reference's _makeAffineView."""
+    _require_cuda(x, weight, out)
+    ax = _axes(axes)
+    if weight is not None:
+        want = [x.shape[a] for a in ax]
+        if list(weight.shape) != want:
+            raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "rmsNorm: weight shape must match affine axes")
+        weight = weight.contiguous()
+    y = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
+    xx, shape, xs = _nd(x)
+    check(lib().ytcuda_rmsnorm(_dt(x), _dt(y), _dt(weight) if weight is not None else F32, x.data_ptr(),
+                               weight.data_ptr() if weight is not None else None, y.data_ptr(), shape, xs,
+                               _i64(y.stride() or (1,)), xx.dim(), _i32(ax), len(ax), eps, _stream()))
+    return y
+
+
+def rmsNorm_(x, weight, axes=-1, eps: float = 1e-5):
+    return rmsNorm(x, weight, axes, eps, out=x)
+
+
+def layerNorm(x: torch.Tensor, gamma: torch.Tensor | None = None, bias: torch.Tensor | None = None, axes=-1,
+              eps: float = 1e-5, out: torch.Tensor | None = None) -> torch.Tensor:
+    """(x - mean) / sqrt(var + eps) [* gamma + bias] (reference yt::function::layerNorm,
+    src/function/normalization.inl:159-230)."""
+    _require_cuda(x, gamma, bias, out)
+    ax = _axes(axes)
+    if (gamma is None) != (bias is None):
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "layerNorm: gamma and bias come together")
+    if gamma is not None:
+        want = [x.shape[a] for a in ax]
+        if list(gamma.shape) != want or list(bias.shape) != want:
+            raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "layerNorm: gamma/bias shape must match affine axes")
+        gamma, bias = gamma.contiguous(), bias.contiguous().to(gamma.dtype)
+    y = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
+    xx, shape, xs = _nd(x)
+    check(lib().ytcuda_layernorm(_dt(x), _dt(y), _dt(gamma) if gamma is not None else F32, x.data_ptr(),
+                                 gamma.data_ptr() if gamma is not None else None,
+                                 bias.data_ptr() if bias is not None else None, y.data_ptr(), shape, xs,
+                                 _i64(y.stride() or (1,)), xx.dim(), _i32(ax), len(ax), eps, _stream()))
+    return y
+
+
+def layerNorm_(x, gamma=None, bias=None, axes=-1, eps: float = 1e-5):
+    return layerNorm(x, gamma, bias, axes, eps, out=x)
+
+
+def rmsnorm_add_softmax_cast(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
+                             out_dtype: torch.dtype = torch.bfloat16, eps: float = 1e-6) -> torch.Tensor:
+    """cast(softmax(rmsNorm(x, w, -1, eps) + residual, -1)) in one pass. x [B, L, H] fp32 contiguous,
+    residual [B, L, H] or [1, L, H]."""
+    _require_cuda(x, weight, residual)
+    if x.dim() != 3 or x.dtype != torch.float32 or not x.is_contiguous():
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "chain: x must be a contiguous fp32 [B, L, H] tensor")
+    B, Lr, H = x.shape
+    if tuple(residual.shape) not in ((B, Lr, H), (1, Lr, H)) or tuple(weight.shape) != (H,):
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "chain: residual / weight shape mismatch")
+    residual, weight = residual.contiguous().float(), weight.contiguous().float()
+    out = torch.empty(B, Lr, H, dtype=out_dtype, device=x.device)
+    check(lib().ytcuda_rmsnorm_add_softmax_cast(_DT[out_dtype], x.data_ptr(), weight.data_ptr(), residual.data_ptr(),
+                                                out.data_ptr(), B, Lr, H, int(residual.shape[0] == B), eps, _stream()))
+    return out
+
+
+# ------------------------------------------------------------------ reductions
+def _reduce(op: int, x: torch.Tensor, axes, want_index: bool):
+    _require_cuda(x)
+    ax = _axes(axes)
+    xx, shape, xs = _nd(x)
+    ks = list(xx.shape)
+    for a in ax:
+        ks[a % xx.dim()] = 1
+    y = torch.empty(ks, dtype=x.dtype, device=x.device)
+    idx = torch.empty(ks, dtype=torch.int32, device=x.device) if want_index else None
+    check(lib().ytcuda_reduce(op, _dt(x), _dt(y), x.data_ptr(), y.data_ptr(), idx.data_ptr() if want_index else None,
+                              shape, xs, xx.dim(), _i32(ax), len(ax), _stream()))
+    return (y, idx) if want_index else y
+
+
+def sum(x: torch.Tensor, axes) -> torch.Tensor:  # noqa: A001 - mirrors YTensor::sum
+    """Keep-dim sum over an axis or axes (reference YTensor::sum, src/ytensor_math.inl:414-509)."""
+    return _reduce(0, x, axes, False)
+
+
+def mean(x: torch.Tensor, axes) -> torch.Tensor:
+    """Keep-dim mean (reference YTensor::mean, src/ytensor_math.inl:531-574)."""
+    return _reduce(1, x, axes, False)
+
+
+def max(x: torch.Tensor, axes):  # noqa: A001 - mirrors YTensor::max
+    """Keep-dim maximum and the int index of its first occurrence (reference YTensor::max,
+    src/ytensor_math.inl:591-692)."""
+    return _reduce(2, x, axes, True)
+
+
+# ------------------------------------------------------------------ elementwise
+_BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+
+
+def _binary(op: str, a: torch.Tensor, b, out: torch.Tensor | None) -> torch.Tensor:
+    if not isinstance(b, torch.Tensor):
+        return _unary({"add": 3, "sub": 3, "mul": 2, "div": 2}[op], a, out,
+                      {"add": float(b), "sub": -float(b), "mul": float(b), "div": 1.0 / float(b)}[op])
+    _require_cuda(a, b, out)
+    try:
+        shape = torch.broadcast_shapes(a.shape, b.shape)
+    except RuntimeError as e:  # std::runtime_error in the reference (src/kernel/broadcast.inl:133)
+        raise _lib.YtCudaError(_lib.INVALID_ARG, f"broadcast mismatch: {e}")
+    if out is None:
+        out = torch.empty(shape, dtype=a.dtype, device=a.device)
+    elif tuple(out.shape) != tuple(shape):
+        raise _lib.YtCudaError(_lib.INVALID_ARG, "in-place operand cannot be broadcast to the result shape")
+    ae, be = a.expand(shape), b.expand(shape)
+    if len(shape) == 0:
+        ae, be, o = ae.reshape(1), be.reshape(1), out.reshape(1)
+    else:
+        o = out
+    check(lib().ytcuda_binary(_BIN[op], _dt(a), _dt(b), _dt(out), ae.data_ptr(), be.data_ptr(), o.data_ptr(), o.dim(),
+                              _i64(o.shape), _i64(ae.stride()), _i64(be.stride()), _i64(o.stride()), _stream()))
+    return out
+
+
+def add(a, b): return _binary("add", a, b, None)
+def sub(a, b): return _binary("sub", a, b, None)
+def mul(a, b): return _binary("mul", a, b, None)
+def div(a, b): return _binary("div", a, b, None)
+def add_(a, b): return _binary("add", a, b, a)
+def sub_(a, b): return _binary("sub", a, b, a)
+def mul_(a, b): return _binary("mul", a, b, a)
+def div_(a, b): return _binary("div", a, b, a)
+
+
+def _unary(op: int, x: torch.Tensor, out: torch.Tensor | None, param: float = 0.0,
+           out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    _require_cuda(x, out)
+    if out is None:
+        out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    elif tuple(out.shape) != tuple(x.shape):
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "unary: shape mismatch")
+    xx, oo = (x.reshape(1), out.reshape(1)) if x.dim() == 0 else (x, out)
+    check(lib().ytcuda_unary(op, _dt(x), _dt(out), xx.data_ptr(), oo.data_ptr(), xx.dim(), _i64(xx.shape),
+                             _i64(xx.stride()), _i64(oo.stride()), param, _stream()))
+    return out
+
+
+def swish(x): return _unary(1, x, None)
+
+
+def swish_(x):
+    """x * sigmoid(x) in place (reference yt::function::swish_, src/function/activation.inl:631-647)."""
+    return _unary(1, x, x)
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """dtype conversion with the reference's rounding (YTensorBase::cast, include/ytensor_base.hpp:399-404)."""
+    _require_cuda(x)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    return copy_(out, x)
+
+
+def copy_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """Strided copy with conversion (YTensorBase::copy_, src/ytensor_base.inl:257-430)."""
+    _require_cuda(dst, src)
+    if tuple(dst.shape) != tuple(src.shape):
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "copy_: shape mismatch")
+    d, s_ = (dst.reshape(1), src.reshape(1)) if dst.dim() == 0 else (dst, src)
+    check(lib().ytcuda_cast(_dt(src), _dt(dst), s_.data_ptr(), d.data_ptr(), d.dim(), _i64(d.shape), _i64(s_.stride()),
+                            _i64(d.stride()), _stream()))
+    return dst
+
+
+def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """swish(gate) * up for a fused [..., 2*I] projection (example/qwen3/src/qwen3.cpp:193-200)."""
+    _require_cuda(gate_up)
+    if gate_up.stride(-1) != 1 or gate_up.shape[-1] % 2:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "swiglu: last dim must be contiguous and even")
+    inter = gate_up.shape[-1] // 2
+    g2 = gate_up.reshape(-1, 2 * inter)
+    out = torch.empty(*gate_up.shape[:-1], inter, dtype=out_dtype or gate_up.dtype, device=gate_up.device)
+    check(lib().ytcuda_swiglu(_dt(g2), _dt(out), g2.data_ptr(), out.data_ptr(), g2.shape[0], inter, g2.stride(0), inter,
+                              _stream()))
+    return out

@@ -1,0 +1,285 @@
+// Broadcast elementwise operators, unary maps and dtype casts with N-d strides.
+//
+// Contiguous operands move as 128-bit (fp32) / 64-bit (16-bit types) vectors in a grid-stride loop;
+// a right operand that repeats over the leading dims (bias, residual shared by the batch) is
+// indexed by a modulo; everything else goes through per-element index arithmetic on the device.
+//
+// Replaces the operator macros and yt::kernel::broadcast / broadcastInplace (reference
+// src/ytensor_math.inl:22-124, src/kernel/broadcast.inl:167-469), yt::function::swish_
+// (src/function/activation.inl:631-647) and YTensorBase::copy_ / cast (src/ytensor_base.inl:257-430).
+#include "ytc_common.cuh"
+
+namespace ytk {
+
+constexpr int EW_MAXD = 8;
+enum BinOp { B_ADD = 0, B_SUB = 1, B_MUL = 2, B_DIV = 3 };
+enum UnOp { U_COPY = 0, U_SWISH = 1, U_SCALE = 2, U_ADD_SCALAR = 3 };
+
+__device__ __forceinline__ float bin_apply(int op, float a, float b) {
+  switch (op) {
+    case B_ADD: return a + b;
+    case B_SUB: return a - b;
+    case B_MUL: return a * b;
+    default: return a / b;
+  }
+}
+// swish(x) = x * sigmoid(x), sigmoid in the reference's two-branch stable form
+// (src/ytensor_function.inl:42-52).
+__device__ __forceinline__ float swish_ref(float v) {
+  float sig;
+  if (v >= 0.f) {
+    const float z = expf(-v);
+    sig = 1.0f / (1.0f + z);
+  } else {
+    const float z = expf(v);
+    sig = z / (1.0f + z);
+  }
+  return v * sig;
+}
+__device__ __forceinline__ float un_apply(int op, float a, float param) {
+  switch (op) {
+    case U_COPY: return a;
+    case U_SWISH: return swish_ref(a);
+    case U_SCALE: return a * param;
+    default: return a + param;
+  }
+}
+
+struct V4 {
+  float v[4];
+};
+__device__ __forceinline__ V4 ld4(const void* p, int64_t i, int dt) {
+  V4 r;
+  if (dt == YTC_F32) {
+    const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
+    r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+  } else {
+    const uint2 t = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p) + i);
+    const uint16_t h[4] = {static_cast<uint16_t>(t.x & 0xFFFF), static_cast<uint16_t>(t.x >> 16),
+                           static_cast<uint16_t>(t.y & 0xFFFF), static_cast<uint16_t>(t.y >> 16)};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) r.v[k] = (dt == YTC_BF16) ? bf16_bits_to_f32(h[k]) : f16_bits_to_f32_ref(h[k]);
+  }
+  return r;
+}
+__device__ __forceinline__ void st4(void* p, int64_t i, const V4& r, int dt) {
+  if (dt == YTC_F32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(p) + i) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  } else {
+    uint16_t h[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = (dt == YTC_BF16) ? f32_to_bf16_bits_ref(r.v[k]) : f32_to_f16_bits_ref(r.v[k]);
+    uint2 t;
+    t.x = static_cast<uint32_t>(h[0]) | (static_cast<uint32_t>(h[1]) << 16);
+    t.y = static_cast<uint32_t>(h[2]) | (static_cast<uint32_t>(h[3]) << 16);
+    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p) + i) = t;
+  }
+}
+
+// out[i] = a[i] op b[i % bmod] over contiguous memory, 4 elements per thread per trip.
+__global__ void __launch_bounds__(256) binary_vec_kernel(int op, const void* a, const void* b, void* out, int64_t n4,
+                                                         int64_t bmod, int dt_a, int dt_b, int dt_out) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = i * 4;
+    const V4 x = ld4(a, e, dt_a);
+    const V4 y = ld4(b, e % bmod, dt_b);
+    V4 r;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) r.v[k] = bin_apply(op, x.v[k], y.v[k]);
+    st4(out, e, r, dt_out);
+  }
+}
+
+struct NdIndex {
+  int nd;
+  int64_t shape[EW_MAXD], s0[EW_MAXD], s1[EW_MAXD], s2[EW_MAXD];
+};
+
+__global__ void __launch_bounds__(256) binary_nd_kernel(int op, const void* a, const void* b, void* out, int64_t n,
+                                                        const NdIndex ix, int dt_a, int dt_b, int dt_out) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t rem = i, oa = 0, ob = 0, oo = 0;
+    for (int d = ix.nd - 1; d >= 0; --d) {
+      const int64_t c = rem % ix.shape[d];
+      rem /= ix.shape[d];
+      oa += c * ix.s0[d];
+      ob += c * ix.s1[d];
+      oo += c * ix.s2[d];
+    }
+    store_from_f32(out, oo, bin_apply(op, load_as_f32(a, oa, dt_a), load_as_f32(b, ob, dt_b)), dt_out);
+  }
+}
+
+__global__ void __launch_bounds__(256) unary_vec_kernel(int op, const void* x, void* y, int64_t n4, float param,
+                                                        int dt_in, int dt_out) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    V4 v = ld4(x, i * 4, dt_in);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v.v[k] = un_apply(op, v.v[k], param);
+    st4(y, i * 4, v, dt_out);
+  }
+}
+
+__global__ void __launch_bounds__(256) unary_nd_kernel(int op, const void* x, void* y, int64_t n, const NdIndex ix,
+                                                       float param, int dt_in, int dt_out) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t rem = i, oi = 0, oo = 0;
+    for (int d = ix.nd - 1; d >= 0; --d) {
+      const int64_t c = rem % ix.shape[d];
+      rem /= ix.shape[d];
+      oi += c * ix.s0[d];
+      oo += c * ix.s2[d];
+    }
+    store_from_f32(y, oo, un_apply(op, load_as_f32(x, oi, dt_in), param), dt_out);
+  }
+}
+
+// out[r, i] = swish(gu[r, i]) * gu[r, inter + i]: the gate/up halves of a fused projection
+// (reference example/qwen3/src/qwen3.cpp:193-200 does swish_ on one slice, then *= the other).
+__global__ void __launch_bounds__(256) swiglu_kernel(const void* gu, void* out, int64_t rows, int inter, int64_t gu_rs,
+                                                     int64_t out_rs, int dt_in, int dt_out) {
+  const int64_t per_row = inter / 4;
+  const int64_t n4 = rows * per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / per_row, c = (i - r * per_row) * 4;
+    const V4 g = ld4(gu, r * gu_rs + c, dt_in);
+    const V4 u = ld4(gu, r * gu_rs + inter + c, dt_in);
+    V4 o;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o.v[k] = swish_ref(g.v[k]) * u.v[k];
+    st4(out, r * out_rs + c, o, dt_out);
+  }
+}
+
+static int grid_for(int64_t work_items) {
+  const int64_t blocks = (work_items + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+static bool is_contig(int nd, const int64_t* shape, const int64_t* st) {
+  int64_t exp = 1;
+  for (int d = nd - 1; d >= 0; --d) {
+    if (shape[d] != 1 && st[d] != exp) return false;
+    exp *= shape[d];
+  }
+  return true;
+}
+static bool aligned(const void* p, int dt) { return (reinterpret_cast<uint64_t>(p) % (4 * dtype_size(dt))) == 0; }
+
+}  // namespace ytk
+
+using namespace ytk;
+
+extern "C" {
+
+int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const void* b, void* out, int ndim,
+                  const int64_t* shape, const int64_t* astrides, const int64_t* bstrides, const int64_t* ostrides,
+                  void* stream) {
+  YTC_REQUIRE(op >= 0 && op <= 3, "ytcuda_binary: op must be 0..3 (add, sub, mul, div)");
+  YTC_REQUIRE(ndim >= 1 && ndim <= EW_MAXD, "ytcuda_binary: ndim %d outside [1, %d]", ndim, EW_MAXD);
+  YTC_REQUIRE(shape && astrides && bstrides && ostrides, "ytcuda_binary: null shape/strides");
+  YTC_REQUIRE(dt_a >= 0 && dt_a <= 2 && dt_b >= 0 && dt_b <= 2 && dt_out >= 0 && dt_out <= 2, "ytcuda_binary: bad dtype");
+  int64_t n = 1;
+  for (int d = 0; d < ndim; ++d) {
+    YTC_REQUIRE(shape[d] >= 0, "ytcuda_binary: negative extent");
+    n *= shape[d];
+  }
+  if (n == 0) return YTC_OK;
+  YTC_REQUIRE(a && b && out, "ytcuda_binary: null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_contig(ndim, shape, astrides) && is_contig(ndim, shape, ostrides) && n % 4 == 0 && aligned(a, dt_a) &&
+      aligned(b, dt_b) && aligned(out, dt_out)) {
+    // b: zero stride on leading dims, contiguous on the trailing ones => index i % bmod
+    int split = ndim;
+    int64_t exp = 1;
+    while (split > 0 && (shape[split - 1] == 1 || bstrides[split - 1] == exp)) {
+      exp *= shape[split - 1];
+      --split;
+    }
+    bool lead_zero = true;
+    for (int d = 0; d < split; ++d)
+      if (shape[d] != 1 && bstrides[d] != 0) lead_zero = false;
+    if (lead_zero && exp % 4 == 0) {
+      binary_vec_kernel<<<grid_for(n / 4), 256, 0, st>>>(op, a, b, out, n / 4, exp, dt_a, dt_b, dt_out);
+      count_launch();
+      YTC_CUDA(cudaGetLastError());
+      return YTC_OK;
+    }
+  }
+  NdIndex ix;
+  ix.nd = ndim;
+  for (int d = 0; d < ndim; ++d) {
+    ix.shape[d] = shape[d];
+    ix.s0[d] = astrides[d];
+    ix.s1[d] = bstrides[d];
+    ix.s2[d] = ostrides[d];
+  }
+  binary_nd_kernel<<<grid_for(n), 256, 0, st>>>(op, a, b, out, n, ix, dt_a, dt_b, dt_out);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
+                 const int64_t* xstrides, const int64_t* ystrides, float param, void* stream) {
+  YTC_REQUIRE(op >= 0 && op <= 3, "ytcuda_unary: op must be 0..3 (copy, swish, scale, add scalar)");
+  YTC_REQUIRE(ndim >= 1 && ndim <= EW_MAXD, "ytcuda_unary: ndim %d outside [1, %d]", ndim, EW_MAXD);
+  YTC_REQUIRE(shape && xstrides && ystrides, "ytcuda_unary: null shape/strides");
+  YTC_REQUIRE(dt_in >= 0 && dt_in <= 2 && dt_out >= 0 && dt_out <= 2, "ytcuda_unary: bad dtype");
+  int64_t n = 1;
+  for (int d = 0; d < ndim; ++d) {
+    YTC_REQUIRE(shape[d] >= 0, "ytcuda_unary: negative extent");
+    n *= shape[d];
+  }
+  if (n == 0) return YTC_OK;
+  YTC_REQUIRE(x && y, "ytcuda_unary: null tensor");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_contig(ndim, shape, xstrides) && is_contig(ndim, shape, ystrides) && n % 4 == 0 && aligned(x, dt_in) &&
+      aligned(y, dt_out)) {
+    unary_vec_kernel<<<grid_for(n / 4), 256, 0, st>>>(op, x, y, n / 4, param, dt_in, dt_out);
+  } else {
+    NdIndex ix;
+    ix.nd = ndim;
+    for (int d = 0; d < ndim; ++d) {
+      ix.shape[d] = shape[d];
+      ix.s0[d] = xstrides[d];
+      ix.s1[d] = 0;
+      ix.s2[d] = ystrides[d];
+    }
+    unary_nd_kernel<<<grid_for(n), 256, 0, st>>>(op, x, y, n, ix, param, dt_in, dt_out);
+  }
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+int ytcuda_cast(int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape, const int64_t* xstrides,
+                const int64_t* ystrides, void* stream) {
+  return ytcuda_unary(U_COPY, dt_in, dt_out, x, y, ndim, shape, xstrides, ystrides, 0.f, stream);
+}
+
+int ytcuda_swiglu(int dt_in, int dt_out, const void* gate_up, void* out, int64_t rows, int inter, int64_t gu_row_stride,
+                  int64_t out_row_stride, void* stream) {
+  YTC_REQUIRE(dt_in >= 0 && dt_in <= 2 && dt_out >= 0 && dt_out <= 2, "ytcuda_swiglu: bad dtype");
+  YTC_REQUIRE(rows >= 0 && inter >= 0, "ytcuda_swiglu: negative extent");
+  if (rows == 0 || inter == 0) return YTC_OK;
+  YTC_REQUIRE(gate_up && out, "ytcuda_swiglu: null tensor");
+  if (inter % 4 != 0 || gu_row_stride % 4 != 0 || out_row_stride % 4 != 0 || !aligned(gate_up, dt_in) ||
+      !aligned(out, dt_out)) {
+    set_last_error("ytcuda_swiglu: the half width and the row strides must be multiples of 4 elements");
+    return YTC_UNSUPPORTED;
+  }
+  swiglu_kernel<<<grid_for(rows * (inter / 4)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      gate_up, out, rows, inter, gu_row_stride, out_row_stride, dt_in, dt_out);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+}  // extern "C"

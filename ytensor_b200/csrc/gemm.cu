@@ -32,6 +32,8 @@ struct GemmTcParams {
   int64_t rsc, csc, bsc;
   int out_dtype;
   int tiles_m, tiles_n, total_tiles, k_blocks;
+  int a_prefetch;  // k-blocks by which an L2 prefetch of A runs ahead of the shared-memory loads (0 = off)
+  int split_loads; // K-major tiles fetched as 64-row boxes
   int* status;
 };
 
@@ -174,6 +176,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
+      // A is streamed from HBM once; an L2 prefetch a few k-blocks ahead of the shared-memory ring
+      // takes the DRAM latency off the ring (B is small and stays L2-resident by reuse).
+      auto prefetch_a = [&](int tile, int kb) {
+        if (tile >= p.total_tiles) return;
+        const int b = tile / tiles_per_batch;
+        const int rem = tile - b * tiles_per_batch;
+        const int mb = rem / p.tiles_n;
+        const int ba = p.a_bcast ? 0 : b;
+        if (!p.a_mn) {
+          tma_prefetch_l2_3d(&tmA, kb * TC_BK, mb * TC_BM, ba);
+        } else {
+#pragma unroll
+          for (int c = 0; c < TC_BM / 64; ++c) tma_prefetch_l2_3d(&tmA, mb * TC_BM + c * 64, kb * TC_BK, ba);
+        }
+      };
+      int pf_tile = blockIdx.x, pf_kb = 0;
+      if (p.a_prefetch > 0) {
+        for (int i = 0; i < p.a_prefetch; ++i) {
+          prefetch_a(pf_tile, pf_kb);
+          if (++pf_kb == p.k_blocks) {
+            pf_kb = 0;
+            pf_tile += gridDim.x;
+          }
+        }
+      }
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
         const int b = tile / tiles_per_batch;
         const int rem = tile - b * tiles_per_batch;
@@ -186,18 +213,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             ok = false;
             break;
           }
+          if (p.a_prefetch > 0) {
+            prefetch_a(pf_tile, pf_kb);
+            if (++pf_kb == p.k_blocks) {
+              pf_kb = 0;
+              pf_tile += gridDim.x;
+            }
+          }
           mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
           if (!p.a_mn) {
-            tma_load_3d(sa, &tmA, &full_bar[stage], kb * TC_BK, mb * TC_BM, ba);
+            if (p.split_loads) {
+#pragma unroll
+              for (int c = 0; c < TC_BM / 64; ++c)
+                tma_load_3d(sa + c * 8192, &tmA, &full_bar[stage], kb * TC_BK, mb * TC_BM + c * 64, ba);
+            } else {
+              tma_load_3d(sa, &tmA, &full_bar[stage], kb * TC_BK, mb * TC_BM, ba);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < TC_BM / 64; ++c)
               tma_load_3d(sa + c * 8192, &tmA, &full_bar[stage], mb * TC_BM + c * 64, kb * TC_BK, ba);
           }
           if (!p.b_mn) {
-            tma_load_3d(sb, &tmB, &full_bar[stage], kb * TC_BK, nb * BN, bb);
+            if (p.split_loads) {
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c)
+                tma_load_3d(sb + c * 8192, &tmB, &full_bar[stage], kb * TC_BK, nb * BN + c * 64, bb);
+            } else {
+              tma_load_3d(sb, &tmB, &full_bar[stage], kb * TC_BK, nb * BN, bb);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
@@ -467,6 +513,11 @@ static bool tc_operand_ok(const void* ptr, int64_t rs, int64_t cs, int64_t bs, i
   return true;
 }
 
+// L2 prefetch distance of the A operand in k-blocks (see GemmTcParams::a_prefetch).
+static int g_tc_a_prefetch = 0;
+// 1 = fetch K-major operand tiles as 64-row boxes instead of one tall box.
+static int g_tc_split_loads = 0;
+
 static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
                      float alpha, float beta, int a_mn, int64_t lda, int b_mn, int64_t ldb, int64_t rsc, int64_t csc,
                      int64_t batch, int64_t bsa, int64_t bsb, int64_t bsc, cudaStream_t st) {
@@ -479,7 +530,7 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
     const uint64_t nb = (a_bcast || batch == 1) ? 1 : static_cast<uint64_t>(batch);
     uint64_t dims[3], strides[2];
     uint32_t box[3];
-    if (!a_mn) { dims[0] = k; dims[1] = m; box[0] = TC_BK; box[1] = TC_BM; }
+    if (!a_mn) { dims[0] = k; dims[1] = m; box[0] = TC_BK; box[1] = g_tc_split_loads ? 64 : TC_BM; }
     else       { dims[0] = m; dims[1] = k; box[0] = 64;    box[1] = TC_BK; }
     dims[2] = nb;
     box[2] = 1;
@@ -493,7 +544,7 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
     const uint64_t nb = (b_bcast || batch == 1) ? 1 : static_cast<uint64_t>(batch);
     uint64_t dims[3], strides[2];
     uint32_t box[3];
-    if (!b_mn) { dims[0] = k; dims[1] = n; box[0] = TC_BK; box[1] = static_cast<uint32_t>(BN); }
+    if (!b_mn) { dims[0] = k; dims[1] = n; box[0] = TC_BK; box[1] = g_tc_split_loads ? 64u : static_cast<uint32_t>(BN); }
     else       { dims[0] = n; dims[1] = k; box[0] = 64;    box[1] = TC_BK; }
     dims[2] = nb;
     box[2] = 1;
@@ -521,6 +572,8 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
   }
   p.total_tiles = static_cast<int>(total);
   p.k_blocks = (k + TC_BK - 1) / TC_BK;
+  p.a_prefetch = g_tc_a_prefetch;
+  p.split_loads = g_tc_split_loads;
   p.status = device_status_word();
   if (!p.status) {
     set_last_error("ytcuda_gemm: no device status word");
@@ -593,6 +646,13 @@ static int g_gemm_path = 0;
 using namespace ytk;
 
 extern "C" {
+
+int ytcuda_gemm_set_tuning(int a_prefetch_kblocks, int split_loads) {
+  YTC_REQUIRE(a_prefetch_kblocks >= 0 && a_prefetch_kblocks <= 64, "ytcuda_gemm_set_tuning: prefetch distance outside [0, 64]");
+  g_tc_a_prefetch = a_prefetch_kblocks;
+  g_tc_split_loads = split_loads ? 1 : 0;
+  return YTC_OK;
+}
 
 int ytcuda_gemm_set_path(int path) {
   YTC_REQUIRE(path >= 0 && path <= 2, "ytcuda_gemm_set_path: path must be 0, 1 or 2");

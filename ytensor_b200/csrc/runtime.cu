@@ -72,6 +72,27 @@ int read_device_status(cudaStream_t st) {
   return h;
 }
 
+static void* g_ws[kMaxDev] = {nullptr};
+static size_t g_ws_cap[kMaxDev] = {0};
+
+void* device_workspace(size_t bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_ws_cap[dev] < bytes) {
+    if (g_ws[dev]) {
+      cudaDeviceSynchronize();
+      cudaFree(g_ws[dev]);
+      g_ws[dev] = nullptr;
+      g_ws_cap[dev] = 0;
+    }
+    size_t cap = bytes < (1u << 20) ? (1u << 20) : bytes;
+    if (cudaMalloc(&g_ws[dev], cap) != cudaSuccess) return nullptr;
+    g_ws_cap[dev] = cap;
+  }
+  return g_ws[dev];
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

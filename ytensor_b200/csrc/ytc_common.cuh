@@ -162,6 +162,10 @@ int* device_status_word();
 // Reads and clears the device status word (synchronises the stream).
 int read_device_status(cudaStream_t st);
 
+// Per-device scratch buffer owned by the library (grown on demand, never shrunk). One buffer per
+// device: calls that use it and overlap on different streams would race.
+void* device_workspace(size_t bytes);
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup, so that
 // the library has no link-time dependency on libcuda.
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base,
