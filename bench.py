@@ -29,6 +29,8 @@ sys.path.insert(0, str(ROOT))
 
 BATCH, M, K, N = 64, 2048, 4096, 4096
 FLOPS_PER_STEP = 2.0 * BATCH * M * K * N          # 4 398 046 511 104
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised under profiles/
+TRAFFIC_BYTES_PER_LAUNCH = 2.048e9
 WORKLOAD = "configs[1]: bf16 batched GEMM A[64,2048,4096] . B[4096,4096], fp32 accumulate, bf16 out"
 
 
@@ -61,7 +63,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -271,7 +273,9 @@ def device_arm(args) -> None:
         avg_launch_ms = statistics.mean(per_launch_ms)
         achieved = FLOPS_PER_STEP / (avg_launch_ms * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                    "frac": achieved / peaks["bf16_tflops"], "traffic": TRAFFIC_BYTES_PER_LAUNCH if BATCH == 64 else None,
+                    "traffic_note": "ncu dram read+write of a batch-8 capture scaled to batch 64 (A and C x8, B once); "
+                                    "see profiles/gemm_tc_kernel_bf16_config2.md",
                     "kernel": "gemm_tc_kernel<256>", "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
                     "frac_of_sustained_peak": (achieved / peaks["bf16_tflops_sustained"]
                                                if peaks.get("bf16_tflops_sustained") else None),
@@ -290,18 +294,116 @@ def device_arm(args) -> None:
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------- other configs
+def _time_steps(torch, fn, steps, warmup):
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        fn()
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    return [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+
+
+def attention_arm(args) -> None:
+    """BASELINE configs[2]: causal flash attention bf16, batch 16, 32 q / 8 kv heads, head_dim 128, seq 4096.
+    `--batch` shrinks the batch for profiling captures. Single GPU; prints one JSON line."""
+    import torch
+
+    from ytensor_b200 import _lib, api
+
+    torch.cuda.set_device(0)
+    L = _lib.lib()
+    B = 16 if args.batch == 64 else args.batch
+    H, KVH, S, D = 32, 8, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(B, H, S, D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B, KVH, S, D, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B, KVH, S, D, device="cuda", generator=g).to(torch.bfloat16)
+    flops = 4.0 * B * H * S * S * D / 2  # causal convention: half of the square
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = L.ytcuda_launch_count()
+    ts = _time_steps(torch, lambda: api.scaledDotProductAttention(q, k, v, causal=True), args.steps, args.warmup)
+    launches = L.ytcuda_launch_count() - n0 - max(args.warmup, 3)
+    clocks = sampler.stop()
+    _lib.check(L.ytcuda_device_status(None))
+    peaks = measured_peaks()
+    ms = statistics.mean(ts)
+    val = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "flash_attn_causal_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"configs[2]: causal flash attention bf16, batch {B}, 32 q / 8 kv heads, head_dim 128, "
+                               f"seq 4096" + ("" if B == 16 else " (PROFILING CASE: reduced batch)"),
+                   "l2": "inputs larger than L2 (Q alone is 33.5 MB per batch item)"},
+        "roofline": {"bound": "tensor", "achieved": val, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": val / peaks["bf16_tflops"], "traffic": None, "kernel": "flash_tc_kernel<128>",
+                     "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
+                     "algorithmic_flops_per_launch": flops, "non_causal_equivalent_tflops": 2 * val},
+        "gpu_launches": int(launches), "clocks": clocks}))
+
+
+def chain_arm(args) -> None:
+    """BASELINE configs[3]: y = bf16(softmax(rmsNorm(x, w, -1, 1e-6) + r, -1)) on x [32,4096,4096] fp32 with the
+    residual [1,4096,4096] shared by the batch. `--batch` shrinks the batch for profiling captures."""
+    import torch
+
+    from ytensor_b200 import _lib, api
+
+    torch.cuda.set_device(0)
+    L = _lib.lib()
+    B = 32 if args.batch == 64 else args.batch
+    R, H = 4096, 4096
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(B, R, H, device="cuda", generator=g)
+    w = torch.rand(H, device="cuda", generator=g) * 0.2 + 0.9
+    r = torch.randn(1, R, H, device="cuda", generator=g)
+    algo_bytes = x.numel() * 4 + r.numel() * 4 + H * 4 + x.numel() * 2
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = L.ytcuda_launch_count()
+    ts = _time_steps(torch, lambda: api.rmsnorm_add_softmax_cast(x, w, r), args.steps, args.warmup)
+    launches = L.ytcuda_launch_count() - n0 - max(args.warmup, 3)
+    clocks = sampler.stop()
+    peaks = measured_peaks()
+    ms = statistics.mean(ts)
+    val = algo_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "memory_chain_gbs", "value": val, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 in, bf16 out", "data": "synthetic",
+        "config": {"workload": f"configs[3]: RMSNorm + broadcast residual + row softmax + cast on [{B},4096,4096]"
+                               + ("" if B == 32 else " (PROFILING CASE: reduced batch)"),
+                   "l2": "inputs larger than L2 (x is 2.1 GB)"},
+        "roofline": {"bound": "hbm", "achieved": val, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": val / peaks["hbm_gbs"], "traffic": None, "kernel": "row_kernel<OP_CHAIN,256>",
+                     "peak_source": f"{peaks['source']} (copy bandwidth)", "algorithmic_bytes_per_launch": algo_bytes},
+        "gpu_launches": int(launches), "clocks": clocks}))
+
+
 def main() -> None:
     global BATCH, FLOPS_PER_STEP, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "attn", "chain"],
+                    help="gemm (default) is the headline bench line; attn and chain measure configs[2] and configs[3]")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures only)")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="batch items per step; anything but 64 is a profiling case, not a bench line")
     args = ap.parse_args()
+    if args.workload == "attn":
+        return attention_arm(args)
+    if args.workload == "chain":
+        return chain_arm(args)
     if args.batch != BATCH:
         BATCH = args.batch
         FLOPS_PER_STEP = 2.0 * BATCH * M * K * N

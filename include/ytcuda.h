@@ -147,6 +147,31 @@ int ytcuda_cast(int dt_in, int dt_out, const void* x, void* y, int ndim, const i
 int ytcuda_swiglu(int dt_in, int dt_out, const void* gate_up, void* out, int64_t rows, int inter, int64_t gu_row_stride,
                   int64_t out_row_stride, void* stream);
 
+/* ---------------------------------------------------------------- attention
+ * O = softmax(scale * Q K^T + bias, masked) V per (batch, query head). Q [batch, kv_heads*groups, q_len, head_dim],
+ * K [batch, kv_heads, kv_len, head_dim], V [batch, kv_heads, kv_len, value_dim], O like Q with value_dim; query head
+ * h reads K/V head h / groups (the zero-stride repeat_kv view of example/qwen3/src/qwen3.cpp:252-264,583-589).
+ * *_strides = {batch, head, row} strides in elements; the innermost dim has unit stride.
+ * scale == 0 means 1/sqrt(head_dim) (src/function/ops.inl:378-381).
+ * mask_kind 0: none; 1: causal, key c is visible to query r iff c <= r + causal_offset (the reference's
+ * make_causal_mask uses causal_offset = kv_len - q_len, qwen3.cpp:46-55); 2: bool mask bytes [q_len, kv_len] with
+ * row stride mask_row_stride. bias: optional fp32 [q_len, kv_len] added to the scaled scores. A query row that sees
+ * no key yields zeros (src/kernel/avx2/flash_attention.inl:241-244,327-331).
+ * BF16 / F16 with head_dim == value_dim in {64, 128} and 16-byte aligned rows run on the tcgen05 kernel; every other
+ * case (F32 included) runs on the one-warp-per-row kernel.
+ * Replaces yt::function::scaledDotProductAttention (include/function/ops.hpp:26-70, src/function/ops.inl:109-234,
+ * 368-503) and yt::kernel::avx2::flash_attention (include/kernel/avx2/flash_attention.hpp:21-69). */
+int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V, void* O, int batch, int kv_heads,
+                          int groups, int q_len, int kv_len, int head_dim, int value_dim, float scale,
+                          const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                          const int64_t* o_strides, int mask_kind, int causal_offset, const uint8_t* mask,
+                          int64_t mask_row_stride, const float* bias, int64_t bias_row_stride, int64_t bias_col_stride,
+                          void* stream);
+
+/* Kernel choice of ytcuda_flash_attn_fwd: 0 = automatic, 1 = always the one-warp-per-row kernel, 2 = tcgen05 or
+ * YTC_UNSUPPORTED. The counterpart of the per-call sdpaBackend argument (include/function/ops.hpp:21-24). */
+int ytcuda_attn_set_path(int path);
+
 #ifdef __cplusplus
 }
 #endif

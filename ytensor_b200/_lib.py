@@ -39,6 +39,9 @@ SIGNATURES = {
     "ytcuda_unary": (_i, [_i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp]),
     "ytcuda_cast": (_i, [_i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
     "ytcuda_swiglu": (_i, [_i, _i, _vp, _vp, _i64, _i, _i64, _i64, _vp]),
+    "ytcuda_flash_attn_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _i, _i,
+                                   _vp, _i64, _vp, _i64, _i64, _vp]),
+    "ytcuda_attn_set_path": (_i, [_i]),
 }
 
 

@@ -320,3 +320,80 @@ def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch
     check(lib().ytcuda_swiglu(_dt(g2), _dt(out), g2.data_ptr(), out.data_ptr(), g2.shape[0], inter, g2.stride(0), inter,
                               _stream()))
     return out
+
+
+# ------------------------------------------------------------------ attention
+def _heads_view(t: torch.Tensor, what: str):
+    """[batch..., heads..., len, dim] -> (tensor, batch, heads, strides {batch, head, row}); the leading dims must
+    collapse into one batch stride and one head stride, and the last dim must have unit stride."""
+    if t.stride(-1) != 1 and t.shape[-1] != 1:
+        t = copy_(torch.empty(t.shape, dtype=t.dtype, device=t.device), t)
+    return t
+
+
+def scaledDotProductAttention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, scale: float = 0.0,
+                              mask: torch.Tensor | None = None, bias: torch.Tensor | None = None, *,
+                              causal: bool = False, causal_offset: int | None = None) -> torch.Tensor:
+    """softmax(scale * Q K^T + bias, masked) V (reference yt::function::scaledDotProductAttention,
+    src/function/ops.inl:368-425).
+
+    Shapes as the reference's callers use them: query [b, kv_heads, groups, q_len, d] with key / value either the
+    zero-stride repeat [b, kv_heads, groups, kv_len, d] or plain [b, kv_heads, kv_len, d]; 4-D query
+    [b, heads, q_len, d] with [b, kv_heads, kv_len, d] keys (heads a multiple of kv_heads); 3-D and 2-D forms have no
+    batch / head dims. `mask` is a bool [q_len, kv_len] tensor; `causal=True` is the predicate form c <= r + offset
+    with offset = kv_len - q_len unless given. Mismatched shapes raise ValueError like std::invalid_argument."""
+    _require_cuda(query, key, value, mask, bias)
+    if query.shape[-1] != key.shape[-1]:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "Query and key head dim must match.")
+    if key.shape[-2] != value.shape[-2]:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "Key/value sequence length must match.")
+    if not (query.dtype == key.dtype == value.dtype):
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "scaledDotProductAttention: dtypes differ")
+    lq, d = query.shape[-2:]
+    lk, dv = value.shape[-2:]
+    out_shape = (*query.shape[:-1], dv)
+    q, k, v = query, key, value
+    if q.dim() == 5:
+        b, kvh, g = q.shape[:3]
+        if k.dim() == 5:
+            k, v = k[:, :, 0], v[:, :, 0]
+        q = q.reshape(b, kvh * g, lq, d)
+    elif q.dim() == 4:
+        b, h = q.shape[:2]
+        kvh = k.shape[1]
+        if h % kvh:
+            raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "query heads must be a multiple of key/value heads")
+        g = h // kvh
+    else:
+        lead = q.shape[:-2]
+        n = 1
+        for x in lead:
+            n *= x
+        q, k, v = q.reshape(1, n, lq, d), k.reshape(1, n, lk, d), v.reshape(1, n, lk, dv)
+        b, kvh, g = 1, n, 1
+    if tuple(k.shape) != (b, kvh, lk, d) or tuple(v.shape) != (b, kvh, lk, dv):
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "key/value batch or head dims do not match the query")
+    q, k, v = _heads_view(q, "query"), _heads_view(k, "key"), _heads_view(v, "value")
+    mask_kind, mptr, mrs, off = 0, None, 0, 0
+    if mask is not None:
+        if tuple(mask.shape) != (lq, lk):
+            raise _lib.YtCudaInvalidArgument(
+                _lib.INVALID_ARG, "Mask shape must match the last two dimensions of the score tensor.")
+        m8 = mask.to(torch.uint8) if mask.dtype != torch.uint8 else mask
+        m8 = m8.contiguous()
+        mask_kind, mptr, mrs = 2, m8.data_ptr(), m8.stride(0)
+    elif causal:
+        mask_kind, off = 1, (lk - lq) if causal_offset is None else int(causal_offset)
+    bptr, brs, bcs = None, 0, 0
+    if bias is not None:
+        if tuple(bias.shape) != (lq, lk):
+            raise _lib.YtCudaInvalidArgument(
+                _lib.INVALID_ARG, "Bias shape must match the last two dimensions of the score tensor.")
+        bias = bias.float()
+        bptr, brs, bcs = bias.data_ptr(), bias.stride(0), bias.stride(1)
+    out = torch.empty(b, kvh * g, lq, dv, dtype=query.dtype, device=query.device)
+    check(lib().ytcuda_flash_attn_fwd(_dt(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b, kvh, g, lq,
+                                      lk, d, dv, float(scale), _i64(q.stride()[:3]), _i64(k.stride()[:3]),
+                                      _i64(v.stride()[:3]), _i64(out.stride()[:3]), mask_kind, off, mptr, mrs, bptr,
+                                      brs, bcs, _stream()))
+    return out.reshape(out_shape)

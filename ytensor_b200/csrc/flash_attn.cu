@@ -1,0 +1,741 @@
+// Scaled dot-product attention forward for the YTensor device backend.
+//
+//  * flash_tc_kernel  : bf16 / fp16, head_dim == value_dim in {64, 128}. One CTA works on TWO 128-row query
+//                       tiles that share the same K/V stream (two query heads of one GQA group, or two
+//                       neighbouring row blocks of one head). Warp 0 feeds shared memory with TMA, warp 1
+//                       issues tcgen05.mma: S_t = Q_t K^T into tensor memory, and O_t += P_t V with P_t read
+//                       straight from tensor memory. Two softmax warpgroups (one per tile, one thread per
+//                       query row) turn S into P with an online softmax kept in registers: running maximum
+//                       and sum in the log2 domain, exp2 with the scale folded in, and O rescaled only when
+//                       the maximum has grown by more than 2^8. While one warpgroup does softmax, the tensor
+//                       core works on the other tile.
+//  * attn_simt_kernel : any dtype (fp32 included), any head / value dim, one warp per query row. The
+//                       catch-all for shapes the tensor-core kernel does not take.
+//
+// Both honour: no mask / causal window anchored at the end of the keys / a bool mask [q_len, kv_len];
+// an optional additive fp32 bias [q_len, kv_len]; rows that see no key produce zeros.
+// Replaces yt::function::scaledDotProductAttention and yt::kernel::avx2::flash_attention
+// (reference src/function/ops.inl:109-234,368-425, src/kernel/avx2/flash_attention.inl:202-443).
+#include <math_constants.h>
+
+#include "ptx_sm100.cuh"
+#include "ytc_common.cuh"
+
+namespace ytk {
+
+constexpr int FA_BM = 128;      // query rows per tile
+constexpr int FA_BN = 128;      // keys per K/V tile
+constexpr int FA_STAGES = 2;    // K/V ring depth
+constexpr int FA_THREADS = 384; // 4 service warps + 2 softmax warpgroups
+constexpr float FA_LOG2E = 1.4426950408889634f;
+constexpr float FA_RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct FlashParams {
+  void* O;
+  int64_t o_sb, o_sh, o_sr;  // output strides (elements): batch, head, row; unit stride on the value dim
+  const uint8_t* mask;       // bool mask [q_len, kv_len] or null
+  int64_t mask_rs;
+  const float* bias;         // additive bias [q_len, kv_len] or null
+  int64_t bias_rs, bias_cs;
+  int batch, kv_heads, groups, q_len, kv_len;
+  int causal;                // 1: key c visible to row r iff c <= r + causal_off
+  int causal_off;
+  float scale_log2;          // scale * log2(e)
+  int is_bf16;
+  int pair_heads;            // 1: the two tiles are two heads of one group; 0: two neighbouring row blocks
+  int row_blocks;            // query row blocks per CTA column (in units of one or two tiles, see kernel)
+  uint32_t idesc_s, idesc_pv;
+  int* status;
+};
+
+// 2^x by the special-function unit (ex2.approx.ftz): -inf gives 0, relative error about 2^-22.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D>
+struct FaSmem {
+  static constexpr int TILE_BYTES = FA_BM * D * 2;  // one Q / K / V tile
+  static constexpr int Q_OFF = 0;
+  static constexpr int KV_OFF = 2 * TILE_BYTES;
+  static constexpr int BAR_OFF = KV_OFF + FA_STAGES * 2 * TILE_BYTES;
+  // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full[2], o_ready[2], tmem slot, abort
+  static constexpr int NBAR = 1 + 3 * FA_STAGES + 6;
+  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+// Loads one [128 x D] tile as D/64 boxes of [128 rows x 128 bytes] (128-byte swizzle).
+template <int D>
+__device__ __forceinline__ void fa_load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int row, int head,
+                                             int batch) {
+#pragma unroll
+  for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (FA_BM * 128), m, bar, c * 64, row, head, batch);
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+    flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+  using S = FaSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::BAR_OFF);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* v_full = k_full + FA_STAGES;
+  uint64_t* kv_empty = v_full + FA_STAGES;
+  uint64_t* s_full = kv_empty + FA_STAGES;
+  uint64_t* p_full = s_full + 2;
+  uint64_t* o_ready = p_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which two query tiles this CTA owns ---------------------------------------------------
+  // blockIdx.x walks row blocks from the LAST one down (the longest causal rows start first).
+  const int rb = p.row_blocks - 1 - static_cast<int>(blockIdx.x);
+  const int hsel = blockIdx.y;  // head pair (pair_heads) or head
+  const int b = blockIdx.z;
+  int q_head[2], q_row0[2], kv_head;
+  if (p.pair_heads) {
+    const int heads = p.kv_heads * p.groups;
+    q_head[0] = hsel * 2;
+    q_head[1] = hsel * 2 + 1;
+    if (q_head[1] >= heads) q_head[1] = q_head[0];
+    q_row0[0] = q_row0[1] = rb * FA_BM;
+    kv_head = q_head[0] / p.groups;
+  } else {
+    q_head[0] = q_head[1] = hsel;
+    q_row0[0] = rb * 2 * FA_BM;
+    q_row0[1] = rb * 2 * FA_BM + FA_BM;
+    kv_head = hsel / p.groups;
+  }
+  const bool tile_on[2] = {q_row0[0] < p.q_len,
+                           q_row0[1] < p.q_len && !(p.pair_heads && q_head[1] == q_head[0])};
+  // number of K/V tiles each query tile needs
+  int n_tiles[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    int last_key = p.kv_len - 1;
+    if (p.causal) {
+      const int lim = q_row0[t] + FA_BM - 1 + p.causal_off;
+      if (lim < last_key) last_key = lim;
+    }
+    n_tiles[t] = (!tile_on[t] || last_key < 0) ? 0 : last_key / FA_BN + 1;
+  }
+  const int n_max = n_tiles[0] > n_tiles[1] ? n_tiles[0] : n_tiles[1];
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < FA_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 4);  // one arrival per softmax warp
+      mbar_init(&o_ready[t], 1);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // tensor-memory columns: S0/P0 at 0, S1/P1 at 128, O0 at 256, O1 at 384
+  const uint32_t t_s[2] = {tmem_base, tmem_base + 128u};
+  const uint32_t t_o[2] = {tmem_base + 256u, tmem_base + 384u};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_max > 0) {
+      int n_q = 0;
+      for (int t = 0; t < 2; ++t) n_q += tile_on[t] ? 1 : 0;
+      mbar_expect_tx(q_full, static_cast<uint32_t>(n_q) * S::TILE_BYTES);
+      for (int t = 0; t < 2; ++t)
+        if (tile_on[t]) fa_load_tile<D>(smem + S::Q_OFF + t * S::TILE_BYTES, &tmQ, q_full, q_row0[t], q_head[t], b);
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % FA_STAGES;
+        if (!mbar_wait(&kv_empty[s], phase ^ 1u, abort_word)) {
+          ok = false;
+          break;
+        }
+        uint8_t* ks = smem + S::KV_OFF + s * 2 * S::TILE_BYTES;
+        uint8_t* vs = ks + S::TILE_BYTES;
+        mbar_expect_tx(&k_full[s], S::TILE_BYTES);
+        fa_load_tile<D>(ks, &tmK, &k_full[s], j * FA_BN, kv_head, b);
+        mbar_expect_tx(&v_full[s], S::TILE_BYTES);
+        fa_load_tile<D>(vs, &tmV, &v_full[s], j * FA_BN, kv_head, b);
+        ++issued;
+        if (s == FA_STAGES - 1) phase ^= 1u;
+      }
+      if (!ok) {
+        // bounded drain of the copies still in flight
+        const long long t0 = clock64();
+        for (int s = 0; s < FA_STAGES && s < issued; ++s)
+          while (!mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1) && clock64() - t0 < 20000000ll) {
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_max > 0) {
+      const uint32_t q_base = smem_u32(smem + S::Q_OFF);
+      // S_t = Q_t . K^T : both operands K-major, D/16 steps; 64-element chunks are FA_BM*128 bytes apart
+      auto issue_s = [&](int t, int stage) {
+        const uint32_t qa = q_base + t * S::TILE_BYTES;
+        const uint32_t ka = smem_u32(smem + S::KV_OFF + stage * 2 * S::TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (FA_BM * 128) + (kk & 3) * 32;
+          tc_mma_f16(t_s[t], umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                     p.idesc_s, kk != 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[t]);
+      };
+      // O_t (+)= P_t . V : A = P from tensor memory (16-bit pairs, 8 columns per 16 keys),
+      // B = V, unit stride along the value dim (MN-major): 16 keys = 2048 bytes, 64-wide chunks 16 KiB apart
+      auto issue_pv = [&](int t, int stage, bool accumulate) {
+        const uint32_t va = smem_u32(smem + S::KV_OFF + stage * 2 * S::TILE_BYTES + S::TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < FA_BN / 16; ++kk)
+          tc_mma_f16_ts(t_o[t], t_s[t] + kk * 8, umma_smem_desc_sw128(va + kk * 2048, FA_BM * 128, 1024), p.idesc_pv,
+                        (accumulate || kk != 0) ? 1u : 0u);
+        tc_commit(&o_ready[t]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_word);
+      uint32_t kv_phase = 0;
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_word);
+      if (ok) {
+        tc_fence_after();
+        if (n_tiles[0] > 0) issue_s(0, 0);
+        if (n_tiles[1] > 0) issue_s(1, 0);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % FA_STAGES;
+        const int sn = (j + 1) % FA_STAGES;
+        const uint32_t next_phase = (sn == 0) ? (kv_phase ^ 1u) : kv_phase;
+        const uint32_t pj = static_cast<uint32_t>(j & 1);
+        if (!mbar_wait(&v_full[s], kv_phase, abort_word)) break;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < n_tiles[t]) {
+            if (!mbar_wait(&p_full[t], pj, abort_word)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_pv(t, s, j > 0);
+          }
+          if (j + 1 < n_tiles[t]) {
+            if (!mbar_wait(&k_full[sn], next_phase, abort_word)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_s(t, sn);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&kv_empty[s]);  // every MMA that read stage s has been issued before this point
+        if (s == FA_STAGES - 1) kv_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ softmax warpgroups (one per query tile)
+    const int t = (warp - 4) >> 2;
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    const int row = q_row0[t] + row_in_tile;  // global query row
+    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t ts = t_s[t] + lane_sel, to = t_o[t] + lane_sel;
+    const int nt = n_tiles[t];
+    float m_run = -CUDART_INF_F;  // running maximum, log2 domain
+    float l_run = 0.f;
+    bool ok = true;
+    const bool elementwise_mask = (p.mask != nullptr) || (p.bias != nullptr);
+
+    for (int j = 0; j < nt; ++j) {
+      if (!mbar_wait(&s_full[t], static_cast<uint32_t>(j & 1), abort_word)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int key0 = j * FA_BN;
+      // Three kinds of tile: `full` (every key visible to every row), limited (visibility is "key <= per-row
+      // limit": causal diagonal, end of the keys, rows past q_len), general (bool mask or bias present).
+      int row_limit = (row < p.q_len) ? p.kv_len - 1 : -1;
+      if (p.causal && row + p.causal_off < row_limit) row_limit = row + p.causal_off;
+      const int cl = row_limit - key0;  // columns 0..cl of this tile are visible to this thread's row
+      const bool full = !elementwise_mask && (key0 + FA_BN <= p.kv_len) && (q_row0[t] + FA_BM <= p.q_len) &&
+                        (!p.causal || key0 + FA_BN - 1 <= q_row0[t] + p.causal_off);
+      auto score = [&](uint32_t raw, int c) -> float {  // general tiles only
+        float v = __uint_as_float(raw) * p.scale_log2;
+        const int key = key0 + c;
+        bool vis = c <= cl;
+        if (vis && p.mask) vis = p.mask[static_cast<int64_t>(row) * p.mask_rs + key] != 0;
+        if (vis && p.bias) v += p.bias[static_cast<int64_t>(row) * p.bias_rs + key * p.bias_cs] * FA_LOG2E;
+        return vis ? v : -CUDART_INF_F;
+      };
+      // pass 1: row maximum. Without mask / bias the maximum is taken over the raw scores (one instruction per
+      // element, two with the per-row limit) and scaled afterwards; a negative scale flips max into min.
+      float mx = -CUDART_INF_F;
+      if (!elementwise_mask) {
+        const bool pos = p.scale_log2 >= 0.f;
+        const float ident = pos ? -CUDART_INF_F : CUDART_INF_F;
+        float a0 = ident, a1 = ident, a2 = ident, a3 = ident;
+#pragma unroll 1
+        for (int c0 = 0; c0 < FA_BN; c0 += 64) {
+          uint32_t r[64];
+          tmem_ld_32x32b_x64(ts + c0, r);
+          tmem_ld_wait();
+          if (full && pos) {  // the common tile: one max per element
+#pragma unroll
+            for (int e = 0; e < 64; e += 4) {
+              a0 = fmaxf(a0, __uint_as_float(r[e]));
+              a1 = fmaxf(a1, __uint_as_float(r[e + 1]));
+              a2 = fmaxf(a2, __uint_as_float(r[e + 2]));
+              a3 = fmaxf(a3, __uint_as_float(r[e + 3]));
+            }
+          } else {
+            const int cc = full ? 64 : cl - c0;
+#pragma unroll
+            for (int e = 0; e < 64; e += 4) {
+              const float v0 = (e <= cc) ? __uint_as_float(r[e]) : ident;
+              const float v1 = (e + 1 <= cc) ? __uint_as_float(r[e + 1]) : ident;
+              const float v2 = (e + 2 <= cc) ? __uint_as_float(r[e + 2]) : ident;
+              const float v3 = (e + 3 <= cc) ? __uint_as_float(r[e + 3]) : ident;
+              if (pos) {
+                a0 = fmaxf(a0, v0); a1 = fmaxf(a1, v1); a2 = fmaxf(a2, v2); a3 = fmaxf(a3, v3);
+              } else {
+                a0 = fminf(a0, v0); a1 = fminf(a1, v1); a2 = fminf(a2, v2); a3 = fminf(a3, v3);
+              }
+            }
+          }
+        }
+        const float ext = pos ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : fminf(fminf(a0, a1), fminf(a2, a3));
+        mx = (ext == ident) ? -CUDART_INF_F : ext * p.scale_log2;
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < FA_BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(ts + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, score(r[e], c0 + e));
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      if (j == 0) {
+        m_run = m_new;
+      } else {
+        const bool grow = (m_new - m_run) > FA_RESCALE_THRESHOLD;  // also true when m_run is -inf and m_new finite
+        if (__any_sync(0xffffffffu, grow)) {
+          // O_t *= 2^(m_run - m_new) for this warp's 32 rows; needs the previous P.V to have landed
+          if (!mbar_wait(&o_ready[t], static_cast<uint32_t>((j - 1) & 1), abort_word)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const float alpha = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_run - m_new);  // m_run == -inf gives 0
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(to + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st_32x32b_x16(to + c0, r);
+          }
+          l_run *= alpha;
+          m_run = m_new;
+        }
+      }
+      const float m_use = (m_run == -CUDART_INF_F) ? 0.f : m_run;
+      // pass 2: P = 2^(s - m), packed to 16 bits, written over the S columns already consumed.
+      // Without mask / bias: one FMA and one ex2.approx per element (plus a select on limited tiles).
+      float l0 = 0.f, l1 = 0.f;
+      const float neg_m = -m_use;
+      auto pack2 = [&](float p0, float p1) -> uint32_t {
+        if (p.is_bf16) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          return *reinterpret_cast<const uint32_t*>(&h);
+        }
+        const __half2 h = __floats2half2_rn(p0, p1);
+        return *reinterpret_cast<const uint32_t*>(&h);
+      };
+      if (!elementwise_mask) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < FA_BN; c0 += 64) {
+          uint32_t r[64];
+          tmem_ld_32x32b_x64(ts + c0, r);
+          tmem_ld_wait();
+          uint32_t pk[32];
+          if (full) {
+#pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_m));
+              l0 += p0;
+              l1 += p1;
+              pk[e >> 1] = pack2(p0, p1);
+            }
+          } else {
+            const int cc = cl - c0;
+#pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+              float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
+              float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_m));
+              p0 = (e <= cc) ? p0 : 0.f;
+              p1 = (e + 1 <= cc) ? p1 : 0.f;
+              l0 += p0;
+              l1 += p1;
+              pk[e >> 1] = pack2(p0, p1);
+            }
+          }
+          tmem_st_32x32b_x32(ts + (c0 >> 1), pk);
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < FA_BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(ts + c0, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = fast_exp2(score(r[e], c0 + e) + neg_m);
+            const float p1 = fast_exp2(score(r[e + 1], c0 + e + 1) + neg_m);
+            l0 += p0;
+            l1 += p1;
+            pk[e >> 1] = pack2(p0, p1);
+          }
+          tmem_st_32x32b_x16(ts + (c0 >> 1), pk);
+        }
+      }
+      l_run += l0 + l1;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+
+    // ---- epilogue: O / l -> global -----------------------------------------------------------
+    if (tile_on[t]) {
+      bool have = false;
+      if (ok && nt > 0) {
+        have = mbar_wait(&o_ready[t], static_cast<uint32_t>((nt - 1) & 1), abort_word);
+        tc_fence_after();
+      }
+      const float inv = (have && l_run > 0.f) ? 1.0f / l_run : 0.f;
+      const bool row_ok = row < p.q_len;
+      char* orow = static_cast<char*>(p.O) +
+                   (static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(q_head[t]) * p.o_sh +
+                    static_cast<int64_t>(row) * p.o_sr) * 2;
+      const bool vec = ((reinterpret_cast<uint64_t>(orow) & 15u) == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        if (have) {
+          tmem_ld_32x32b_x32(to + c0, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
+        if (row_ok) {
+          uint32_t w[16];
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float a0 = __uint_as_float(r[e]) * inv, a1 = __uint_as_float(r[e + 1]) * inv;
+            const uint16_t lo = p.is_bf16 ? f32_to_bf16_bits_ref(a0) : f32_to_f16_bits_ref(a0);
+            const uint16_t hi = p.is_bf16 ? f32_to_bf16_bits_ref(a1) : f32_to_f16_bits_ref(a1);
+            w[e >> 1] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+          }
+          if (vec) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) dst[v4] = make_uint4(w[4 * v4], w[4 * v4 + 1], w[4 * v4 + 2], w[4 * v4 + 3]);
+          } else {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(orow + c0 * 2);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) dst[e] = w[e];
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word) atomicExch(p.status, YTC_TIMEOUT);
+}
+
+// ------------------------------------------------------------------ catch-all: one warp per query row
+struct AttnSimtParams {
+  const void* Q;
+  const void* K;
+  const void* V;
+  void* O;
+  int64_t q_sb, q_sh, q_sr, k_sb, k_sh, k_sr, v_sb, v_sh, v_sr, o_sb, o_sh, o_sr;
+  const uint8_t* mask;
+  int64_t mask_rs;
+  const float* bias;
+  int64_t bias_rs, bias_cs;
+  int batch, kv_heads, groups, q_len, kv_len, d, dv;
+  int causal, causal_off;
+  float scale;
+  int dt;
+};
+
+constexpr int SIMT_MAX_D = 256;
+
+__global__ void __launch_bounds__(128) attn_simt_kernel(const AttnSimtParams p) {
+  __shared__ float q_s[4][SIMT_MAX_D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.kv_heads * p.groups;
+  const int64_t total_rows = static_cast<int64_t>(p.batch) * heads * p.q_len;
+  for (int64_t gr = static_cast<int64_t>(blockIdx.x) * 4 + warp; gr < total_rows;
+       gr += static_cast<int64_t>(gridDim.x) * 4) {
+    const int row = static_cast<int>(gr % p.q_len);
+    const int h = static_cast<int>((gr / p.q_len) % heads);
+    const int b = static_cast<int>(gr / (static_cast<int64_t>(p.q_len) * heads));
+    const int kvh = h / p.groups;
+    const int64_t qo = b * p.q_sb + h * p.q_sh + row * p.q_sr;
+    const int64_t ko = b * p.k_sb + kvh * p.k_sh;
+    const int64_t vo = b * p.v_sb + kvh * p.v_sh;
+    __syncwarp();
+    for (int i = lane; i < p.d; i += 32) q_s[warp][i] = load_as_f32(p.Q, qo + i, p.dt);
+    __syncwarp();
+    float acc[SIMT_MAX_D / 32];
+#pragma unroll
+    for (int i = 0; i < SIMT_MAX_D / 32; ++i) acc[i] = 0.f;
+    float m_run = -CUDART_INF_F, l_run = 0.f;
+    int last = p.kv_len - 1;
+    if (p.causal && row + p.causal_off < last) last = row + p.causal_off;
+    for (int k0 = 0; k0 <= last; k0 += 32) {
+      const int key = k0 + lane;
+      bool vis = key <= last;
+      if (vis && p.mask) vis = p.mask[static_cast<int64_t>(row) * p.mask_rs + key] != 0;
+      float s = -CUDART_INF_F;
+      if (vis) {
+        float dot = 0.f;
+        const int64_t kb = ko + static_cast<int64_t>(key) * p.k_sr;
+        for (int i = 0; i < p.d; ++i) dot = fmaf(q_s[warp][i], load_as_f32(p.K, kb + i, p.dt), dot);
+        s = dot * p.scale;
+        if (p.bias) s += p.bias[static_cast<int64_t>(row) * p.bias_rs + key * p.bias_cs];
+      }
+      float mx = s;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_new = fmaxf(m_run, mx);
+      if (m_new == -CUDART_INF_F) continue;  // nothing visible in this chunk yet
+      const float alpha = (m_run == -CUDART_INF_F) ? 0.f : expf(m_run - m_new);
+      const float pr = vis ? expf(s - m_new) : 0.f;
+      float ps = pr;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      l_run = l_run * alpha + ps;
+      m_run = m_new;
+#pragma unroll
+      for (int i = 0; i < SIMT_MAX_D / 32; ++i) acc[i] *= alpha;
+      const int nk = (last - k0 + 1 < 32) ? last - k0 + 1 : 32;
+      for (int kk = 0; kk < nk; ++kk) {
+        const float pk = __shfl_sync(0xffffffffu, pr, kk);
+        if (pk == 0.f) continue;
+        const int64_t vb = vo + static_cast<int64_t>(k0 + kk) * p.v_sr;
+#pragma unroll
+        for (int i = 0; i < SIMT_MAX_D / 32; ++i) {
+          const int c = i * 32 + lane;
+          if (c < p.dv) acc[i] = fmaf(pk, load_as_f32(p.V, vb + c, p.dt), acc[i]);
+        }
+      }
+    }
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    const int64_t oo = b * p.o_sb + h * p.o_sh + row * p.o_sr;
+#pragma unroll
+    for (int i = 0; i < SIMT_MAX_D / 32; ++i) {
+      const int c = i * 32 + lane;
+      if (c < p.dv) store_from_f32(p.O, oo + c, acc[i] * inv, p.dt);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+static int g_attn_path = 0;  // 0 automatic, 1 always the one-warp-per-row kernel, 2 tensor-core kernel or fail
+
+static int make_qkv_map(CUtensorMap* map, const void* base, int d, int64_t len, int64_t heads, int64_t batch,
+                        int64_t s_row, int64_t s_head, int64_t s_batch) {
+  // dims {d, len, heads, batch}; a dim of extent 1 may carry any stride: give it a harmless one
+  uint64_t dims[4] = {static_cast<uint64_t>(d), static_cast<uint64_t>(len), static_cast<uint64_t>(heads),
+                      static_cast<uint64_t>(batch)};
+  uint64_t strides[3] = {static_cast<uint64_t>(s_row) * 2, static_cast<uint64_t>(s_head) * 2,
+                         static_cast<uint64_t>(s_batch) * 2};
+  if (len == 1) strides[0] = static_cast<uint64_t>(d) * 2;
+  if (heads == 1) strides[1] = strides[0] * dims[1];
+  if (batch == 1) strides[2] = strides[1] * dims[2];
+  uint32_t box[4] = {64, FA_BM, 1, 1};
+  return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, base, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+static bool tc_strides_ok(const void* ptr, int64_t s_row, int64_t s_head, int64_t s_batch, int64_t len, int64_t heads,
+                          int64_t batch) {
+  if (reinterpret_cast<uint64_t>(ptr) & 15u) return false;
+  if (len > 1 && (s_row <= 0 || (s_row * 2) % 16)) return false;
+  if (heads > 1 && (s_head <= 0 || (s_head * 2) % 16)) return false;
+  if (batch > 1 && (s_batch <= 0 || (s_batch * 2) % 16)) return false;
+  return true;
+}
+
+}  // namespace ytk
+
+using namespace ytk;
+
+extern "C" {
+
+int ytcuda_attn_set_path(int path) {
+  YTC_REQUIRE(path >= 0 && path <= 2, "ytcuda_attn_set_path: path must be 0, 1 or 2");
+  g_attn_path = path;
+  return YTC_OK;
+}
+
+int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V, void* O, int batch, int kv_heads,
+                          int groups, int q_len, int kv_len, int head_dim, int value_dim, float scale,
+                          const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                          const int64_t* o_strides, int mask_kind, int causal_offset, const uint8_t* mask,
+                          int64_t mask_row_stride, const float* bias, int64_t bias_row_stride, int64_t bias_col_stride,
+                          void* stream) {
+  YTC_REQUIRE(dtype >= YTC_F32 && dtype <= YTC_F16, "ytcuda_flash_attn_fwd: bad dtype %d", dtype);
+  YTC_REQUIRE(batch >= 0 && kv_heads >= 0 && groups >= 0 && q_len >= 0 && kv_len >= 0 && head_dim >= 0 &&
+                  value_dim >= 0,
+              "ytcuda_flash_attn_fwd: negative extent");
+  YTC_REQUIRE(mask_kind >= 0 && mask_kind <= 2, "ytcuda_flash_attn_fwd: mask_kind must be 0 (none), 1 (causal), 2 (bool)");
+  YTC_REQUIRE(mask_kind != 2 || mask != nullptr, "ytcuda_flash_attn_fwd: bool mask requested but the pointer is null");
+  if (batch == 0 || kv_heads == 0 || groups == 0 || q_len == 0 || value_dim == 0) return YTC_OK;
+  YTC_REQUIRE(Q && K && V && O, "ytcuda_flash_attn_fwd: null tensor");
+  YTC_REQUIRE(q_strides && k_strides && v_strides && o_strides, "ytcuda_flash_attn_fwd: null strides");
+  if (scale == 0.f) scale = 1.0f / sqrtf(static_cast<float>(head_dim));  // reference src/function/ops.inl:378-381
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int heads = kv_heads * groups;
+  const int causal = mask_kind == 1 ? 1 : 0;
+  const uint8_t* mptr = mask_kind == 2 ? mask : nullptr;
+
+  bool tc = dtype != YTC_F32 && g_attn_path != 1 && head_dim == value_dim && (head_dim == 64 || head_dim == 128) &&
+            kv_len > 0 && tc_strides_ok(Q, q_strides[2], q_strides[1], q_strides[0], q_len, heads, batch) &&
+            tc_strides_ok(K, k_strides[2], k_strides[1], k_strides[0], kv_len, kv_heads, batch) &&
+            tc_strides_ok(V, v_strides[2], v_strides[1], v_strides[0], kv_len, kv_heads, batch) &&
+            (reinterpret_cast<uint64_t>(O) & 3u) == 0 && o_strides[2] % 2 == 0 && o_strides[1] % 2 == 0 &&
+            o_strides[0] % 2 == 0;
+  if (!tc && g_attn_path == 2) {
+    set_last_error("ytcuda_flash_attn_fwd: tensor-core path required but the operands do not qualify");
+    return YTC_UNSUPPORTED;
+  }
+  if (tc) {
+    CUtensorMap tmQ, tmK, tmV;
+    int s = make_qkv_map(&tmQ, Q, head_dim, q_len, heads, batch, q_strides[2], q_strides[1], q_strides[0]);
+    if (s != YTC_OK) return s;
+    s = make_qkv_map(&tmK, K, head_dim, kv_len, kv_heads, batch, k_strides[2], k_strides[1], k_strides[0]);
+    if (s != YTC_OK) return s;
+    s = make_qkv_map(&tmV, V, value_dim, kv_len, kv_heads, batch, v_strides[2], v_strides[1], v_strides[0]);
+    if (s != YTC_OK) return s;
+    FlashParams p;
+    p.O = O;
+    p.o_sb = o_strides[0]; p.o_sh = o_strides[1]; p.o_sr = o_strides[2];
+    p.mask = mptr; p.mask_rs = mask_row_stride;
+    p.bias = bias; p.bias_rs = bias_row_stride; p.bias_cs = bias_col_stride;
+    p.batch = batch; p.kv_heads = kv_heads; p.groups = groups; p.q_len = q_len; p.kv_len = kv_len;
+    p.causal = causal; p.causal_off = causal_offset;
+    p.scale_log2 = scale * FA_LOG2E;
+    p.is_bf16 = dtype == YTC_BF16;
+    p.pair_heads = (groups % 2 == 0) ? 1 : 0;
+    const uint32_t fmt = dtype == YTC_BF16 ? 1u : 0u;
+    p.idesc_s = umma_idesc(fmt, 0, 0, FA_BM, FA_BN);
+    p.idesc_pv = umma_idesc(fmt, 0, 1, FA_BM, static_cast<uint32_t>(value_dim));
+    p.status = device_status_word();
+    if (!p.status) {
+      set_last_error("ytcuda_flash_attn_fwd: no device status word");
+      return YTC_CUDA_ERROR;
+    }
+    dim3 grid;
+    if (p.pair_heads) {
+      p.row_blocks = (q_len + FA_BM - 1) / FA_BM;
+      grid = dim3(p.row_blocks, heads / 2, batch);
+    } else {
+      p.row_blocks = (q_len + 2 * FA_BM - 1) / (2 * FA_BM);
+      grid = dim3(p.row_blocks, heads, batch);
+    }
+    if (grid.y > 65535 || grid.z > 65535) {
+      set_last_error("ytcuda_flash_attn_fwd: more than 65535 heads or batch items");
+      return YTC_UNSUPPORTED;
+    }
+    if (head_dim == 128) {
+      static bool attr = false;
+      if (!attr) {
+        YTC_CUDA(cudaFuncSetAttribute(flash_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      FaSmem<128>::DYN_BYTES));
+        attr = true;
+      }
+      flash_tc_kernel<128><<<grid, FA_THREADS, FaSmem<128>::DYN_BYTES, st>>>(tmQ, tmK, tmV, p);
+    } else {
+      static bool attr = false;
+      if (!attr) {
+        YTC_CUDA(cudaFuncSetAttribute(flash_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      FaSmem<64>::DYN_BYTES));
+        attr = true;
+      }
+      flash_tc_kernel<64><<<grid, FA_THREADS, FaSmem<64>::DYN_BYTES, st>>>(tmQ, tmK, tmV, p);
+    }
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
+  }
+
+  if (head_dim > SIMT_MAX_D || value_dim > SIMT_MAX_D) {
+    set_last_error("ytcuda_flash_attn_fwd: head_dim / value_dim above %d are not supported", SIMT_MAX_D);
+    return YTC_UNSUPPORTED;
+  }
+  AttnSimtParams p;
+  p.Q = Q; p.K = K; p.V = V; p.O = O;
+  p.q_sb = q_strides[0]; p.q_sh = q_strides[1]; p.q_sr = q_strides[2];
+  p.k_sb = k_strides[0]; p.k_sh = k_strides[1]; p.k_sr = k_strides[2];
+  p.v_sb = v_strides[0]; p.v_sh = v_strides[1]; p.v_sr = v_strides[2];
+  p.o_sb = o_strides[0]; p.o_sh = o_strides[1]; p.o_sr = o_strides[2];
+  p.mask = mptr; p.mask_rs = mask_row_stride;
+  p.bias = bias; p.bias_rs = bias_row_stride; p.bias_cs = bias_col_stride;
+  p.batch = batch; p.kv_heads = kv_heads; p.groups = groups; p.q_len = q_len; p.kv_len = kv_len;
+  p.d = head_dim; p.dv = value_dim;
+  p.causal = causal; p.causal_off = causal_offset;
+  p.scale = scale; p.dt = dtype;
+  const int64_t rows = static_cast<int64_t>(batch) * heads * q_len;
+  const int64_t blocks = (rows + 3) / 4;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  attn_simt_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 128, 0, st>>>(p);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+}  // extern "C"
