@@ -172,6 +172,53 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
  * YTC_UNSUPPORTED. The counterpart of the per-call sdpaBackend argument (include/function/ops.hpp:21-24). */
 int ytcuda_attn_set_path(int path);
 
+/* ---------------------------------------------------------------- decoder (Qwen3 block structure)
+ * The reference's example model (example/qwen3/include/qwen3.hpp:46-182, src/qwen3.cpp) on the device. Activations,
+ * residual stream, KV cache and logits are fp32 as in the reference; weights stay in bfloat16 storage. */
+
+/* cos / sin tables [max_len, dim] on the HOST, as RoPECache::precompute fills them (qwen3.cpp:161-175). */
+int ytcuda_rope_tables(int dim, int max_len, float theta, float* cos_host, float* sin_host);
+
+/* out[t, :] = float(table[ids[t], :]), table bf16 [vocab, hidden] (embedding gather, qwen3.cpp:378-385). */
+int ytcuda_embedding(const void* table_bf16, const int32_t* ids, float* out, int64_t n, int hidden, int vocab,
+                     void* stream);
+
+/* y[m, n] (+)= x[m, k] . W[n, k]^T with fp32 x, y and bf16 W [n, k] row-major: yt::function::linear
+ * (src/function/ops.inl:84-91) with the weight left in its storage type. Up to 32 rows: one pass over W with FFMA
+ * (decode). More rows: x is split into two bf16 planes (hi + lo) and multiplied on tcgen05; `hi_lo_scratch` must then
+ * hold 4*m*k bytes of device memory. */
+int ytcuda_linear_w16(const float* x, int64_t x_row_stride, const void* w_bf16, float* y, int64_t y_row_stride,
+                      int64_t m, int n, int k, int accumulate, void* hi_lo_scratch, void* stream);
+
+/* Fused per-head RMSNorm (q, k) + rotate-half RoPE + KV-cache append on the fused projection output
+ * qkv [batch, len, (heads + 2 kv_heads) * 128] -> q_out [batch, heads, len, 128], k_cache / v_cache
+ * [batch, kv_heads, max_len, 128] at slots slot0 .. slot0 + len - 1, RoPE positions pos0 .. (qwen3.cpp:237-247,
+ * 70-88, 522-559). */
+int ytcuda_qwen3_qkv_post(const float* qkv, float* q_out, float* k_cache, float* v_cache, const float* q_norm,
+                          const float* k_norm, const float* cos_table, const float* sin_table, int batch, int len,
+                          int heads, int kv_heads, int head_dim, int max_len, int pos0, int slot0, float eps,
+                          void* stream);
+
+/* Model handle: qwen3::Qwen3ForCausalLM (qwen3.hpp:146-168) with its KV caches, for `batch` sequences, as rank
+ * tp_rank of tp_world tensor-parallel ranks (heads and FFN columns split; vocabulary rows split for the logits).
+ * Returns NULL on an unsupported configuration (see ytcuda_last_error_string). */
+void* ytcuda_qwen3_create(int hidden, int layers, int vocab, int inter, int heads, int kv_heads, int head_dim, float eps,
+                          float theta, int max_pos, int batch, int tp_rank, int tp_world);
+void ytcuda_qwen3_destroy(void* handle);
+/* Registers a device weight (borrowed, not copied). "embed" [vocab, hidden], "lm_head" [rank's vocab rows, hidden],
+ * per layer "qkv", "o", "gate_up", "down": bf16 [out, in] already sliced for the rank; "norm", "q_norm", "k_norm",
+ * "norm1", "norm2": fp32 (members of Qwen3Model / Qwen3DecoderLayer, qwen3.hpp:62-137). */
+int ytcuda_qwen3_set_weight(void* handle, const char* name, int layer, const void* dptr);
+/* Sum all-reduce over the tensor-parallel group, called between kernels after the attention output projection and
+ * after the down projection (the reference has no counterpart: it is single-process). */
+int ytcuda_qwen3_set_allreduce(void* handle, int (*fn)(void* buf, int64_t count, void* user), void* user);
+/* Qwen3ForCausalLM::reset_kv_cache / get_kv_cache_len (qwen3.cpp:425-435). */
+int ytcuda_qwen3_reset(void* handle);
+int ytcuda_qwen3_cache_len(void* handle);
+/* ids [batch, len] int32 (device) -> logits of the last position [batch, rank's vocab rows] fp32 (device); appends
+ * len tokens to the KV caches (Qwen3ForCausalLM::forward, qwen3.cpp:449-457). */
+int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

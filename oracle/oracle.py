@@ -135,6 +135,9 @@ class _Backend:
         assert rc == 0, rc
         return out
 
+    def qwen3(self, cfg: dict, batch: int = 1) -> "_Qwen3Handle":
+        return _Qwen3Handle(self, cfg, batch)
+
     def swish(self, x):
         x = _f32(x)
         y = np.empty_like(x)
@@ -165,6 +168,49 @@ class _Backend:
         rc = self._sdpa(q, k, v, out, b, kvh, g, ql, kl, d, dv, scale, kind, m, bs, **kw)
         assert rc == 0, rc
         return out
+
+
+class _Qwen3Handle:
+    """The reference's Qwen3ForCausalLM (ref back-end) or its restatement (port back-end) on the CPU."""
+
+    def __init__(self, backend: "_Backend", cfg: dict, batch: int):
+        self.be, self.cfg, self.batch = backend, cfg, batch
+        create = backend._fn("qwen3_create")
+        create.restype = C.c_void_p
+        self.h = C.c_void_p(create(cfg["hidden"], cfg["layers"], cfg["vocab"], cfg["inter"], cfg["heads"],
+                                   cfg["kv_heads"], cfg["head_dim"], C.c_float(cfg["eps"]), C.c_float(cfg["theta"]),
+                                   cfg["max_pos"], batch))
+        assert self.h.value, "qwen3_create failed"
+
+    def set_weight(self, name: str, layer: int, data_f32: np.ndarray):
+        a = _f32(data_f32)
+        rows, cols = (a.shape[0], a.shape[1]) if a.ndim == 2 else (a.shape[0], 1)
+        rc = self.be._fn("qwen3_set_weight")(self.h, name.encode(), layer, _opt(a), rows, cols)
+        assert rc == 0, (name, rc)
+
+    def reset(self):
+        self.be._fn("qwen3_reset")(self.h)
+
+    def forward(self, ids: np.ndarray) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, np.int32)
+        assert ids.shape[0] == self.batch
+        logits = np.empty((self.batch, self.cfg["vocab"]), np.float32)
+        rc = self.be._fn("qwen3_forward")(self.h, _opt(ids), ids.shape[1], _opt(logits))
+        assert rc == 0, rc
+        return logits
+
+    def close(self):
+        if self.h:
+            fn = self.be._fn("qwen3_destroy")
+            fn.restype = None
+            fn(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class PortOracle(_Backend):

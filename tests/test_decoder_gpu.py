@@ -1,0 +1,132 @@
+"""GPU parity tests of the decoder (ytcuda_qwen3_*) against the reference example model.
+
+Contract: fp32 logits within 1e-4 of the reference's (normwise; fp32 sums in another order over 28 layers), and
+argmax-identical greedy tokens for the first 32 decode steps on the Qwen3-0.6B shape with random bf16 weights."""
+import hashlib
+
+import numpy as np
+import pytest
+
+from _util import normwise
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(hidden_size=64, num_hidden_layers=2, vocab_size=512, intermediate_size=96, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=128, max_position_embeddings=64)
+
+
+@pytest.fixture(scope="module")
+def qwen3_golden():
+    from pathlib import Path
+    return np.load(Path(__file__).resolve().parent / "golden" / "golden_qwen3.npz")
+
+
+@pytest.fixture(scope="module")
+def Q():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from ytensor_b200 import qwen3
+    return qwen3
+
+
+def dev_ids(a):
+    return torch.from_numpy(np.ascontiguousarray(a, np.int32)).cuda()
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_small_model_logits_match_reference(Q, qwen3_golden, B):
+    cfg = Q.Qwen3Config(**SMALL)
+    w = Q.random_weights(cfg, seed=4, std=0.05)
+    assert hashlib.sha256(w["embed"].tobytes()).hexdigest() == str(qwen3_golden["small_embed_sha256"])
+    m = Q.Qwen3ForCausalLM(cfg, batch=B)
+    m.load_weights(w)
+    want = qwen3_golden[f"small_logits_b{B}"]
+    logits = m.forward(dev_ids(qwen3_golden[f"small_ids_b{B}"]))
+    for step in range(6):
+        got = logits.cpu().numpy()
+        assert normwise(got, want[step]) < 1e-4
+        assert np.array_equal(got.argmax(1), want[step].argmax(1))
+        if step < 5:
+            logits = m.forward(dev_ids(want[step].argmax(1).reshape(B, 1)))
+    assert m.get_kv_cache_len() == 9 + 5
+    m.reset_kv_cache()
+    assert m.get_kv_cache_len() == 0
+    m.close()
+
+
+def test_long_prefill_uses_tensor_cores_and_matches_oracle(Q, port):
+    """More than 32 rows: activations are split into two bf16 planes and multiplied on tcgen05."""
+    cfg = Q.Qwen3Config(**SMALL)
+    w = Q.random_weights(cfg, seed=5, std=0.05)
+    ids = np.random.default_rng(1).integers(0, cfg.vocab_size, (2, 40)).astype(np.int32)
+    om = port.qwen3(cfg.oracle_dict(), 2)
+    for key, arr in w.items():
+        name, layer = (key, 0) if isinstance(key, str) else key
+        om.set_weight(name, layer, Q.bf16_bits_to_f32(arr) if arr.dtype == np.uint16 else arr)
+    want = om.forward(ids)
+    m = Q.Qwen3ForCausalLM(cfg, batch=2)
+    m.load_weights(w)
+    got = m.forward(dev_ids(ids)).cpu().numpy()
+    assert normwise(got, want) < 1e-4
+    nxt = want.argmax(1).astype(np.int32).reshape(2, 1)
+    assert normwise(m.forward(dev_ids(nxt)).cpu().numpy(), om.forward(nxt)) < 1e-4
+    m.close()
+    om.close()
+
+
+def test_cache_overflow_is_reported(Q):
+    from ytensor_b200 import _lib
+    cfg = Q.Qwen3Config(**SMALL)
+    m = Q.Qwen3ForCausalLM(cfg, batch=1)
+    m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
+    m.forward(dev_ids(np.zeros((1, 60), np.int32)))
+    with pytest.raises(_lib.YtCudaInvalidArgument):  # the device has no ring-buffer wrap: it refuses instead
+        m.forward(dev_ids(np.zeros((1, 5), np.int32)))
+    m.close()
+
+
+def test_linear_w16_kernels(Q, port):
+    from ytensor_b200 import _lib
+    L = _lib.lib()
+    rng = np.random.default_rng(2)
+    for M, N, K in [(1, 1000, 1024), (5, 77, 512), (32, 300, 3072), (100, 256, 1024), (9, 8, 8)]:
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        wb = Q.f32_to_bf16_bits((rng.standard_normal((N, K)) * 0.05).astype(np.float32))
+        want = port.matmul(x, np.ascontiguousarray(Q.bf16_bits_to_f32(wb).T))
+        tx = torch.from_numpy(x).cuda()
+        tw = torch.from_numpy(wb.view(np.int16)).cuda()
+        y = torch.empty(M, N, device="cuda")
+        scratch = torch.empty(4 * M * K, dtype=torch.uint8, device="cuda")
+        _lib.check(L.ytcuda_linear_w16(tx.data_ptr(), K, tw.data_ptr(), y.data_ptr(), N, M, N, K, 0,
+                                       scratch.data_ptr(), None))
+        assert normwise(y.cpu().numpy(), want) < 2e-5
+        _lib.check(L.ytcuda_linear_w16(tx.data_ptr(), K, tw.data_ptr(), y.data_ptr(), N, M, N, K, 1,
+                                       scratch.data_ptr(), None))
+        assert normwise(y.cpu().numpy(), 2 * want) < 2e-5
+
+
+def test_full_model_greedy_tokens_match_reference(Q, qwen3_golden):
+    """BASELINE config 5, batch 1: 512-token prompt, 32 greedy steps, tokens identical to the reference's."""
+    cfg = Q.Qwen3Config(max_position_embeddings=768)
+    w = Q.random_weights(cfg, seed=4)
+    assert hashlib.sha256(w["embed"].tobytes()).hexdigest() == str(qwen3_golden["full_embed_sha256"])
+    m = Q.Qwen3ForCausalLM(cfg, batch=1)
+    m.load_weights(w)
+    logits = m.forward(dev_ids(qwen3_golden["full_prompt"]))
+    want_tok, top_i, top_v = qwen3_golden["full_tokens"], qwen3_golden["full_top8_indices"], qwen3_golden["full_top8_values"]
+    for s in range(32):
+        tok, _ = m.argmax(logits)
+        got = logits[0].cpu().numpy()
+        assert int(tok[0]) == int(want_tok[s]), f"step {s}: margin in the reference was {qwen3_golden['full_margins'][s]}"
+        assert np.abs(got[top_i[s]] - top_v[s]).max() < 1e-3
+        if s < 31:
+            logits = m.forward(tok.reshape(1, 1).contiguous())
+    # batch 2 with the same prompt twice gives the same tokens in both rows
+    m.close()
+    m2 = Q.Qwen3ForCausalLM(cfg, batch=2)
+    m2.load_weights(w)
+    p2 = np.repeat(qwen3_golden["full_prompt"], 2, axis=0)
+    toks = m2.generate_greedy(dev_ids(p2), 8).cpu().numpy()
+    assert np.array_equal(toks[0], want_tok[:8]) and np.array_equal(toks[1], want_tok[:8])
+    m2.close()

@@ -1,0 +1,599 @@
+// Decoder-only language model forward (Qwen3 block structure) for the YTensor device backend.
+//
+// The host loop below is the device counterpart of qwen3::Qwen3ForCausalLM::forward (reference
+// example/qwen3/src/qwen3.cpp:271-283,365-457): embedding gather, per layer
+//   h1 = rmsNorm(x); qkv = linear(h1, Wqkv); per-head rmsNorm(q), rmsNorm(k); rope; KV-cache append;
+//   attention over the cache; x2 = linear(attn, Wo) + x; h2 = rmsNorm(x2); x2 += linear(swish(gate)*up, Wdown)
+// then the final rmsNorm of the last position and logits = h . W_vocab^T.
+// As in the reference, the residual stream, the activations, the KV cache and the logits are fp32; the weights
+// are bfloat16 (the reference widens bf16 checkpoints to fp32 at load, qwen3.cpp:16-44 - the products are the same
+// numbers). Tensor parallelism splits heads and FFN columns over ranks; the partial sums after the attention
+// output projection and after the down projection are reduced by a callback the caller provides (NCCL all-reduce).
+//
+// Kernels here: embedding gather; weight-streaming linear for few rows (decode); fp32 -> (hi, lo) bf16 split that
+// lets the tcgen05 GEMM multiply fp32 activations by bf16 weights (prefill); fused per-head RMSNorm + RoPE + KV
+// append; argmax partials for a vocabulary split over ranks.
+#include <math_constants.h>
+
+#include <cmath>
+#include <string>
+#include <vector>
+
+#include "ytc_common.cuh"
+
+namespace ytk {
+
+// ------------------------------------------------------------------ embedding gather
+// out[t, :] = float(table[ids[t], :])   (reference qwen3.cpp:378-385)
+__global__ void __launch_bounds__(256) embedding_kernel(const uint16_t* table, const int* ids, float* out, int64_t n,
+                                                        int hidden, int vocab) {
+  const int per_row = hidden / 4;
+  const int64_t total = n * per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / per_row;
+    const int c = static_cast<int>(i - t * per_row) * 4;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const uint2 w = *reinterpret_cast<const uint2*>(table + static_cast<int64_t>(id) * hidden + c);
+    float4 o;
+    o.x = bf16_bits_to_f32(static_cast<uint16_t>(w.x & 0xFFFF));
+    o.y = bf16_bits_to_f32(static_cast<uint16_t>(w.x >> 16));
+    o.z = bf16_bits_to_f32(static_cast<uint16_t>(w.y & 0xFFFF));
+    o.w = bf16_bits_to_f32(static_cast<uint16_t>(w.y >> 16));
+    *reinterpret_cast<float4*>(out + t * hidden + c) = o;
+  }
+}
+
+// ------------------------------------------------------------------ few-row linear (decode)
+// y[m, n] (+)= sum_k x[m, k] * float(W[n, k]),  m < M <= MT. One warp owns ROWS weight rows and streams them once
+// with 128-bit loads (32 lanes x 8 bf16 = 256 consecutive k per trip, fully coalesced); x lives in shared memory
+// in K-chunks; every lane keeps M partial sums per weight row and the warp reduces them at the end in a fixed
+// order (bit-stable from run to run). Memory-bound on W for small M; FFMA-bound as M grows.
+constexpr int SK_WARPS = 4;
+constexpr int SK_ROWS = 2;
+constexpr int SK_KC = 512;
+
+template <int MT>
+__global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(const float* __restrict__ x, int64_t x_rs,
+                                                                      const uint16_t* __restrict__ W, int64_t w_rs,
+                                                                      float* __restrict__ y, int64_t y_rs, int M, int N,
+                                                                      int K, int accumulate) {
+  extern __shared__ float xs[];  // [MT][SK_KC]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * SK_WARPS + warp) * SK_ROWS;
+  float acc[SK_ROWS][MT];
+#pragma unroll
+  for (int r = 0; r < SK_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += SK_KC) {
+    const int kc = (K - k0 < SK_KC) ? K - k0 : SK_KC;
+    __syncthreads();
+    for (int i = threadIdx.x; i < MT * (SK_KC / 4); i += SK_WARPS * 32) {
+      const int m = i / (SK_KC / 4), c = (i - m * (SK_KC / 4)) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (m < M && c < kc) v = *reinterpret_cast<const float4*>(x + m * x_rs + k0 + c);
+      *reinterpret_cast<float4*>(&xs[m * SK_KC + c]) = v;
+    }
+    __syncthreads();
+    for (int kk = lane * 8; kk < kc; kk += 256) {
+      uint4 w[SK_ROWS];
+#pragma unroll
+      for (int r = 0; r < SK_ROWS; ++r) {
+        const int n = n0 + r;
+        w[r] = (n < N) ? *reinterpret_cast<const uint4*>(W + static_cast<int64_t>(n) * w_rs + k0 + kk)
+                       : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float4 xa = *reinterpret_cast<const float4*>(&xs[m * SK_KC + kk]);
+        const float4 xb = *reinterpret_cast<const float4*>(&xs[m * SK_KC + kk + 4]);
+#pragma unroll
+        for (int r = 0; r < SK_ROWS; ++r) {
+          float a = acc[r][m];
+          a = fmaf(xa.x, __uint_as_float(w[r].x << 16), a);
+          a = fmaf(xa.y, __uint_as_float(w[r].x & 0xFFFF0000u), a);
+          a = fmaf(xa.z, __uint_as_float(w[r].y << 16), a);
+          a = fmaf(xa.w, __uint_as_float(w[r].y & 0xFFFF0000u), a);
+          a = fmaf(xb.x, __uint_as_float(w[r].z << 16), a);
+          a = fmaf(xb.y, __uint_as_float(w[r].z & 0xFFFF0000u), a);
+          a = fmaf(xb.z, __uint_as_float(w[r].w << 16), a);
+          a = fmaf(xb.w, __uint_as_float(w[r].w & 0xFFFF0000u), a);
+          acc[r][m] = a;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < SK_ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float v = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      acc[r][m] = v;
+    }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < SK_ROWS; ++r) {
+      const int n = n0 + r;
+      if (n >= N) continue;
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+        if (m < M) {
+          float* dst = y + m * y_rs + n;
+          *dst = accumulate ? *dst + acc[r][m] : acc[r][m];
+        }
+    }
+  }
+}
+
+// x (fp32) = hi + lo with hi = bf16(x) (round to nearest even) and lo = bf16(x - hi): the two 16-bit operands of
+// the tensor-core products that together carry 16 mantissa bits of the activation.
+__global__ void __launch_bounds__(256) split_hi_lo_kernel(const float* x, int64_t x_rs, uint16_t* hi, uint16_t* lo,
+                                                          int64_t rows, int K) {
+  const int per_row = K / 4;
+  const int64_t total = rows * per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / per_row;
+    const int c = static_cast<int>(i - r * per_row) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(x + r * x_rs + c);
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    uint16_t h[4], l[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __nv_bfloat16 hb = __float2bfloat16_rn(f[k]);
+      const float rest = f[k] - __bfloat162float(hb);
+      const __nv_bfloat16 lb = __float2bfloat16_rn(rest);
+      h[k] = *reinterpret_cast<const uint16_t*>(&hb);
+      l[k] = *reinterpret_cast<const uint16_t*>(&lb);
+    }
+    uint2 ph, pl;
+    ph.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
+    ph.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
+    pl.x = l[0] | (static_cast<uint32_t>(l[1]) << 16);
+    pl.y = l[2] | (static_cast<uint32_t>(l[3]) << 16);
+    *reinterpret_cast<uint2*>(hi + r * K + c) = ph;
+    *reinterpret_cast<uint2*>(lo + r * K + c) = pl;
+  }
+}
+
+// ------------------------------------------------------------------ per-head RMSNorm + RoPE + KV append
+// qkv [B, L, (H + 2*KVH) * D] fp32 (the fused projection output). One warp per (b, t, head) vector, D == 128:
+//   q heads: rmsNorm over D with q_norm, rotate-half RoPE at position pos0 + t -> q_out [B, H, L, D]
+//   k heads: rmsNorm with k_norm, RoPE -> k_cache [B, KVH, max_len, D] at slot slot0 + t
+//   v heads: copy -> v_cache at the same slot
+// (reference qwen3.cpp:237-247: slice/reshape/permute, HeadRMSNorm, ops::rope, KVCache::append; rope math :522-559).
+__global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* q_out, float* k_cache, float* v_cache,
+                                                       const float* q_norm, const float* k_norm, const float* cos_t,
+                                                       const float* sin_t, int B, int L, int H, int KVH, int max_len,
+                                                       int pos0, int slot0, float eps) {
+  constexpr int D = 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_all = H + 2 * KVH;
+  const int64_t vecs = static_cast<int64_t>(B) * L * heads_all;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * 4 + warp; v < vecs; v += static_cast<int64_t>(gridDim.x) * 4) {
+    const int hh = static_cast<int>(v % heads_all);
+    const int t = static_cast<int>((v / heads_all) % L);
+    const int b = static_cast<int>(v / (static_cast<int64_t>(heads_all) * L));
+    const float* src = qkv + (static_cast<int64_t>(b) * L + t) * heads_all * D + static_cast<int64_t>(hh) * D;
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = src[lane + 32 * i];
+    if (hh >= H + KVH) {  // value head
+      float* dst = v_cache + ((static_cast<int64_t>(b) * KVH + (hh - H - KVH)) * max_len + slot0 + t) * D;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = x[i];
+      continue;
+    }
+    const bool is_q = hh < H;
+    float ss = x[0] * x[0];
+    ss = fmaf(x[1], x[1], ss);
+    ss = fmaf(x[2], x[2], ss);
+    ss = fmaf(x[3], x[3], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float denom = sqrtf(ss * (1.0f / D) + eps);
+    const float* wn = is_q ? q_norm : k_norm;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = (x[i] / denom) * wn[lane + 32 * i];
+    // rotate-half pairs (i, i + 64): elements {lane, lane+64} and {lane+32, lane+96} sit in this lane
+    const float* cr = cos_t + static_cast<int64_t>(pos0 + t) * D;
+    const float* sr = sin_t + static_cast<int64_t>(pos0 + t) * D;
+    float y[4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float c = cr[lane + 32 * i], s = sr[lane + 32 * i];
+      const float re = x[i], im = x[i + 2];
+      y[i] = re * c - im * s;
+      y[i + 2] = im * c + re * s;
+    }
+    float* dst = is_q ? q_out + ((static_cast<int64_t>(b) * H + hh) * L + t) * D
+                      : k_cache + ((static_cast<int64_t>(b) * KVH + (hh - H)) * max_len + slot0 + t) * D;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = y[i];
+  }
+}
+
+// ------------------------------------------------------------------ model
+struct LayerW {
+  const uint16_t *qkv = nullptr, *o = nullptr, *gate_up = nullptr, *down = nullptr;  // bf16 [out, in]
+  const float *q_norm = nullptr, *k_norm = nullptr, *norm1 = nullptr, *norm2 = nullptr;
+};
+
+typedef int (*AllReduceFn)(void* buf, int64_t count, void* user);
+
+struct Qwen3Model {
+  // global shape
+  int hidden, layers, vocab, inter, heads, kv_heads, head_dim, max_pos;
+  float eps, theta;
+  // this rank's share (tensor parallel)
+  int tp_rank = 0, tp_world = 1;
+  int l_heads, l_kv_heads, l_inter, l_vocab;
+  int batch = 0;
+  std::vector<LayerW> lw;
+  const uint16_t* embed = nullptr;    // [vocab, hidden] (full, replicated: the gather needs every row)
+  const uint16_t* lm_head = nullptr;  // [l_vocab, hidden] (this rank's rows)
+  const float* final_norm = nullptr;
+  // device state owned by the model
+  float *cos_t = nullptr, *sin_t = nullptr;
+  float *k_cache = nullptr, *v_cache = nullptr;  // [layers][batch, l_kv_heads, max_pos, head_dim]
+  int cur_len = 0;
+  // activations
+  float *x = nullptr, *h = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr, *act = nullptr,
+        *proj = nullptr, *last = nullptr;
+  uint16_t *hi = nullptr, *lo = nullptr;
+  int64_t act_rows = 0;
+  AllReduceFn allreduce = nullptr;
+  void* allreduce_user = nullptr;
+  std::vector<void*> owned;
+};
+
+static int dev_alloc(Qwen3Model* m, void** p, size_t bytes) {
+  YTC_CUDA(cudaMalloc(p, bytes));
+  m->owned.push_back(*p);
+  return YTC_OK;
+}
+
+// y[M, N] (+)= x[M, K] . W[N, K]^T with fp32 x / y and bf16 W.
+static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_t* W, float* y, int64_t y_rs, int64_t M,
+                      int N, int K, bool accumulate, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return YTC_OK;
+  if (M <= 32) {
+    const int blocks = (N + SK_WARPS * SK_ROWS - 1) / (SK_WARPS * SK_ROWS);
+    const int Mi = static_cast<int>(M);
+#define SK_LAUNCH(MT)                                                                                          \
+  skinny_linear_kernel<MT><<<blocks, SK_WARPS * 32, MT * SK_KC * sizeof(float), st>>>(x, x_rs, W, K, y, y_rs, Mi, N, K, \
+                                                                                      accumulate ? 1 : 0)
+    if (Mi == 1) SK_LAUNCH(1);
+    else if (Mi <= 2) SK_LAUNCH(2);
+    else if (Mi <= 4) SK_LAUNCH(4);
+    else if (Mi <= 8) SK_LAUNCH(8);
+    else if (Mi <= 16) {
+      static bool attr = false;
+      if (!attr) {
+        YTC_CUDA(cudaFuncSetAttribute(skinny_linear_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      16 * SK_KC * 4));
+        attr = true;
+      }
+      SK_LAUNCH(16);
+    } else {
+      static bool attr = false;
+      if (!attr) {
+        YTC_CUDA(cudaFuncSetAttribute(skinny_linear_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      32 * SK_KC * 4));
+        attr = true;
+      }
+      SK_LAUNCH(32);
+    }
+#undef SK_LAUNCH
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
+  }
+  // many rows: split the activation into two bf16 planes and run the tensor-core GEMM on each
+  const int64_t total4 = M * (K / 4);
+  const int64_t blocks = (total4 + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  split_hi_lo_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, x_rs, m->hi, m->lo, M, K);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  int s = ytcuda_gemm(YTC_BF16, YTC_F32, m->hi, W, y, static_cast<int>(M), N, K, 1.f, accumulate ? 1.f : 0.f, K, 1, 1,
+                      K, y_rs, 1, 1, 0, 0, 0, st);
+  if (s != YTC_OK) return s;
+  return ytcuda_gemm(YTC_BF16, YTC_F32, m->lo, W, y, static_cast<int>(M), N, K, 1.f, 1.f, K, 1, 1, K, y_rs, 1, 1, 0, 0,
+                     0, st);
+}
+
+static int rmsnorm_rows(const float* x, const float* w, float* y, int64_t rows, int hidden, float eps, cudaStream_t st) {
+  const int64_t shape[2] = {rows, hidden}, strides[2] = {hidden, 1};
+  const int axes[1] = {-1};
+  return ytcuda_rmsnorm(YTC_F32, YTC_F32, YTC_F32, x, w, y, shape, strides, strides, 2, axes, 1, eps, st);
+}
+static int add_inplace(float* a, const float* b, int64_t n, cudaStream_t st) {
+  const int64_t shape[1] = {n}, strides[1] = {1};
+  return ytcuda_binary(0, YTC_F32, YTC_F32, YTC_F32, a, b, a, 1, shape, strides, strides, strides, st);
+}
+
+}  // namespace ytk
+
+using namespace ytk;
+
+extern "C" {
+
+// cos / sin tables as the reference precomputes them on the host (example/qwen3/src/qwen3.cpp:161-175):
+// freq = 1 / pow(theta, 2 i / dim), angle = t * freq, both halves of a row hold the same values.
+int ytcuda_rope_tables(int dim, int max_len, float theta, float* cos_host, float* sin_host) {
+  YTC_REQUIRE(dim > 0 && dim % 2 == 0 && max_len >= 0 && cos_host && sin_host, "ytcuda_rope_tables: bad arguments");
+  const int half = dim / 2;
+  for (int t = 0; t < max_len; ++t)
+    for (int i = 0; i < half; ++i) {
+      const float freq = 1.0f / std::pow(theta, 2.0f * i / dim);
+      const float angle = t * freq;
+      cos_host[static_cast<int64_t>(t) * dim + i] = cos_host[static_cast<int64_t>(t) * dim + i + half] = std::cos(angle);
+      sin_host[static_cast<int64_t>(t) * dim + i] = sin_host[static_cast<int64_t>(t) * dim + i + half] = std::sin(angle);
+    }
+  return YTC_OK;
+}
+
+int ytcuda_embedding(const void* table_bf16, const int32_t* ids, float* out, int64_t n, int hidden, int vocab,
+                     void* stream) {
+  YTC_REQUIRE(n >= 0 && hidden >= 0 && vocab > 0, "ytcuda_embedding: bad extent");
+  if (n == 0 || hidden == 0) return YTC_OK;
+  YTC_REQUIRE(table_bf16 && ids && out, "ytcuda_embedding: null tensor");
+  YTC_REQUIRE(hidden % 4 == 0, "ytcuda_embedding: hidden must be a multiple of 4");
+  const int64_t blocks = (n * (hidden / 4) + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  embedding_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(table_bf16), ids, out, n, hidden, vocab);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+// y[M, N] (+)= x[M, K] . W[N, K]^T, x / y fp32 (row strides in elements), W bf16 row-major [N, K].
+// The device form of yt::function::linear on fp32 activations with weights kept in their bf16 storage
+// (reference src/function/ops.inl:84-91; weights widened at load in example/qwen3/src/qwen3.cpp:16-44).
+int ytcuda_linear_w16(const float* x, int64_t x_row_stride, const void* w_bf16, float* y, int64_t y_row_stride,
+                      int64_t m, int n, int k, int accumulate, void* hi_lo_scratch, void* stream) {
+  YTC_REQUIRE(m >= 0 && n >= 0 && k >= 0, "ytcuda_linear_w16: negative extent");
+  if (m == 0 || n == 0) return YTC_OK;
+  YTC_REQUIRE(x && w_bf16 && y, "ytcuda_linear_w16: null tensor");
+  YTC_REQUIRE(k % 8 == 0 && x_row_stride % 4 == 0 && (reinterpret_cast<uint64_t>(x) & 15) == 0 &&
+                  (reinterpret_cast<uint64_t>(w_bf16) & 15) == 0,
+              "ytcuda_linear_w16: k must be a multiple of 8 and x / W 16-byte aligned");
+  Qwen3Model tmp{};
+  if (m > 32) {
+    YTC_REQUIRE(hi_lo_scratch != nullptr, "ytcuda_linear_w16: more than 32 rows need a scratch of 4*m*k bytes");
+    tmp.hi = static_cast<uint16_t*>(hi_lo_scratch);
+    tmp.lo = tmp.hi + m * k;
+  }
+  return linear_w16(&tmp, x, x_row_stride, static_cast<const uint16_t*>(w_bf16), y, y_row_stride, m, n, k,
+                    accumulate != 0, static_cast<cudaStream_t>(stream));
+}
+
+int ytcuda_qwen3_qkv_post(const float* qkv, float* q_out, float* k_cache, float* v_cache, const float* q_norm,
+                          const float* k_norm, const float* cos_table, const float* sin_table, int batch, int len,
+                          int heads, int kv_heads, int head_dim, int max_len, int pos0, int slot0, float eps,
+                          void* stream) {
+  YTC_REQUIRE(batch >= 0 && len >= 0 && heads >= 0 && kv_heads >= 0, "ytcuda_qwen3_qkv_post: negative extent");
+  if (batch == 0 || len == 0) return YTC_OK;
+  if (head_dim != 128) {
+    set_last_error("ytcuda_qwen3_qkv_post: head_dim %d is not supported (128 only)", head_dim);
+    return YTC_UNSUPPORTED;
+  }
+  YTC_REQUIRE(qkv && q_out && k_cache && v_cache && q_norm && k_norm && cos_table && sin_table,
+              "ytcuda_qwen3_qkv_post: null tensor");
+  YTC_REQUIRE(slot0 >= 0 && slot0 + len <= max_len, "ytcuda_qwen3_qkv_post: %d new tokens do not fit the cache at slot %d of %d",
+              len, slot0, max_len);
+  const int64_t vecs = static_cast<int64_t>(batch) * len * (heads + 2 * kv_heads);
+  const int64_t blocks = (vecs + 3) / 4;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  qkv_post_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      qkv, q_out, k_cache, v_cache, q_norm, k_norm, cos_table, sin_table, batch, len, heads, kv_heads, max_len, pos0,
+      slot0, eps);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+// ---------------------------------------------------------------- model handle
+void* ytcuda_qwen3_create(int hidden, int layers, int vocab, int inter, int heads, int kv_heads, int head_dim, float eps,
+                          float theta, int max_pos, int batch, int tp_rank, int tp_world) {
+  if (hidden <= 0 || layers <= 0 || vocab <= 0 || inter <= 0 || heads <= 0 || kv_heads <= 0 || head_dim != 128 ||
+      max_pos <= 0 || batch <= 0 || tp_world <= 0 || tp_rank < 0 || tp_rank >= tp_world || heads % kv_heads ||
+      kv_heads % tp_world || inter % tp_world || hidden % 8 || inter % 8) {
+    set_last_error("ytcuda_qwen3_create: unsupported configuration (head_dim must be 128; kv_heads and the FFN width "
+                   "must divide by the tensor-parallel size)");
+    return nullptr;
+  }
+  auto* m = new Qwen3Model();
+  m->hidden = hidden; m->layers = layers; m->vocab = vocab; m->inter = inter; m->heads = heads;
+  m->kv_heads = kv_heads; m->head_dim = head_dim; m->max_pos = max_pos; m->eps = eps; m->theta = theta;
+  m->tp_rank = tp_rank; m->tp_world = tp_world; m->batch = batch;
+  m->l_heads = heads / tp_world; m->l_kv_heads = kv_heads / tp_world; m->l_inter = inter / tp_world;
+  m->l_vocab = (vocab + tp_world - 1) / tp_world;
+  if (tp_rank == tp_world - 1) m->l_vocab = vocab - m->l_vocab * (tp_world - 1);
+  m->lw.resize(layers);
+  std::vector<float> ch(static_cast<size_t>(max_pos) * head_dim), sh(ch.size());
+  ytcuda_rope_tables(head_dim, max_pos, theta, ch.data(), sh.data());
+  const size_t cache = static_cast<size_t>(layers) * batch * m->l_kv_heads * max_pos * head_dim * sizeof(float);
+  bool ok = dev_alloc(m, reinterpret_cast<void**>(&m->cos_t), ch.size() * 4) == YTC_OK &&
+            dev_alloc(m, reinterpret_cast<void**>(&m->sin_t), sh.size() * 4) == YTC_OK &&
+            dev_alloc(m, reinterpret_cast<void**>(&m->k_cache), cache) == YTC_OK &&
+            dev_alloc(m, reinterpret_cast<void**>(&m->v_cache), cache) == YTC_OK;
+  if (ok) {
+    ok = cudaMemcpy(m->cos_t, ch.data(), ch.size() * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+         cudaMemcpy(m->sin_t, sh.data(), sh.size() * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+         cudaMemset(m->k_cache, 0, cache) == cudaSuccess && cudaMemset(m->v_cache, 0, cache) == cudaSuccess;
+  }
+  if (!ok) {
+    set_last_error("ytcuda_qwen3_create: device allocation failed (KV cache needs %zu bytes twice)", cache);
+    for (void* p : m->owned) cudaFree(p);
+    delete m;
+    return nullptr;
+  }
+  return m;
+}
+
+void ytcuda_qwen3_destroy(void* handle) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  if (!m) return;
+  for (void* p : m->owned) cudaFree(p);
+  delete m;
+}
+
+// Registers a device weight (not copied; the caller keeps it alive). Names: "embed" [vocab, hidden] bf16,
+// "lm_head" [this rank's vocab rows, hidden] bf16, "norm" [hidden] f32; per layer "qkv" [(l_heads + 2 l_kv_heads)
+// * head_dim, hidden], "o" [hidden, l_heads * head_dim], "gate_up" [2 * l_inter, hidden], "down" [hidden, l_inter]
+// (bf16, already sliced for this rank) and "q_norm", "k_norm" [head_dim], "norm1", "norm2" [hidden] (f32).
+int ytcuda_qwen3_set_weight(void* handle, const char* name, int layer, const void* dptr) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m && name && dptr, "ytcuda_qwen3_set_weight: null argument");
+  YTC_REQUIRE((reinterpret_cast<uint64_t>(dptr) & 15) == 0, "ytcuda_qwen3_set_weight: weights must be 16-byte aligned");
+  const std::string n(name);
+  if (n == "embed") { m->embed = static_cast<const uint16_t*>(dptr); return YTC_OK; }
+  if (n == "lm_head") { m->lm_head = static_cast<const uint16_t*>(dptr); return YTC_OK; }
+  if (n == "norm") { m->final_norm = static_cast<const float*>(dptr); return YTC_OK; }
+  YTC_REQUIRE(layer >= 0 && layer < m->layers, "ytcuda_qwen3_set_weight: layer %d out of range", layer);
+  LayerW& L = m->lw[layer];
+  if (n == "qkv") L.qkv = static_cast<const uint16_t*>(dptr);
+  else if (n == "o") L.o = static_cast<const uint16_t*>(dptr);
+  else if (n == "gate_up") L.gate_up = static_cast<const uint16_t*>(dptr);
+  else if (n == "down") L.down = static_cast<const uint16_t*>(dptr);
+  else if (n == "q_norm") L.q_norm = static_cast<const float*>(dptr);
+  else if (n == "k_norm") L.k_norm = static_cast<const float*>(dptr);
+  else if (n == "norm1") L.norm1 = static_cast<const float*>(dptr);
+  else if (n == "norm2") L.norm2 = static_cast<const float*>(dptr);
+  else {
+    set_last_error("ytcuda_qwen3_set_weight: unknown weight name '%s'", name);
+    return YTC_INVALID_ARG;
+  }
+  return YTC_OK;
+}
+
+// Sum-reduction over the tensor-parallel group of `count` floats in place, called on the forward's stream between
+// kernels (after the attention output projection and after the down projection). NULL when tp_world == 1.
+int ytcuda_qwen3_set_allreduce(void* handle, int (*fn)(void*, int64_t, void*), void* user) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m, "ytcuda_qwen3_set_allreduce: null handle");
+  m->allreduce = fn;
+  m->allreduce_user = user;
+  return YTC_OK;
+}
+
+int ytcuda_qwen3_reset(void* handle) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m, "ytcuda_qwen3_reset: null handle");
+  m->cur_len = 0;
+  return YTC_OK;
+}
+int ytcuda_qwen3_cache_len(void* handle) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  return m ? m->cur_len : -1;
+}
+
+static int ensure_activations(Qwen3Model* m, int64_t rows) {
+  if (rows <= m->act_rows) return YTC_OK;
+  // (buffers of earlier, smaller calls stay owned until destroy)
+  const int D = m->head_dim;
+  const int qkv_w = (m->l_heads + 2 * m->l_kv_heads) * D;
+  const int kmax = m->hidden > m->l_inter ? m->hidden : m->l_inter;
+  const int kmax2 = kmax > m->l_heads * D ? kmax : m->l_heads * D;
+  int s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->x), rows * m->hidden * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->h), rows * m->hidden * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->proj), rows * m->hidden * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->qkv), rows * qkv_w * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->q), rows * m->l_heads * D * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->attn), rows * m->l_heads * D * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->gu), rows * 2 * m->l_inter * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->act), rows * m->l_inter * 4)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->hi), rows * kmax2 * 2)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->lo), rows * kmax2 * 2)) != YTC_OK) return s;
+  if (!m->last && (s = dev_alloc(m, reinterpret_cast<void**>(&m->last), static_cast<size_t>(m->batch) * m->hidden * 8)) != YTC_OK)
+    return s;
+  m->act_rows = rows;
+  return YTC_OK;
+}
+
+// ids [batch, len] (device int32) -> logits [batch, this rank's vocab rows] (device fp32) of the LAST position;
+// appends `len` tokens to the KV caches (qwen3::Qwen3ForCausalLM::forward, reference qwen3.cpp:449-457).
+int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m && ids && logits, "ytcuda_qwen3_forward: null argument");
+  YTC_REQUIRE(len > 0, "ytcuda_qwen3_forward: len must be positive");
+  if (m->cur_len + len > m->max_pos) {
+    set_last_error("ytcuda_qwen3_forward: %d cached + %d new tokens exceed max_position_embeddings %d "
+                   "(the reference's ring-buffer wrap is not implemented on the device)", m->cur_len, len, m->max_pos);
+    return YTC_UNSUPPORTED;
+  }
+  YTC_REQUIRE(m->embed && m->lm_head && m->final_norm, "ytcuda_qwen3_forward: embed / lm_head / norm not set");
+  for (const LayerW& L : m->lw)
+    YTC_REQUIRE(L.qkv && L.o && L.gate_up && L.down && L.q_norm && L.k_norm && L.norm1 && L.norm2,
+                "ytcuda_qwen3_forward: a layer weight is not set");
+  YTC_REQUIRE(m->tp_world == 1 || m->allreduce, "ytcuda_qwen3_forward: tensor parallel needs an all-reduce callback");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int B = m->batch, D = m->head_dim, Hd = m->hidden;
+  const int64_t rows = static_cast<int64_t>(B) * len;
+  int s = ensure_activations(m, rows);
+  if (s != YTC_OK) return s;
+  const int pos0 = m->cur_len;
+  const int kv_len = pos0 + len;
+  const int qkv_w = (m->l_heads + 2 * m->l_kv_heads) * D;
+  const int groups = m->heads / m->kv_heads;
+  const float scale = 1.0f / std::sqrt(static_cast<float>(D));
+  const size_t cache_layer = static_cast<size_t>(B) * m->l_kv_heads * m->max_pos * D;
+
+  if ((s = ytcuda_embedding(m->embed, ids, m->x, rows, Hd, m->vocab, st)) != YTC_OK) return s;
+  for (int l = 0; l < m->layers; ++l) {
+    const LayerW& W = m->lw[l];
+    float* kc = m->k_cache + l * cache_layer;
+    float* vc = m->v_cache + l * cache_layer;
+    if ((s = rmsnorm_rows(m->x, W.norm1, m->h, rows, Hd, m->eps, st)) != YTC_OK) return s;
+    if ((s = linear_w16(m, m->h, Hd, W.qkv, m->qkv, qkv_w, rows, qkv_w, Hd, false, st)) != YTC_OK) return s;
+    if ((s = ytcuda_qwen3_qkv_post(m->qkv, m->q, kc, vc, W.q_norm, W.k_norm, m->cos_t, m->sin_t, B, len, m->l_heads,
+                                   m->l_kv_heads, D, m->max_pos, pos0, pos0, m->eps, st)) != YTC_OK)
+      return s;
+    // attention over the cache; the output lands as [B, len, heads, D] = rows x (heads * D)
+    const int64_t qs[3] = {static_cast<int64_t>(m->l_heads) * len * D, static_cast<int64_t>(len) * D, D};
+    const int64_t ks[3] = {static_cast<int64_t>(m->l_kv_heads) * m->max_pos * D, static_cast<int64_t>(m->max_pos) * D, D};
+    const int64_t os[3] = {static_cast<int64_t>(len) * m->l_heads * D, D, static_cast<int64_t>(m->l_heads) * D};
+    if ((s = ytcuda_flash_attn_fwd(YTC_F32, m->q, kc, vc, m->attn, B, m->l_kv_heads, groups, len, kv_len, D, D, scale, qs,
+                                   ks, ks, os, 1, kv_len - len, nullptr, 0, nullptr, 0, 0, st)) != YTC_OK)
+      return s;
+    if ((s = linear_w16(m, m->attn, m->l_heads * D, W.o, m->proj, Hd, rows, Hd, m->l_heads * D, false, st)) != YTC_OK)
+      return s;
+    if (m->tp_world > 1 && (s = m->allreduce(m->proj, rows * Hd, m->allreduce_user)) != 0) {
+      set_last_error("ytcuda_qwen3_forward: all-reduce callback failed with %d", s);
+      return YTC_CUDA_ERROR;
+    }
+    if ((s = add_inplace(m->x, m->proj, rows * Hd, st)) != YTC_OK) return s;  // x2 = attn + x
+    if ((s = rmsnorm_rows(m->x, W.norm2, m->h, rows, Hd, m->eps, st)) != YTC_OK) return s;
+    if ((s = linear_w16(m, m->h, Hd, W.gate_up, m->gu, 2 * m->l_inter, rows, 2 * m->l_inter, Hd, false, st)) != YTC_OK)
+      return s;
+    if ((s = ytcuda_swiglu(YTC_F32, YTC_F32, m->gu, m->act, rows, m->l_inter, 2 * m->l_inter, m->l_inter, st)) != YTC_OK)
+      return s;
+    if ((s = linear_w16(m, m->act, m->l_inter, W.down, m->proj, Hd, rows, Hd, m->l_inter, false, st)) != YTC_OK) return s;
+    if (m->tp_world > 1 && (s = m->allreduce(m->proj, rows * Hd, m->allreduce_user)) != 0) {
+      set_last_error("ytcuda_qwen3_forward: all-reduce callback failed with %d", s);
+      return YTC_CUDA_ERROR;
+    }
+    if ((s = add_inplace(m->x, m->proj, rows * Hd, st)) != YTC_OK) return s;  // x2 += mlp
+  }
+  // last position of every sequence -> final norm -> vocabulary projection
+  float* last_in = m->last;
+  float* last_out = m->last + static_cast<size_t>(B) * Hd;
+  YTC_CUDA(cudaMemcpy2DAsync(last_in, Hd * sizeof(float), m->x + static_cast<int64_t>(len - 1) * Hd,
+                             static_cast<size_t>(len) * Hd * sizeof(float), Hd * sizeof(float), B,
+                             cudaMemcpyDeviceToDevice, st));
+  if ((s = rmsnorm_rows(last_in, m->final_norm, last_out, B, Hd, m->eps, st)) != YTC_OK) return s;
+  if ((s = linear_w16(m, last_out, Hd, m->lm_head, logits, m->l_vocab, B, m->l_vocab, Hd, false, st)) != YTC_OK) return s;
+  m->cur_len = kv_len;
+  return YTC_OK;
+}
+
+}  // extern "C"
