@@ -113,6 +113,20 @@ int ytcuda_layernorm(int dt_in, int dt_out, int dt_w, const void* x, const void*
 int ytcuda_reduce(int op, int dt_in, int dt_out, const void* x, void* y, int32_t* index, const int64_t* shape,
                   const int64_t* xstrides, int ndim, const int* axes, int naxes, void* stream);
 
+/* Same result as ytcuda_reduce for callers that must not allocate device memory while they run: a serving or
+ * real-time loop that cannot afford the allocator's lock and implicit synchronisation, a process whose device memory
+ * budget is fixed at start-up, a plug-in host that forbids cudaMalloc after initialisation. It has no counterpart in the reference (a CPU library, whose temporaries
+ * are thread_local host buffers). The long-reduction path keeps its partial results in a fixed 64 KiB array compiled
+ * into the library (8192 value/index pairs; each GPU that loads the library holds it until the process ends) instead
+ * of the library's grown-on-demand workspace, and the call makes no cudaMalloc / cudaFree of its own.
+ * A request whose partials do not fit the array is refused with YTC_INVALID_ARG and a message naming both sizes.
+ * The very first call on each device looks up the array's device address (cudaGetSymbolAddress); make that call once,
+ * with the device current, before starting any stream capture. All calls share the one array and do not clear
+ * it (every slot a call reads it has written first): two calls that overlap on the GPU, on different streams or
+ * from different threads, race on it - serialise them. */
+int ytcuda_reduce_noalloc(int op, int dt_in, int dt_out, const void* x, void* y, int32_t* index, const int64_t* shape,
+                          const int64_t* xstrides, int ndim, const int* axes, int naxes, void* stream);
+
 /* Fused memory-bound chain: out = cast(softmax(rmsNorm(x, weight, -1, eps) + residual, -1)).
  * x [batch, rows, hidden] fp32 contiguous; residual [batch, rows, hidden] (residual_batched != 0) or
  * [1, rows, hidden] broadcast over batch; one read of x and of the residual, one write of out.

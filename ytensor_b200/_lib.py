@@ -34,6 +34,7 @@ SIGNATURES = {
     "ytcuda_rmsnorm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp]),
     "ytcuda_layernorm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp]),
     "ytcuda_reduce": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "ytcuda_reduce_noalloc": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "ytcuda_rmsnorm_add_softmax_cast": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _f, _vp]),
     "ytcuda_binary": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "ytcuda_unary": (_i, [_i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp]),

@@ -16,6 +16,8 @@
 // (src/ytensor_math.inl:414-692).
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "ytc_common.cuh"
 
 namespace ytk {
@@ -746,11 +748,64 @@ static int run_nd(int op, int dt_in, int dt_out, int dt_w, const void* x, void* 
   return YTC_OK;
 }
 
+// ------------------------------------------------------------------ fixed scratch for callers that cannot allocate
+// Partial results of the split reduction for ytcuda_reduce_noalloc live here instead of in a cudaMalloc'ed
+// workspace: 8192 (value, index) pairs. Every GPU that loads the library carries these 64 KiB until exit.
+constexpr size_t NOALLOC_SCRATCH_BYTES = 64 * 1024;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// The array's name is only a host-side handle here: the device address has to be asked for, once per device,
+// while that device is current.
+static void* noalloc_scratch_address() {
+  static void* addr[16] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) {
+    set_last_error("ytcuda_reduce_noalloc: cannot identify the current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) {
+      set_last_error("ytcuda_reduce_noalloc: cudaGetSymbolAddress failed with %d (%s)", static_cast<int>(e),
+                     cudaGetErrorString(e));
+      return nullptr;
+    }
+    addr[dev] = p;
+  }
+  return addr[dev];
+}
+
 }  // namespace ytk
 
 using namespace ytk;
 
 extern "C" {
+
+int ytcuda_reduce_noalloc(int op, int dt_in, int dt_out, const void* x, void* y, int32_t* index, const int64_t* shape,
+                          const int64_t* xstrides, int ndim, const int* axes, int naxes, void* stream) {
+  YTC_REQUIRE(op >= 0 && op <= 2, "ytcuda_reduce_noalloc: op must be 0 (sum), 1 (mean) or 2 (max)");
+  YTC_REQUIRE(shape && xstrides && axes, "ytcuda_reduce_noalloc: null shape/strides/axes");
+  YTC_REQUIRE(ndim >= 1 && ndim <= MAXD, "ytcuda_reduce_noalloc: ndim %d outside [1, %d]", ndim, MAXD);
+  void* scratch = noalloc_scratch_address();
+  if (!scratch) return YTC_CUDA_ERROR;
+  int64_t ys[MAXD];
+  {
+    bool red[MAXD] = {false};
+    for (int i = 0; i < naxes && i < MAXD; ++i) red[((axes[i] % ndim) + ndim) % ndim] = true;
+    int64_t acc = 1;
+    for (int d = ndim - 1; d >= 0; --d) {
+      ys[d] = red[d] ? 0 : acc;
+      if (!red[d]) acc *= shape[d];
+    }
+  }
+  NdArgs a{shape, xstrides, ys, ndim, axes, naxes};
+  const int rop = op == 0 ? OP_SUM : op == 1 ? OP_MEAN : OP_MAX;
+  return run_nd(rop, dt_in, dt_out, YTC_F32, x, y, nullptr, nullptr, index, a, 0.f, true,
+                static_cast<cudaStream_t>(stream), "ytcuda_reduce_noalloc", scratch, NOALLOC_SCRATCH_BYTES);
+}
 
 int ytcuda_softmax(int dt_in, int dt_out, const void* x, void* y, const int64_t* shape, const int64_t* xstrides,
                    const int64_t* ystrides, int ndim, const int* axes, int naxes, void* stream) {
