@@ -55,15 +55,16 @@ class ClockSampler:
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, interval_ms: int = 100):
         self.idx = gpu_index
+        self.interval_ms = interval_ms
         self.proc = None
         self.lines: list[str] = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", str(self.interval_ms),
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -386,16 +387,115 @@ def chain_arm(args) -> None:
         "gpu_launches": int(launches), "clocks": clocks}))
 
 
+def decode_arm(args) -> None:
+    """BASELINE configs[4]: random-init decoder of the Qwen3-0.6B shape, 512-token prompt, greedy decode of 256
+    tokens. `--batch` = sequences (1 or 32; the default 64 of the GEMM workload means 1 here). Under
+    torch.distributed.run the ranks form one tensor-parallel group (total work fixed: strong scaling).
+    value = decoded tokens per second over all sequences; the prompt pass is reported next to it."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from ytensor_b200 import _lib
+    from ytensor_b200 import qwen3 as Q
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = _lib.lib()
+    B = 1 if args.batch == 64 else args.batch
+    prompt_len, new_tokens = 512, (256 if args.steps == 100 else args.steps)
+    cfg = Q.Qwen3Config(max_position_embeddings=prompt_len + new_tokens)
+    m = Q.Qwen3ForCausalLM(cfg, batch=B, tp_rank=rank, tp_world=world)
+    m.load_weights(Q.random_weights(cfg, seed=4))
+    prompt_host = torch.from_numpy(np.random.default_rng(4).integers(0, cfg.vocab_size, (B, prompt_len))
+                                   .astype(np.int32)).pin_memory()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run():
+        m.reset_kv_cache()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
+        ids = prompt_host.cuda(non_blocking=True)           # H2D of the step's input
+        logits = m.forward(ids)
+        tok, _ = m.argmax(logits)
+        ev[1].record()
+        out = [tok]
+        for _ in range(new_tokens - 1):
+            logits = m.forward(tok.reshape(B, 1).contiguous())
+            tok, _ = m.argmax(logits)
+            out.append(tok)
+        ev[2].record()
+        toks = torch.stack(out, 1).cpu()                     # D2H of the result
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2]), toks
+
+    run()  # warm-up: allocations, first-use attributes
+    barrier()
+    # a slow sampling period: every nvidia-smi query briefly holds the driver and delays kernel launches,
+    # which a launch-bound decode loop feels
+    sampler = ClockSampler(local, interval_ms=1000 if not args.no_clock_sampling else 10 ** 6)
+    if rank == 0 and not args.no_clock_sampling:
+        sampler.start()
+    n0 = L.ytcuda_launch_count()
+    t0 = time.perf_counter()
+    prefill_ms, decode_ms, toks = run()
+    barrier()
+    wall = time.perf_counter() - t0
+    launches = L.ytcuda_launch_count() - n0
+    clocks = sampler.stop() if (rank == 0 and not args.no_clock_sampling) else None
+    t = torch.tensor([prefill_ms, decode_ms, wall], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    prefill_ms, decode_ms, wall = (float(v) for v in t)
+    if rank == 0:
+        peaks = measured_peaks()
+        steps = new_tokens - 1
+        tok_s = B * steps / (decode_ms * 1e-3)
+        params = 28 * 15728640 + 151936 * 1024
+        bytes_per_step = params * 2 / world
+        achieved = bytes_per_step / (decode_ms * 1e-3 / steps) / 1e9
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": new_tokens,
+            "warmup": 1, "ms_per_step": decode_ms / steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 weights, f32 activations", "data": "synthetic",
+            "config": {"workload": "configs[4]: Qwen3-0.6B-shape decoder, random bf16 weights, prompt 512, greedy decode",
+                       "batch": B, "new_tokens": new_tokens, "parallelism": f"tp{world}",
+                       "l2": "weights (1.19 GB) larger than L2"},
+            "prefill_tokens_per_s": B * prompt_len / (prefill_ms * 1e-3), "prefill_ms": prefill_ms,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "skinny_linear_kernel",
+                         "peak_source": f"{peaks['source']} (copy bandwidth)",
+                         "algorithmic_bytes_per_launch": bytes_per_step,
+                         "note": "bytes of this rank's bf16 weights streamed once per decode step / step time"},
+            "e2e": {"value": B * new_tokens / wall, "unit": "tok/s", "h2d_bytes_per_step": int(prompt_host.numel() * 4),
+                    "d2h_bytes_per_step": int(toks.numel() * 4),
+                    "note": "prompt H2D + prefill + decode + tokens D2H, wall clock, generated tokens / s"},
+            "gpu_launches": int(launches), "clocks": clocks, "first_tokens": toks[0, :8].tolist()}))
+    m.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     global BATCH, FLOPS_PER_STEP, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "attn", "chain"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "attn", "chain", "decode"],
                     help="gemm (default) is the headline bench line; attn and chain measure configs[2] and configs[3]")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-clock-sampling", action="store_true", help="decode workload: do not run nvidia-smi beside it")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures only)")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="batch items per step; anything but 64 is a profiling case, not a bench line")
@@ -404,6 +504,8 @@ def main() -> None:
         return attention_arm(args)
     if args.workload == "chain":
         return chain_arm(args)
+    if args.workload == "decode":
+        return decode_arm(args)
     if args.batch != BATCH:
         BATCH = args.batch
         FLOPS_PER_STEP = 2.0 * BATCH * M * K * N

@@ -1,0 +1,78 @@
+"""GPU (2 devices): the tensor-parallel decoder gives the reference's logits and greedy tokens.
+Two child processes, one per GPU, NCCL all-reduce after the attention output and down projections.
+Skipped when fewer than two devices are visible."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+SMALL = dict(hidden_size=64, num_hidden_layers=2, vocab_size=512, intermediate_size=96, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=128, max_position_embeddings=64)
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    from ytensor_b200 import qwen3 as Q
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        g = np.load(ROOT / "tests" / "golden" / "golden_qwen3.npz")
+        # small model: full logits against the reference, every rank holding its vocabulary rows
+        cfg = Q.Qwen3Config(**SMALL)
+        m = Q.Qwen3ForCausalLM(cfg, batch=2, tp_rank=rank, tp_world=world)
+        m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
+        want = g["small_logits_b2"]
+        ids = torch.from_numpy(g["small_ids_b2"]).cuda()
+        logits = m.forward(ids)
+        for step in range(6):
+            got = logits.cpu().numpy()
+            ref = want[step][:, m.v0:m.v1]
+            err = np.abs(got - ref).max() / np.abs(want[step]).max()
+            assert err < 1e-4, (step, err)
+            tok, _ = m.argmax(logits)
+            assert np.array_equal(tok.cpu().numpy(), want[step].argmax(1))
+            if step < 5:
+                logits = m.forward(tok.reshape(2, 1).contiguous())
+        m.close()
+        # Qwen3-0.6B shape: the first 16 greedy tokens of the reference
+        cfg = Q.Qwen3Config(max_position_embeddings=768)
+        m = Q.Qwen3ForCausalLM(cfg, batch=1, tp_rank=rank, tp_world=world)
+        m.load_weights(Q.random_weights(cfg, seed=4))
+        toks = m.generate_greedy(torch.from_numpy(g["full_prompt"]).cuda(), 16).cpu().numpy()[0]
+        assert np.array_equal(toks, g["full_tokens"][:16]), (toks, g["full_tokens"][:16])
+        m.close()
+        ret[rank] = "ok"
+    except Exception as e:  # noqa: BLE001 - reported to the parent
+        ret[rank] = f"{type(e).__name__}: {e}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_tensor_parallel_matches_reference():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = 29600 + (os.getpid() % 2000)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(600)
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+                pytest.fail("a rank did not finish")
+        assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)

@@ -583,6 +583,294 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(const AttnSimtParams p) 
   }
 }
 
+
+// ------------------------------------------------------------------ few query rows (decode): split over the keys
+// One CTA = one (batch, kv head) and one slice of the keys; all R = groups * q_len query rows that share this K/V
+// head are handled together, so every K / V row is read once (128-bit, coalesced: a warp reads one whole row).
+// Each warp walks its keys with an online softmax per query row (running max, sum, and its 4 value columns per
+// lane and 128 columns), warps are merged through shared memory, and the per-slice partials (max, sum, O) go to a
+// scratch buffer that attn_decode_merge_kernel combines. Memory-bound on the KV cache.
+constexpr int DEC_MAX_ROWS = 8;   // groups * q_len handled per CTA
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_MAX_VEC = 2;    // float4 per lane per row: head / value dim up to 256
+
+struct AttnDecodeParams {
+  AttnSimtParams a;
+  int splits;
+  int keys_per_split;
+  float* part;  // [batch*kv_heads][splits][R][2 + dv]
+};
+
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnDecodeParams dp) {
+  const AttnSimtParams& p = dp.a;
+  __shared__ float sm_m[DEC_WARPS][DEC_MAX_ROWS], sm_l[DEC_WARPS][DEC_MAX_ROWS];
+  __shared__ float sm_o[DEC_WARPS][DEC_MAX_ROWS][DEC_MAX_VEC * 128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x;
+  const int bk = blockIdx.y;  // batch * kv_heads + kv head
+  const int b = bk / p.kv_heads, kvh = bk - b * p.kv_heads;
+  const int R = p.groups * p.q_len;
+  const int nvq = (p.d + 127) / 128, nvv = (p.dv + 127) / 128;  // float4 slots per lane
+  const int64_t ko = b * p.k_sb + kvh * p.k_sh, vo = b * p.v_sb + kvh * p.v_sh;
+
+  // query rows in registers: row r = (group g, query index qi), head = kvh * groups + g
+  float4 q[DEC_MAX_ROWS][DEC_MAX_VEC];
+  float m_run[DEC_MAX_ROWS], l_run[DEC_MAX_ROWS];
+  float4 acc[DEC_MAX_ROWS][DEC_MAX_VEC];
+#pragma unroll
+  for (int r = 0; r < DEC_MAX_ROWS; ++r) {
+    m_run[r] = -CUDART_INF_F;
+    l_run[r] = 0.f;
+#pragma unroll
+    for (int j = 0; j < DEC_MAX_VEC; ++j) {
+      acc[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      q[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < R && j < nvq) {
+        const int g = r / p.q_len, qi = r - g * p.q_len;
+        const int c = j * 128 + lane * 4;
+        if (c < p.d) {
+          const int64_t qo = b * p.q_sb + (kvh * p.groups + g) * p.q_sh + qi * p.q_sr + c;
+          q[r][j] = make_float4(load_as_f32(p.Q, qo, p.dt), load_as_f32(p.Q, qo + 1, p.dt),
+                                load_as_f32(p.Q, qo + 2, p.dt), load_as_f32(p.Q, qo + 3, p.dt));
+        }
+      }
+    }
+  }
+  const int k_begin = split * dp.keys_per_split;
+  int k_end = k_begin + dp.keys_per_split;
+  if (k_end > p.kv_len) k_end = p.kv_len;
+  for (int key = k_begin + warp; key < k_end; key += DEC_WARPS) {
+    float4 kv[DEC_MAX_VEC], vv[DEC_MAX_VEC];
+#pragma unroll
+    for (int j = 0; j < DEC_MAX_VEC; ++j) {
+      kv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      vv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int c = j * 128 + lane * 4;
+      if (j < nvq && c < p.d) {
+        const int64_t o = ko + static_cast<int64_t>(key) * p.k_sr + c;
+        if (p.dt == YTC_F32) kv[j] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.K) + o);
+        else kv[j] = make_float4(load_as_f32(p.K, o, p.dt), load_as_f32(p.K, o + 1, p.dt), load_as_f32(p.K, o + 2, p.dt),
+                                 load_as_f32(p.K, o + 3, p.dt));
+      }
+      if (j < nvv && c < p.dv) {
+        const int64_t o = vo + static_cast<int64_t>(key) * p.v_sr + c;
+        if (p.dt == YTC_F32) vv[j] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.V) + o);
+        else vv[j] = make_float4(load_as_f32(p.V, o, p.dt), load_as_f32(p.V, o + 1, p.dt), load_as_f32(p.V, o + 2, p.dt),
+                                 load_as_f32(p.V, o + 3, p.dt));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < DEC_MAX_ROWS; ++r) {
+      if (r >= R) break;
+      const int qi = r % p.q_len;
+      bool vis = !p.causal || key <= qi + p.causal_off;
+      if (vis && p.mask) vis = p.mask[static_cast<int64_t>(qi) * p.mask_rs + key] != 0;
+      if (!vis) continue;  // uniform over the warp
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < DEC_MAX_VEC; ++j) {
+        dot = fmaf(q[r][j].x, kv[j].x, dot);
+        dot = fmaf(q[r][j].y, kv[j].y, dot);
+        dot = fmaf(q[r][j].z, kv[j].z, dot);
+        dot = fmaf(q[r][j].w, kv[j].w, dot);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      float sc = dot * p.scale;
+      if (p.bias) sc += p.bias[static_cast<int64_t>(qi) * p.bias_rs + key * p.bias_cs];
+      const float m_new = fmaxf(m_run[r], sc);
+      const float alpha = __expf(m_run[r] - m_new);  // 0 on the first visible key (m_run = -inf)
+      const float pr = __expf(sc - m_new);
+      l_run[r] = l_run[r] * alpha + pr;
+      m_run[r] = m_new;
+#pragma unroll
+      for (int j = 0; j < DEC_MAX_VEC; ++j) {
+        acc[r][j].x = fmaf(pr, vv[j].x, acc[r][j].x * alpha);
+        acc[r][j].y = fmaf(pr, vv[j].y, acc[r][j].y * alpha);
+        acc[r][j].z = fmaf(pr, vv[j].z, acc[r][j].z * alpha);
+        acc[r][j].w = fmaf(pr, vv[j].w, acc[r][j].w * alpha);
+      }
+    }
+  }
+  // merge the warps of this CTA
+#pragma unroll
+  for (int r = 0; r < DEC_MAX_ROWS; ++r) {
+    if (r >= R) break;
+    if (lane == 0) {
+      sm_m[warp][r] = m_run[r];
+      sm_l[warp][r] = l_run[r];
+    }
+#pragma unroll
+    for (int j = 0; j < DEC_MAX_VEC; ++j)
+      if (j < nvv) *reinterpret_cast<float4*>(&sm_o[warp][r][j * 128 + lane * 4]) = acc[r][j];
+  }
+  __syncthreads();
+  const int stride = 2 + p.dv;
+  float* out = dp.part + (static_cast<int64_t>(bk) * dp.splits + split) * R * stride;
+  for (int idx = threadIdx.x; idx < R * p.dv; idx += DEC_WARPS * 32) {
+    const int r = idx / p.dv, c = idx - r * p.dv;
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, sm_m[w][r]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float f = (sm_m[w][r] == -CUDART_INF_F) ? 0.f : __expf(sm_m[w][r] - m);
+      l += sm_l[w][r] * f;
+      o += sm_o[w][r][c] * f;
+    }
+    out[r * stride + 2 + c] = o;
+    if (c == 0) {
+      out[r * stride] = m;
+      out[r * stride + 1] = l;
+    }
+  }
+}
+
+// Combines the per-slice partials: O = sum_s O_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m); rows that saw no key -> 0.
+__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const AttnDecodeParams dp) {
+  const AttnSimtParams& p = dp.a;
+  const int bk = blockIdx.x;
+  const int b = bk / p.kv_heads, kvh = bk - b * p.kv_heads;
+  const int R = p.groups * p.q_len;
+  const int stride = 2 + p.dv;
+  const float* base = dp.part + static_cast<int64_t>(bk) * dp.splits * R * stride;
+  for (int idx = threadIdx.x; idx < R * p.dv; idx += blockDim.x) {
+    const int r = idx / p.dv, c = idx - r * p.dv;
+    float m = -CUDART_INF_F;
+    for (int s = 0; s < dp.splits; ++s) m = fmaxf(m, base[(s * R + r) * stride]);
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < dp.splits; ++s) {
+      const float ms = base[(s * R + r) * stride];
+      const float f = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - m);
+      l += base[(s * R + r) * stride + 1] * f;
+      o += base[(s * R + r) * stride + 2 + c] * f;
+    }
+    const int g = r / p.q_len, qi = r - g * p.q_len;
+    const int64_t oo = b * p.o_sb + (kvh * p.groups + g) * p.o_sh + qi * p.o_sr + c;
+    store_from_f32(p.O, oo, l > 0.f ? o / l : 0.f, p.dt);
+  }
+}
+
+// ------------------------------------------------------------------ fp32-accumulating tiled kernel (any dtype)
+// 32 query rows x 32 keys per step, 128 threads: thread (i, g) = (row, quarter). S = Q K^T from shared memory with
+// 8 scores per thread in registers, online softmax across the 4 threads of a row by shuffles, then
+// O[i, 32 g .. 32 g + 31] += P[i, :] V with P passed through shared memory. The prefill path of the fp32 decoder.
+constexpr int TL_BM = 32, TL_BN = 32, TL_D = 128, TL_PAD = 4;
+
+__global__ void __launch_bounds__(128) attn_tile_kernel(const AttnSimtParams p) {
+  extern __shared__ __align__(16) float tl_smem[];
+  float(*Qs)[TL_D + TL_PAD] = reinterpret_cast<float(*)[TL_D + TL_PAD]>(tl_smem);
+  float(*Ks)[TL_D + TL_PAD] = Qs + TL_BM;
+  float(*Vs)[TL_D + TL_PAD] = Ks + TL_BN;
+  float(*Ps)[TL_BN + 1] = reinterpret_cast<float(*)[TL_BN + 1]>(Vs + TL_BN);
+  const int tid = threadIdx.x;
+  const int ri = tid >> 2, g = tid & 3;
+  const int heads = p.kv_heads * p.groups;
+  const int row_blocks = (p.q_len + TL_BM - 1) / TL_BM;
+  const int rbk = row_blocks - 1 - static_cast<int>(blockIdx.x);  // long causal rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / p.groups;
+  const int row0 = rbk * TL_BM;
+  const int row = row0 + ri;
+  const int64_t qo = b * p.q_sb + h * p.q_sh;
+  const int64_t ko = b * p.k_sb + kvh * p.k_sh, vo = b * p.v_sb + kvh * p.v_sh;
+  (void)heads;
+  // stage Q (zero-padded to TL_D columns and TL_BM rows)
+  for (int i = tid; i < TL_BM * TL_D; i += 128) {
+    const int r = i / TL_D, c = i - r * TL_D;
+    Qs[r][c] = (row0 + r < p.q_len && c < p.d)
+                   ? load_as_f32(p.Q, qo + static_cast<int64_t>(row0 + r) * p.q_sr + c, p.dt) : 0.f;
+  }
+  float acc[32];
+#pragma unroll
+  for (int c = 0; c < 32; ++c) acc[c] = 0.f;
+  float m_run = -CUDART_INF_F, l_run = 0.f;
+  int last = p.kv_len - 1;
+  if (p.causal) {
+    const int lim = row0 + TL_BM - 1 + p.causal_off;
+    if (lim < last) last = lim;
+  }
+  const int my_limit = (row < p.q_len) ? ((p.causal && row + p.causal_off < p.kv_len - 1) ? row + p.causal_off : p.kv_len - 1)
+                                       : -1;
+  for (int k0 = 0; k0 <= last; k0 += TL_BN) {
+    __syncthreads();
+    for (int i = tid; i < TL_BN * TL_D; i += 128) {
+      const int r = i / TL_D, c = i - r * TL_D;
+      const bool in = k0 + r < p.kv_len;
+      Ks[r][c] = (in && c < p.d) ? load_as_f32(p.K, ko + static_cast<int64_t>(k0 + r) * p.k_sr + c, p.dt) : 0.f;
+      Vs[r][c] = (in && c < p.dv) ? load_as_f32(p.V, vo + static_cast<int64_t>(k0 + r) * p.v_sr + c, p.dt) : 0.f;
+    }
+    __syncthreads();
+    float sc[8];
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) sc[jj] = 0.f;
+#pragma unroll 4
+    for (int k4 = 0; k4 < TL_D; k4 += 4) {
+      const float4 qv = *reinterpret_cast<const float4*>(&Qs[ri][k4]);
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const float4 kv = *reinterpret_cast<const float4*>(&Ks[g * 8 + jj][k4]);
+        sc[jj] = fmaf(qv.x, kv.x, sc[jj]);
+        sc[jj] = fmaf(qv.y, kv.y, sc[jj]);
+        sc[jj] = fmaf(qv.z, kv.z, sc[jj]);
+        sc[jj] = fmaf(qv.w, kv.w, sc[jj]);
+      }
+    }
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const int key = k0 + g * 8 + jj;
+      bool vis = key <= my_limit;
+      if (vis && p.mask) vis = p.mask[static_cast<int64_t>(row) * p.mask_rs + key] != 0;
+      float v = sc[jj] * p.scale;
+      if (vis && p.bias) v += p.bias[static_cast<int64_t>(row) * p.bias_rs + key * p.bias_cs];
+      sc[jj] = vis ? v : -CUDART_INF_F;
+      mx = fmaxf(mx, sc[jj]);
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+    const float alpha = (m_run == -CUDART_INF_F) ? 0.f : __expf(m_run - m_use);
+    float ps = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const float pr = __expf(sc[jj] - m_use);  // exp(-inf) = 0 for hidden keys
+      Ps[ri][g * 8 + jj] = pr;
+      ps += pr;
+    }
+    ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+    l_run = l_run * alpha + ps;
+    m_run = m_new;
+    __syncwarp();  // the 4 threads of a row sit in one warp: Ps[ri][*] is complete for them
+#pragma unroll
+    for (int c = 0; c < 32; ++c) acc[c] *= alpha;
+#pragma unroll 4
+    for (int j = 0; j < TL_BN; ++j) {
+      const float pr = Ps[ri][j];
+#pragma unroll
+      for (int c4 = 0; c4 < 32; c4 += 4) {
+        const float4 vv = *reinterpret_cast<const float4*>(&Vs[j][g * 32 + c4]);
+        acc[c4] = fmaf(pr, vv.x, acc[c4]);
+        acc[c4 + 1] = fmaf(pr, vv.y, acc[c4 + 1]);
+        acc[c4 + 2] = fmaf(pr, vv.z, acc[c4 + 2]);
+        acc[c4 + 3] = fmaf(pr, vv.w, acc[c4 + 3]);
+      }
+    }
+  }
+  if (row < p.q_len) {
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    const int64_t oo = b * p.o_sb + h * p.o_sh + static_cast<int64_t>(row) * p.o_sr;
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const int col = g * 32 + c;
+      if (col < p.dv) store_from_f32(p.O, oo + col, acc[c] * inv, p.dt);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host side
 static int g_attn_path = 0;  // 0 automatic, 1 always the one-warp-per-row kernel, 2 tensor-core kernel or fail
 
@@ -729,6 +1017,47 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
   p.d = head_dim; p.dv = value_dim;
   p.causal = causal; p.causal_off = causal_offset;
   p.scale = scale; p.dt = dtype;
+  // few query rows per K/V head (decode): split the keys over CTAs, merge through a scratch buffer
+  const bool vec_ok = dtype != YTC_F32 ||
+                      (k_strides[2] % 4 == 0 && k_strides[1] % 4 == 0 && k_strides[0] % 4 == 0 && v_strides[2] % 4 == 0 &&
+                       v_strides[1] % 4 == 0 && v_strides[0] % 4 == 0 && (reinterpret_cast<uint64_t>(K) & 15) == 0 &&
+                       (reinterpret_cast<uint64_t>(V) & 15) == 0);
+  if (groups * q_len <= DEC_MAX_ROWS && head_dim % 4 == 0 && value_dim % 4 == 0 && head_dim <= 128 * DEC_MAX_VEC &&
+      value_dim <= 128 * DEC_MAX_VEC && kv_len > 0 && vec_ok && static_cast<int64_t>(batch) * kv_heads <= 65535) {
+    AttnDecodeParams dp;
+    dp.a = p;
+    const int bk = batch * kv_heads;
+    int splits = (2 * sm_count() + bk - 1) / bk;
+    const int max_splits = (kv_len + 63) / 64;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    dp.keys_per_split = (kv_len + splits - 1) / splits;
+    dp.splits = (kv_len + dp.keys_per_split - 1) / dp.keys_per_split;
+    const size_t need = static_cast<size_t>(bk) * dp.splits * groups * q_len * (2 + value_dim) * sizeof(float);
+    dp.part = static_cast<float*>(device_workspace(need));
+    if (!dp.part) {
+      set_last_error("ytcuda_flash_attn_fwd: cannot allocate %zu bytes of scratch", need);
+      return YTC_CUDA_ERROR;
+    }
+    attn_decode_kernel<<<dim3(dp.splits, bk), DEC_WARPS * 32, 0, st>>>(dp);
+    attn_decode_merge_kernel<<<bk, 128, 0, st>>>(dp);
+    count_launch(2);
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
+  }
+  if (head_dim <= TL_D && value_dim <= TL_D && heads <= 65535 && batch <= 65535) {
+    dim3 grid((q_len + TL_BM - 1) / TL_BM, heads, batch);
+    constexpr int TL_SMEM = ((TL_BM + 2 * TL_BN) * (TL_D + TL_PAD) + TL_BM * (TL_BN + 1)) * 4;
+    static bool attr = false;
+    if (!attr) {
+      YTC_CUDA(cudaFuncSetAttribute(attn_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM));
+      attr = true;
+    }
+    attn_tile_kernel<<<grid, 128, TL_SMEM, st>>>(p);
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
+  }
   const int64_t rows = static_cast<int64_t>(batch) * heads * q_len;
   const int64_t blocks = (rows + 3) / 4;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
