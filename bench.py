@@ -382,7 +382,7 @@ def chain_arm(args) -> None:
                                + ("" if B == 32 else " (PROFILING CASE: reduced batch)"),
                    "l2": "inputs larger than L2 (x is 2.1 GB)"},
         "roofline": {"bound": "hbm", "achieved": val, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": val / peaks["hbm_gbs"], "traffic": None, "kernel": "row_kernel<OP_CHAIN,256>",
+                     "frac": val / peaks["hbm_gbs"], "traffic": None, "kernel": "chain_fast_kernel<4>",
                      "peak_source": f"{peaks['source']} (copy bandwidth)", "algorithmic_bytes_per_launch": algo_bytes},
         "gpu_launches": int(launches), "clocks": clocks}))
 

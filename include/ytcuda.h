@@ -74,6 +74,11 @@ int ytcuda_gemm_set_path(int path);
  * (include/kernel/avx2/gemm_utils.hpp:59-77). */
 int ytcuda_gemm_set_tuning(int a_prefetch_kblocks, int split_loads);
 
+/* Use of the CTA-pair (cta_group::2, 256 x 256 tile per two SMs) form of the tcgen05 kernel: 0 = automatic (large
+ * problems), 1 = whenever the operands qualify, 2 = never. Process-wide, meant for tests and measurements; the
+ * counterpart of the reference's per-call backend choice (include/ytensor_math.hpp:70-73). */
+int ytcuda_gemm_set_pair_mode(int mode);
+
 /* Same computation with HOST buffers (pinned or pageable): copies A and B to the device,
  * multiplies, copies C back, and returns when C is complete. Batch items are pipelined so
  * that copies overlap the multiplication. This is what a YTensor that lives in host memory

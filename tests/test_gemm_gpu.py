@@ -128,6 +128,30 @@ def test_bf16_tcgen05_vs_oracle(L, api, port, layout, m, n, k):
     assert normwise(got, want) < H_TOL
 
 
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (1000, 776, 200), (512, 512, 1088), (264, 520, 72)])
+def test_bf16_cta_pair_kernel_vs_oracle(L, api, port, layout, m, n, k):
+    """The 2-CTA form (cta_group::2, 256 x 256 tile per CTA pair) forced on, against the oracle."""
+    rng = np.random.default_rng(m + 5 * n + 11 * k)
+    a = port.f32_to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    b = port.f32_to_bf16((rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+    want = port.bf16_to_f32(port.matmul_16(a, b, 1))
+    ta = bits_to_torch(a, torch.bfloat16) if layout[0] == "k" else bits_to_torch(a.T.copy(), torch.bfloat16).t()
+    tb = bits_to_torch(b, torch.bfloat16) if layout[1] == "n" else bits_to_torch(b.T.copy(), torch.bfloat16).t()
+    L.ytcuda_gemm_set_path(2)
+    L.ytcuda_gemm_set_pair_mode(1)
+    try:
+        got_pair = torch_to_bits(api.matmul(ta, tb))
+        L.ytcuda_gemm_set_pair_mode(2)
+        got_single = torch_to_bits(api.matmul(ta, tb))
+    finally:
+        L.ytcuda_gemm_set_path(0)
+        L.ytcuda_gemm_set_pair_mode(0)
+    status_ok(L)
+    assert normwise(port.bf16_to_f32(got_pair), want) < H_TOL
+    assert np.array_equal(got_pair, got_single)  # same products, same order of accumulation along k
+
+
 def test_bf16_fp32_output_is_tight(L, api, port):
     """With fp32 output the tensor-core result matches the fp32 oracle far inside the 16-bit tolerance."""
     rng = np.random.default_rng(5)

@@ -363,6 +363,208 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   if (threadIdx.x == 0 && *abort_word) atomicExch(p.status, YTC_TIMEOUT);
 }
 
+
+// ------------------------------------------------------------------ tcgen05 path, CTA pairs
+// Two CTAs (a cluster of 2 on neighbouring SMs) share one 256 x 256 output tile: each loads its own 128 rows of A
+// and HALF of the B tile (128 columns), the leader CTA issues 256 x 256 x 16 MMAs (cta_group::2) that read both
+// halves, and each CTA drains its own 128 x 256 accumulator. Per SM this halves the B bytes moved through shared
+// memory and leaves room for a 6-stage ring. Barriers: TMA completion of both CTAs is counted on the leader's
+// `full` barrier; the leader's commits free the stage in both CTAs and publish the accumulator to both.
+constexpr int TC2_STAGES = 6;
+constexpr int TC2_BN = 256;
+
+struct Tc2Smem {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;         // 128 rows of A
+  static constexpr int B_BYTES = (TC2_BN / 2) * TC_BK * 2;  // 128 columns of B
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = TC2_STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * TC2_STAGES + 4) * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+    gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmTcParams p) {
+  using S = Tc2Smem;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + TC2_STAGES;
+  uint64_t* tfull_bar = empty_bar + TC2_STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const bool leader = cta == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC2_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 8);  // 4 epilogue warps of each CTA
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < p.total_tiles; tile += n_clusters) {
+        const int b = tile / tiles_per_batch;
+        const int rem = tile - b * tiles_per_batch;
+        const int mb = rem / p.tiles_n;
+        const int nb = rem - mb * p.tiles_n;
+        const int ba = p.a_bcast ? 0 : b;
+        const int bb = p.b_bcast ? 0 : b;
+        const int m0 = mb * 256 + static_cast<int>(cta) * TC_BM;
+        const int n0 = nb * TC2_BN + static_cast<int>(cta) * (TC2_BN / 2);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          if (!p.a_mn) {
+            tma_load_3d_pair(sa, &tmA, full_leader, kb * TC_BK, m0, ba);
+          } else {
+#pragma unroll
+            for (int c = 0; c < TC_BM / 64; ++c) tma_load_3d_pair(sa + c * 8192, &tmA, full_leader, m0 + c * 64, kb * TC_BK, ba);
+          }
+          if (!p.b_mn) {
+            tma_load_3d_pair(sb, &tmB, full_leader, kb * TC_BK, n0, bb);
+          } else {
+#pragma unroll
+            for (int c = 0; c < TC2_BN / 128; ++c) tma_load_3d_pair(sb + c * 8192, &tmB, full_leader, n0 + c * 64, kb * TC_BK, bb);
+          }
+          if (++stage == TC2_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < p.total_tiles; tile += n_clusters) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * TC2_BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t b_base = a_base + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            const uint64_t adesc = p.a_mn ? umma_smem_desc_sw128(a_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = p.b_mn ? umma_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            tc_mma_f16_pair(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          tc_commit_pair(smem_u32(&empty_bar[stage]));
+          tc_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == TC2_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(smem_u32(&tfull_bar[acc]));
+        tc_commit_pair(map_to_cta(smem_u32(&tfull_bar[acc]), 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------ epilogue (both CTAs, own 128 rows x 256 columns)
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool c_unit = (p.csc == 1);
+    const int esz = (p.out_dtype == YTC_F32) ? 4 : 2;
+    for (int tile = cluster_id; tile < p.total_tiles; tile += n_clusters) {
+      const int b = tile / tiles_per_batch;
+      const int rem = tile - b * tiles_per_batch;
+      const int mb = rem / p.tiles_n;
+      const int nb = rem - mb * p.tiles_n;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word)) break;
+      tc_fence_after();
+      const int gm = mb * 256 + static_cast<int>(cta) * TC_BM + row;
+      const bool row_ok = gm < p.M;
+      const int64_t row_off = static_cast<int64_t>(b) * p.bsc + static_cast<int64_t>(gm) * p.rsc;
+      const bool vec_ok =
+          c_unit && (((reinterpret_cast<uint64_t>(p.C) + static_cast<uint64_t>(row_off) * esz) & 15u) == 0);
+      const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * TC2_BN) + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < TC2_BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c0, r);
+        tmem_ld_wait();
+        const int gn0 = nb * TC2_BN + c0;
+        if (gn0 < p.N) {
+          if (p.out_dtype == YTC_BF16) tc_store_chunk<TC2_BN, YTC_BF16>(p, r, row_off, gn0, row_ok, vec_ok);
+          else if (p.out_dtype == YTC_F32) tc_store_chunk<TC2_BN, YTC_F32>(p, r, row_off, gn0, row_ok, vec_ok);
+          else tc_store_chunk<TC2_BN, YTC_F16>(p, r, row_off, gn0, row_ok, vec_ok);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still read its shared or tensor memory
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word) atomicExch(p.status, YTC_TIMEOUT);
+}
+
 // ------------------------------------------------------------------ FFMA path
 constexpr int SM_BM = 128, SM_BN = 128, SM_BK = 16, SM_THREADS = 256, SM_PAD = 4;
 
@@ -517,6 +719,8 @@ static bool tc_operand_ok(const void* ptr, int64_t rs, int64_t cs, int64_t bs, i
 static int g_tc_a_prefetch = 0;
 // 1 = fetch K-major operand tiles as 64-row boxes instead of one tall box.
 static int g_tc_split_loads = 0;
+// CTA-pair kernel: 0 = automatic, 1 = whenever the layout allows, 2 = never.
+static int g_tc_pair = 0;
 
 static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
                      float alpha, float beta, int a_mn, int64_t lda, int b_mn, int64_t ldb, int64_t rsc, int64_t csc,
@@ -526,6 +730,9 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
   const int a_bcast = (batch > 1 && bsa == 0) ? 1 : 0;
   const int b_bcast = (batch > 1 && bsb == 0) ? 1 : 0;
   const int BN = (n <= 128) ? 128 : 256;
+  // CTA pairs pay off on large problems; small ones keep one CTA per tile (more tiles to spread over the SMs)
+  const bool pair = g_tc_pair != 2 && (g_tc_pair == 1 || (m >= 512 && n >= 256 && k >= 256 &&
+                                                        static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) * batch >= 74));
   {
     const uint64_t nb = (a_bcast || batch == 1) ? 1 : static_cast<uint64_t>(batch);
     uint64_t dims[3], strides[2];
@@ -544,7 +751,7 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
     const uint64_t nb = (b_bcast || batch == 1) ? 1 : static_cast<uint64_t>(batch);
     uint64_t dims[3], strides[2];
     uint32_t box[3];
-    if (!b_mn) { dims[0] = k; dims[1] = n; box[0] = TC_BK; box[1] = g_tc_split_loads ? 64u : static_cast<uint32_t>(BN); }
+    if (!b_mn) { dims[0] = k; dims[1] = n; box[0] = TC_BK; box[1] = pair ? 128u : (g_tc_split_loads ? 64u : static_cast<uint32_t>(BN)); }
     else       { dims[0] = n; dims[1] = k; box[0] = 64;    box[1] = TC_BK; }
     dims[2] = nb;
     box[2] = 1;
@@ -578,6 +785,23 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
   if (!p.status) {
     set_last_error("ytcuda_gemm: no device status word");
     return YTC_CUDA_ERROR;
+  }
+  if (pair) {
+    p.idesc = umma_idesc(dtype_in == YTC_BF16 ? 1u : 0u, a_mn, b_mn, 256, TC2_BN);
+    p.tiles_m = (m + 255) / 256;
+    p.tiles_n = (n + TC2_BN - 1) / TC2_BN;
+    p.total_tiles = static_cast<int>(static_cast<int64_t>(p.tiles_m) * p.tiles_n * batch);
+    int clusters = sm_count() / 2;
+    if (clusters > p.total_tiles) clusters = p.total_tiles;
+    static bool attr2 = false;
+    if (!attr2) {
+      YTC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc2Smem::DYN_BYTES));
+      attr2 = true;
+    }
+    gemm_tc2_kernel<<<clusters * 2, TC_THREADS, Tc2Smem::DYN_BYTES, st>>>(tmA, tmB, p);
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
   }
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   if (BN == 256) {
@@ -646,6 +870,12 @@ static int g_gemm_path = 0;
 using namespace ytk;
 
 extern "C" {
+
+int ytcuda_gemm_set_pair_mode(int mode) {
+  YTC_REQUIRE(mode >= 0 && mode <= 2, "ytcuda_gemm_set_pair_mode: mode must be 0 (auto), 1 (always) or 2 (never)");
+  g_tc_pair = mode;
+  return YTC_OK;
+}
 
 int ytcuda_gemm_set_tuning(int a_prefetch_kblocks, int split_loads) {
   YTC_REQUIRE(a_prefetch_kblocks >= 0 && a_prefetch_kblocks <= 64, "ytcuda_gemm_set_tuning: prefetch distance outside [0, 64]");

@@ -149,9 +149,14 @@ __global__ void __launch_bounds__(G < 256 ? 256 : G) row_kernel(const RowParams 
   const int64_t row_blocks = (p.rows + RPC - 1) / RPC;
   const float invL = 1.0f / static_cast<float>(p.L);
 
+  // chain with a residual shared by `copies` batch items: walk the rows so that the `copies` rows that read the same
+  // residual row are handled back to back (by neighbouring CTAs) - the residual row then comes from HBM once and
+  // from L2 for the other uses, instead of being evicted between uses that lie a whole batch item apart.
+  const int64_t copies = (OP == OP_CHAIN && p.r_rows < p.rows) ? p.rows / p.r_rows : 1;
   for (int64_t rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
-    const int64_t row = rb * RPC + group;
+    int64_t row = rb * RPC + group;
     const bool row_ok = row < p.rows;
+    if (OP == OP_CHAIN && copies > 1 && row_ok) row = (row % copies) * p.r_rows + row / copies;
     F4 x[VPT];
     bool act[VPT];
 #pragma unroll
@@ -282,6 +287,91 @@ __global__ void __launch_bounds__(G < 256 ? 256 : G) row_kernel(const RowParams 
 #pragma unroll
     for (int v = 0; v < VPT; ++v)
       if (act[v]) store4(p.y, row * p.y_rs + (v * G + t) * 4, x[v], p.dt_out);
+  }
+}
+
+
+
+// ------------------------------------------------------------------ fused chain, specialised
+// fp32 in, bf16 out, contiguous rows of exactly 1024 * VPT columns, 256 threads per row: no predicates, no dtype
+// switches, exp2 by ex2.approx with the log2(e) factor folded into one FMA, bf16 narrowing (the reference's rule:
+// add half an ulp only when the kept LSB is 1, then truncate) in three integer operations plus one byte permute per
+// pair. About a dozen instructions per element, 4 CTAs per SM.
+__device__ __forceinline__ float ex2_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t bf16_pair_ref(float lo, float hi) {
+  uint32_t a = __float_as_uint(lo), b = __float_as_uint(hi);
+  a += (a >> 1) & 0x8000u;
+  b += (b >> 1) & 0x8000u;
+  return __byte_perm(a, b, 0x7632);  // {a.byte2, a.byte3, b.byte2, b.byte3}: the two upper halves
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(256, 4) chain_fast_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                            const float* __restrict__ r, uint2* __restrict__ out,
+                                                            int64_t rows, int64_t r_rows, float eps) {
+  constexpr int L = 1024 * VPT;
+  __shared__ float red[32];
+  const int t = threadIdx.x;
+  const int64_t copies = r_rows < rows ? rows / r_rows : 1;
+  const float invL = 1.0f / static_cast<float>(L);
+  float4 wv[VPT];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) wv[v] = *reinterpret_cast<const float4*>(w + (v * 256 + t) * 4);
+  for (int64_t rb = blockIdx.x; rb < rows; rb += gridDim.x) {
+    // rows that share a residual row are handled back to back (see row_kernel)
+    const int64_t row = copies > 1 ? (rb % copies) * r_rows + rb / copies : rb;
+    const int64_t rrow = copies > 1 ? rb / copies : (r_rows == rows ? rb : rb % r_rows);
+    const float4* xp = reinterpret_cast<const float4*>(x + row * L);
+    const float4* rp = reinterpret_cast<const float4*>(r + rrow * L);
+    float4 xv[VPT], rv[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) xv[v] = xp[v * 256 + t];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) rv[v] = rp[v * 256 + t];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      ss = fmaf(xv[v].x, xv[v].x, ss);
+      ss = fmaf(xv[v].y, xv[v].y, ss);
+      ss = fmaf(xv[v].z, xv[v].z, ss);
+      ss = fmaf(xv[v].w, xv[v].w, ss);
+    }
+    ss = group_sum<256>(ss, red, 0, t);
+    const float inv = 1.0f / sqrtf(ss * invL + eps);
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      xv[v].x = fmaf(xv[v].x * inv, wv[v].x, rv[v].x);
+      xv[v].y = fmaf(xv[v].y * inv, wv[v].y, rv[v].y);
+      xv[v].z = fmaf(xv[v].z * inv, wv[v].z, rv[v].z);
+      xv[v].w = fmaf(xv[v].w * inv, wv[v].w, rv[v].w);
+      m = fmaxf(m, fmaxf(fmaxf(xv[v].x, xv[v].y), fmaxf(xv[v].z, xv[v].w)));
+    }
+    m = group_max<256>(m, red, 0, t);
+    const float nm = -m * 1.4426950408889634f;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      xv[v].x = ex2_ftz(fmaf(xv[v].x, 1.4426950408889634f, nm));
+      xv[v].y = ex2_ftz(fmaf(xv[v].y, 1.4426950408889634f, nm));
+      xv[v].z = ex2_ftz(fmaf(xv[v].z, 1.4426950408889634f, nm));
+      xv[v].w = ex2_ftz(fmaf(xv[v].w, 1.4426950408889634f, nm));
+      s0 += xv[v].x + xv[v].y;
+      s1 += xv[v].z + xv[v].w;
+    }
+    const float isum = 1.0f / group_sum<256>(s0 + s1, red, 0, t);
+    uint2* op = out + row * (L / 4);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      uint2 o;
+      o.x = bf16_pair_ref(xv[v].x * isum, xv[v].y * isum);
+      o.y = bf16_pair_ref(xv[v].z * isum, xv[v].w * isum);
+      op[v * 256 + t] = o;
+    }
   }
 }
 
@@ -874,6 +964,18 @@ int ytcuda_rmsnorm_add_softmax_cast(int dt_out, const float* x, const float* wei
   p.x_rs = hidden; p.y_rs = hidden;
   p.r_rows = residual_batched ? batch * rows : rows;
   p.eps = eps; p.dt_in = YTC_F32; p.dt_out = dt_out; p.dt_w = YTC_F32;
+  if (dt_out == YTC_BF16 && (hidden == 1024 || hidden == 2048 || hidden == 4096)) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 4 * 4;
+    const unsigned grid = static_cast<unsigned>(p.rows < cap ? p.rows : cap);
+    uint2* o2 = static_cast<uint2*>(out);
+    if (hidden == 4096) chain_fast_kernel<4><<<grid, 256, 0, st>>>(x, weight, residual, o2, p.rows, p.r_rows, eps);
+    else if (hidden == 2048) chain_fast_kernel<2><<<grid, 256, 0, st>>>(x, weight, residual, o2, p.rows, p.r_rows, eps);
+    else chain_fast_kernel<1><<<grid, 256, 0, st>>>(x, weight, residual, o2, p.rows, p.r_rows, eps);
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
+  }
   launch_row_op(OP_CHAIN, p, static_cast<cudaStream_t>(stream));
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
