@@ -277,7 +277,7 @@ def device_arm(args) -> None:
                     "frac": achieved / peaks["bf16_tflops"], "traffic": TRAFFIC_BYTES_PER_LAUNCH if BATCH == 64 else None,
                     "traffic_note": "ncu dram read+write of a batch-8 capture scaled to batch 64 (A and C x8, B once); "
                                     "see profiles/gemm_tc_kernel_bf16_config2.md",
-                    "kernel": "gemm_tc_kernel<256>", "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
+                    "kernel": "gemm_tc2_kernel (cta_group::2, 256x256 tile per CTA pair)", "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
                     "frac_of_sustained_peak": (achieved / peaks["bf16_tflops_sustained"]
                                                if peaks.get("bf16_tflops_sustained") else None),
                     "algorithmic_flops_per_launch": FLOPS_PER_STEP}

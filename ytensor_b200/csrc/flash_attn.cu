@@ -55,6 +55,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Packed pairs of fp32 (sm_100 f32x2 arithmetic) and the three-input maximum: they halve the instruction count of
+// the softmax inner loops, which share their issue slots with the MMA and TMA warps.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int D>
 struct FaSmem {
   static constexpr int TILE_BYTES = FA_BM * D * 2;  // one Q / K / V tile
@@ -307,13 +333,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           uint32_t r[64];
           tmem_ld_32x32b_x64(ts + c0, r);
           tmem_ld_wait();
-          if (full && pos) {  // the common tile: one max per element
+          if (full && pos) {  // the common tile: one three-input max per two elements
 #pragma unroll
-            for (int e = 0; e < 64; e += 4) {
-              a0 = fmaxf(a0, __uint_as_float(r[e]));
-              a1 = fmaxf(a1, __uint_as_float(r[e + 1]));
-              a2 = fmaxf(a2, __uint_as_float(r[e + 2]));
-              a3 = fmaxf(a3, __uint_as_float(r[e + 3]));
+            for (int e = 0; e < 64; e += 8) {
+              a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+              a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+              a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+              a3 = fmax3(a3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
             }
           } else {
             const int cc = full ? 64 : cl - c0;
@@ -390,14 +416,20 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           tmem_ld_wait();
           uint32_t pk[32];
           if (full) {
+            const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
+            uint64_t lacc = f2_pack(0.f, 0.f);
 #pragma unroll
             for (int e = 0; e < 64; e += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_m));
-              l0 += p0;
-              l1 += p1;
+              float t0, t1;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc2, nm2), t0, t1);
+              const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+              lacc = f2_add(lacc, f2_pack(p0, p1));
               pk[e >> 1] = pack2(p0, p1);
             }
+            float la, lb;
+            f2_unpack(lacc, la, lb);
+            l0 += la;
+            l1 += lb;
           } else {
             const int cc = cl - c0;
 #pragma unroll
