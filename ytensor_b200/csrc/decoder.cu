@@ -52,7 +52,8 @@ __global__ void __launch_bounds__(256) embedding_kernel(const uint16_t* table, c
 // order (bit-stable from run to run). Memory-bound on W for small M; FFMA-bound as M grows.
 constexpr int SK_WARPS = 4;
 constexpr int SK_ROWS = 2;
-constexpr int SK_KC = 512;
+constexpr int SK_KC = 1024;
+constexpr int SK_UNROLL = 4;  // 256-column trips fetched together per lane
 
 template <int MT>
 __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(const float* __restrict__ x, int64_t x_rs,
@@ -78,30 +79,41 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(const floa
       *reinterpret_cast<float4*>(&xs[m * SK_KC + c]) = v;
     }
     __syncthreads();
-    for (int kk = lane * 8; kk < kc; kk += 256) {
-      uint4 w[SK_ROWS];
+    // SK_UNROLL trips of 256 columns are fetched together: several 128-bit loads per lane are in flight at once,
+    // which is what hides the HBM latency when a row is only a few KB long
+    for (int kk0 = lane * 8; kk0 < kc; kk0 += 256 * SK_UNROLL) {
+      uint4 w[SK_UNROLL][SK_ROWS];
 #pragma unroll
-      for (int r = 0; r < SK_ROWS; ++r) {
-        const int n = n0 + r;
-        w[r] = (n < N) ? *reinterpret_cast<const uint4*>(W + static_cast<int64_t>(n) * w_rs + k0 + kk)
-                       : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        const float4 xa = *reinterpret_cast<const float4*>(&xs[m * SK_KC + kk]);
-        const float4 xb = *reinterpret_cast<const float4*>(&xs[m * SK_KC + kk + 4]);
+      for (int u = 0; u < SK_UNROLL; ++u) {
+        const int kk = kk0 + u * 256;
 #pragma unroll
         for (int r = 0; r < SK_ROWS; ++r) {
-          float a = acc[r][m];
-          a = fmaf(xa.x, __uint_as_float(w[r].x << 16), a);
-          a = fmaf(xa.y, __uint_as_float(w[r].x & 0xFFFF0000u), a);
-          a = fmaf(xa.z, __uint_as_float(w[r].y << 16), a);
-          a = fmaf(xa.w, __uint_as_float(w[r].y & 0xFFFF0000u), a);
-          a = fmaf(xb.x, __uint_as_float(w[r].z << 16), a);
-          a = fmaf(xb.y, __uint_as_float(w[r].z & 0xFFFF0000u), a);
-          a = fmaf(xb.z, __uint_as_float(w[r].w << 16), a);
-          a = fmaf(xb.w, __uint_as_float(w[r].w & 0xFFFF0000u), a);
-          acc[r][m] = a;
+          const int n = n0 + r;
+          w[u][r] = (n < N && kk < kc) ? *reinterpret_cast<const uint4*>(W + static_cast<int64_t>(n) * w_rs + k0 + kk)
+                                       : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < SK_UNROLL; ++u) {
+        const int kk = kk0 + u * 256;
+        if (kk >= kc) break;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const float4 xa = *reinterpret_cast<const float4*>(&xs[m * SK_KC + kk]);
+          const float4 xb = *reinterpret_cast<const float4*>(&xs[m * SK_KC + kk + 4]);
+#pragma unroll
+          for (int r = 0; r < SK_ROWS; ++r) {
+            float a = acc[r][m];
+            a = fmaf(xa.x, __uint_as_float(w[u][r].x << 16), a);
+            a = fmaf(xa.y, __uint_as_float(w[u][r].x & 0xFFFF0000u), a);
+            a = fmaf(xa.z, __uint_as_float(w[u][r].y << 16), a);
+            a = fmaf(xa.w, __uint_as_float(w[u][r].y & 0xFFFF0000u), a);
+            a = fmaf(xb.x, __uint_as_float(w[u][r].z << 16), a);
+            a = fmaf(xb.y, __uint_as_float(w[u][r].z & 0xFFFF0000u), a);
+            a = fmaf(xb.z, __uint_as_float(w[u][r].w << 16), a);
+            a = fmaf(xb.w, __uint_as_float(w[u][r].w & 0xFFFF0000u), a);
+            acc[r][m] = a;
+          }
         }
       }
     }

@@ -625,6 +625,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(const AttnSimtParams p) 
 constexpr int DEC_MAX_ROWS = 8;   // groups * q_len handled per CTA
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_MAX_VEC = 2;    // float4 per lane per row: head / value dim up to 256
+constexpr int DEC_KU = 4;         // keys fetched together per warp trip
 
 struct AttnDecodeParams {
   AttnSimtParams a;
@@ -671,56 +672,66 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnD
   const int k_begin = split * dp.keys_per_split;
   int k_end = k_begin + dp.keys_per_split;
   if (k_end > p.kv_len) k_end = p.kv_len;
-  for (int key = k_begin + warp; key < k_end; key += DEC_WARPS) {
-    float4 kv[DEC_MAX_VEC], vv[DEC_MAX_VEC];
+  // DEC_KU keys per trip: all their K / V rows are requested before the first one is used
+  for (int key0 = k_begin + warp; key0 < k_end; key0 += DEC_WARPS * DEC_KU) {
+    float4 kv[DEC_KU][DEC_MAX_VEC], vv[DEC_KU][DEC_MAX_VEC];
 #pragma unroll
-    for (int j = 0; j < DEC_MAX_VEC; ++j) {
-      kv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      vv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      const int c = j * 128 + lane * 4;
-      if (j < nvq && c < p.d) {
-        const int64_t o = ko + static_cast<int64_t>(key) * p.k_sr + c;
-        if (p.dt == YTC_F32) kv[j] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.K) + o);
-        else kv[j] = make_float4(load_as_f32(p.K, o, p.dt), load_as_f32(p.K, o + 1, p.dt), load_as_f32(p.K, o + 2, p.dt),
-                                 load_as_f32(p.K, o + 3, p.dt));
-      }
-      if (j < nvv && c < p.dv) {
-        const int64_t o = vo + static_cast<int64_t>(key) * p.v_sr + c;
-        if (p.dt == YTC_F32) vv[j] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.V) + o);
-        else vv[j] = make_float4(load_as_f32(p.V, o, p.dt), load_as_f32(p.V, o + 1, p.dt), load_as_f32(p.V, o + 2, p.dt),
-                                 load_as_f32(p.V, o + 3, p.dt));
+    for (int u = 0; u < DEC_KU; ++u) {
+      const int key = key0 + u * DEC_WARPS;
+#pragma unroll
+      for (int j = 0; j < DEC_MAX_VEC; ++j) {
+        kv[u][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        vv[u][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int c = j * 128 + lane * 4;
+        if (key < k_end && j < nvq && c < p.d) {
+          const int64_t o = ko + static_cast<int64_t>(key) * p.k_sr + c;
+          if (p.dt == YTC_F32) kv[u][j] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.K) + o);
+          else kv[u][j] = make_float4(load_as_f32(p.K, o, p.dt), load_as_f32(p.K, o + 1, p.dt),
+                                      load_as_f32(p.K, o + 2, p.dt), load_as_f32(p.K, o + 3, p.dt));
+        }
+        if (key < k_end && j < nvv && c < p.dv) {
+          const int64_t o = vo + static_cast<int64_t>(key) * p.v_sr + c;
+          if (p.dt == YTC_F32) vv[u][j] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.V) + o);
+          else vv[u][j] = make_float4(load_as_f32(p.V, o, p.dt), load_as_f32(p.V, o + 1, p.dt),
+                                      load_as_f32(p.V, o + 2, p.dt), load_as_f32(p.V, o + 3, p.dt));
+        }
       }
     }
 #pragma unroll
-    for (int r = 0; r < DEC_MAX_ROWS; ++r) {
-      if (r >= R) break;
-      const int qi = r % p.q_len;
-      bool vis = !p.causal || key <= qi + p.causal_off;
-      if (vis && p.mask) vis = p.mask[static_cast<int64_t>(qi) * p.mask_rs + key] != 0;
-      if (!vis) continue;  // uniform over the warp
-      float dot = 0.f;
+    for (int u = 0; u < DEC_KU; ++u) {
+      const int key = key0 + u * DEC_WARPS;
+      if (key >= k_end) break;
 #pragma unroll
-      for (int j = 0; j < DEC_MAX_VEC; ++j) {
-        dot = fmaf(q[r][j].x, kv[j].x, dot);
-        dot = fmaf(q[r][j].y, kv[j].y, dot);
-        dot = fmaf(q[r][j].z, kv[j].z, dot);
-        dot = fmaf(q[r][j].w, kv[j].w, dot);
-      }
+      for (int r = 0; r < DEC_MAX_ROWS; ++r) {
+        if (r >= R) break;
+        const int qi = r % p.q_len;
+        bool vis = !p.causal || key <= qi + p.causal_off;
+        if (vis && p.mask) vis = p.mask[static_cast<int64_t>(qi) * p.mask_rs + key] != 0;
+        if (!vis) continue;  // uniform over the warp
+        float dot = 0.f;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      float sc = dot * p.scale;
-      if (p.bias) sc += p.bias[static_cast<int64_t>(qi) * p.bias_rs + key * p.bias_cs];
-      const float m_new = fmaxf(m_run[r], sc);
-      const float alpha = __expf(m_run[r] - m_new);  // 0 on the first visible key (m_run = -inf)
-      const float pr = __expf(sc - m_new);
-      l_run[r] = l_run[r] * alpha + pr;
-      m_run[r] = m_new;
+        for (int j = 0; j < DEC_MAX_VEC; ++j) {
+          dot = fmaf(q[r][j].x, kv[u][j].x, dot);
+          dot = fmaf(q[r][j].y, kv[u][j].y, dot);
+          dot = fmaf(q[r][j].z, kv[u][j].z, dot);
+          dot = fmaf(q[r][j].w, kv[u][j].w, dot);
+        }
 #pragma unroll
-      for (int j = 0; j < DEC_MAX_VEC; ++j) {
-        acc[r][j].x = fmaf(pr, vv[j].x, acc[r][j].x * alpha);
-        acc[r][j].y = fmaf(pr, vv[j].y, acc[r][j].y * alpha);
-        acc[r][j].z = fmaf(pr, vv[j].z, acc[r][j].z * alpha);
-        acc[r][j].w = fmaf(pr, vv[j].w, acc[r][j].w * alpha);
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        float sc = dot * p.scale;
+        if (p.bias) sc += p.bias[static_cast<int64_t>(qi) * p.bias_rs + key * p.bias_cs];
+        const float m_new = fmaxf(m_run[r], sc);
+        const float alpha = __expf(m_run[r] - m_new);  // 0 on the first visible key (m_run = -inf)
+        const float pr = __expf(sc - m_new);
+        l_run[r] = l_run[r] * alpha + pr;
+        m_run[r] = m_new;
+#pragma unroll
+        for (int j = 0; j < DEC_MAX_VEC; ++j) {
+          acc[r][j].x = fmaf(pr, vv[u][j].x, acc[r][j].x * alpha);
+          acc[r][j].y = fmaf(pr, vv[u][j].y, acc[r][j].y * alpha);
+          acc[r][j].z = fmaf(pr, vv[u][j].z, acc[r][j].z * alpha);
+          acc[r][j].w = fmaf(pr, vv[u][j].w, acc[r][j].w * alpha);
+        }
       }
     }
   }
@@ -809,10 +820,25 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(const AttnSimtParams p) 
   const int64_t ko = b * p.k_sb + kvh * p.k_sh, vo = b * p.v_sb + kvh * p.v_sh;
   (void)heads;
   // stage Q (zero-padded to TL_D columns and TL_BM rows)
-  for (int i = tid; i < TL_BM * TL_D; i += 128) {
-    const int r = i / TL_D, c = i - r * TL_D;
-    Qs[r][c] = (row0 + r < p.q_len && c < p.d)
-                   ? load_as_f32(p.Q, qo + static_cast<int64_t>(row0 + r) * p.q_sr + c, p.dt) : 0.f;
+  // fp32 operands with 16-byte aligned rows are staged with 128-bit loads; anything else element by element
+  const bool vec = p.dt == YTC_F32 && p.d % 4 == 0 && p.dv % 4 == 0 && p.q_sr % 4 == 0 && p.k_sr % 4 == 0 &&
+                   p.v_sr % 4 == 0 && p.q_sh % 4 == 0 && p.k_sh % 4 == 0 && p.v_sh % 4 == 0 && p.q_sb % 4 == 0 &&
+                   p.k_sb % 4 == 0 && p.v_sb % 4 == 0 && (reinterpret_cast<uint64_t>(p.Q) & 15) == 0 &&
+                   (reinterpret_cast<uint64_t>(p.K) & 15) == 0 && (reinterpret_cast<uint64_t>(p.V) & 15) == 0;
+  if (vec) {
+    const float* Qf = static_cast<const float*>(p.Q);
+    for (int i = tid; i < TL_BM * (TL_D / 4); i += 128) {
+      const int r = i >> 5, c = (i & 31) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row0 + r < p.q_len && c < p.d) v = *reinterpret_cast<const float4*>(Qf + qo + static_cast<int64_t>(row0 + r) * p.q_sr + c);
+      *reinterpret_cast<float4*>(&Qs[r][c]) = v;
+    }
+  } else {
+    for (int i = tid; i < TL_BM * TL_D; i += 128) {
+      const int r = i / TL_D, c = i - r * TL_D;
+      Qs[r][c] = (row0 + r < p.q_len && c < p.d)
+                     ? load_as_f32(p.Q, qo + static_cast<int64_t>(row0 + r) * p.q_sr + c, p.dt) : 0.f;
+    }
   }
   float acc[32];
 #pragma unroll
@@ -827,11 +853,34 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(const AttnSimtParams p) 
                                        : -1;
   for (int k0 = 0; k0 <= last; k0 += TL_BN) {
     __syncthreads();
-    for (int i = tid; i < TL_BN * TL_D; i += 128) {
-      const int r = i / TL_D, c = i - r * TL_D;
-      const bool in = k0 + r < p.kv_len;
-      Ks[r][c] = (in && c < p.d) ? load_as_f32(p.K, ko + static_cast<int64_t>(k0 + r) * p.k_sr + c, p.dt) : 0.f;
-      Vs[r][c] = (in && c < p.dv) ? load_as_f32(p.V, vo + static_cast<int64_t>(k0 + r) * p.v_sr + c, p.dt) : 0.f;
+    if (vec) {
+      const float* Kf = static_cast<const float*>(p.K);
+      const float* Vf = static_cast<const float*>(p.V);
+      float4 kq[8], vq[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 128;
+        const int r = i >> 5, c = (i & 31) * 4;
+        const bool in = k0 + r < p.kv_len;
+        kq[u] = (in && c < p.d) ? *reinterpret_cast<const float4*>(Kf + ko + static_cast<int64_t>(k0 + r) * p.k_sr + c)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+        vq[u] = (in && c < p.dv) ? *reinterpret_cast<const float4*>(Vf + vo + static_cast<int64_t>(k0 + r) * p.v_sr + c)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 128;
+        const int r = i >> 5, c = (i & 31) * 4;
+        *reinterpret_cast<float4*>(&Ks[r][c]) = kq[u];
+        *reinterpret_cast<float4*>(&Vs[r][c]) = vq[u];
+      }
+    } else {
+      for (int i = tid; i < TL_BN * TL_D; i += 128) {
+        const int r = i / TL_D, c = i - r * TL_D;
+        const bool in = k0 + r < p.kv_len;
+        Ks[r][c] = (in && c < p.d) ? load_as_f32(p.K, ko + static_cast<int64_t>(k0 + r) * p.k_sr + c, p.dt) : 0.f;
+        Vs[r][c] = (in && c < p.dv) ? load_as_f32(p.V, vo + static_cast<int64_t>(k0 + r) * p.v_sr + c, p.dt) : 0.f;
+      }
     }
     __syncthreads();
     float sc[8];
@@ -1060,7 +1109,7 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
     dp.a = p;
     const int bk = batch * kv_heads;
     int splits = (2 * sm_count() + bk - 1) / bk;
-    const int max_splits = (kv_len + 63) / 64;
+    const int max_splits = (kv_len + 31) / 32;
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     dp.keys_per_split = (kv_len + splits - 1) / splits;
