@@ -43,7 +43,10 @@ struct FlashParams {
   float scale_log2;          // scale * log2(e)
   int is_bf16;
   int pair_heads;            // 1: the two tiles are two heads of one group; 0: two neighbouring row blocks
-  int row_blocks;            // query row blocks per CTA column (in units of one or two tiles, see kernel)
+  int row_blocks;            // query row blocks (of one tile with head pairs, of two tiles otherwise)
+  int head_slots;            // head pairs (pair_heads) or heads
+  int items_per_row_block;   // head_slots * batch
+  int n_items;               // row_blocks * items_per_row_block
   uint32_t idesc_s, idesc_pv;
   int* status;
 };
@@ -87,8 +90,8 @@ struct FaSmem {
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = 2 * TILE_BYTES;
   static constexpr int BAR_OFF = KV_OFF + FA_STAGES * 2 * TILE_BYTES;
-  // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full[2], o_ready[2], tmem slot, abort
-  static constexpr int NBAR = 1 + 3 * FA_STAGES + 6;
+  // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full[2], o_ready[2], q_free, o_free[2], tmem slot, abort
+  static constexpr int NBAR = 1 + 3 * FA_STAGES + 6 + 3;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -99,6 +102,51 @@ __device__ __forceinline__ void fa_load_tile(uint8_t* dst, const CUtensorMap* m,
                                              int batch) {
 #pragma unroll
   for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * (FA_BM * 128), m, bar, c * 64, row, head, batch);
+}
+
+// Work item = one pair of query tiles (see the file header). The CTAs are persistent: CTA c handles items c,
+// c + gridDim.x, ... of a list sorted by decreasing length (long causal row blocks first), so that the Q load and the
+// first K/V loads of the next item, and the S MMAs of its first tiles, overlap the last softmax, P.V and the epilogue
+// of the current one.
+struct FaItem {
+  int q_head[2], q_row0[2], kv_head, b;
+  bool tile_on[2];
+  int n_tiles[2], n_max;
+};
+
+__device__ __forceinline__ FaItem fa_decode_item(const FlashParams& p, int w) {
+  FaItem it;
+  const int per_rb = p.items_per_row_block;
+  const int rb = p.row_blocks - 1 - w / per_rb;  // last row block first
+  const int rest = w - (w / per_rb) * per_rb;
+  const int hsel = rest % p.head_slots;
+  it.b = rest / p.head_slots;
+  if (p.pair_heads) {
+    const int heads = p.kv_heads * p.groups;
+    it.q_head[0] = hsel * 2;
+    it.q_head[1] = hsel * 2 + 1;
+    if (it.q_head[1] >= heads) it.q_head[1] = it.q_head[0];
+    it.q_row0[0] = it.q_row0[1] = rb * FA_BM;
+    it.kv_head = it.q_head[0] / p.groups;
+  } else {
+    it.q_head[0] = it.q_head[1] = hsel;
+    it.q_row0[0] = rb * 2 * FA_BM;
+    it.q_row0[1] = rb * 2 * FA_BM + FA_BM;
+    it.kv_head = hsel / p.groups;
+  }
+  it.tile_on[0] = it.q_row0[0] < p.q_len;
+  it.tile_on[1] = it.q_row0[1] < p.q_len && !(p.pair_heads && it.q_head[1] == it.q_head[0]);
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    int last_key = p.kv_len - 1;
+    if (p.causal) {
+      const int lim = it.q_row0[t] + FA_BM - 1 + p.causal_off;
+      if (lim < last_key) last_key = lim;
+    }
+    it.n_tiles[t] = (!it.tile_on[t] || last_key < 0) ? 0 : last_key / FA_BN + 1;
+  }
+  it.n_max = it.n_tiles[0] > it.n_tiles[1] ? it.n_tiles[0] : it.n_tiles[1];
+  return it;
 }
 
 template <int D>
@@ -117,47 +165,16 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   uint64_t* s_full = kv_empty + FA_STAGES;
   uint64_t* p_full = s_full + 2;
   uint64_t* o_ready = p_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 2);
+  uint64_t* q_free = o_ready + 2;   // the MMAs no longer read the Q tiles of the current item
+  uint64_t* o_free = q_free + 1;    // [2] the epilogue has read O_t
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // ---- which two query tiles this CTA owns ---------------------------------------------------
-  // blockIdx.x walks row blocks from the LAST one down (the longest causal rows start first).
-  const int rb = p.row_blocks - 1 - static_cast<int>(blockIdx.x);
-  const int hsel = blockIdx.y;  // head pair (pair_heads) or head
-  const int b = blockIdx.z;
-  int q_head[2], q_row0[2], kv_head;
-  if (p.pair_heads) {
-    const int heads = p.kv_heads * p.groups;
-    q_head[0] = hsel * 2;
-    q_head[1] = hsel * 2 + 1;
-    if (q_head[1] >= heads) q_head[1] = q_head[0];
-    q_row0[0] = q_row0[1] = rb * FA_BM;
-    kv_head = q_head[0] / p.groups;
-  } else {
-    q_head[0] = q_head[1] = hsel;
-    q_row0[0] = rb * 2 * FA_BM;
-    q_row0[1] = rb * 2 * FA_BM + FA_BM;
-    kv_head = hsel / p.groups;
-  }
-  const bool tile_on[2] = {q_row0[0] < p.q_len,
-                           q_row0[1] < p.q_len && !(p.pair_heads && q_head[1] == q_head[0])};
-  // number of K/V tiles each query tile needs
-  int n_tiles[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    int last_key = p.kv_len - 1;
-    if (p.causal) {
-      const int lim = q_row0[t] + FA_BM - 1 + p.causal_off;
-      if (lim < last_key) last_key = lim;
-    }
-    n_tiles[t] = (!tile_on[t] || last_key < 0) ? 0 : last_key / FA_BN + 1;
-  }
-  const int n_max = n_tiles[0] > n_tiles[1] ? n_tiles[0] : n_tiles[1];
-
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_free, 1);
     for (int s = 0; s < FA_STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
@@ -167,6 +184,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       mbar_init(&s_full[t], 1);
       mbar_init(&p_full[t], 4);  // one arrival per softmax warp
       mbar_init(&o_ready[t], 1);
+      mbar_init(&o_free[t], 4);
     }
     *abort_word = 0;
     fence_mbar_init();
@@ -189,42 +207,51 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_max > 0) {
-      int n_q = 0;
-      for (int t = 0; t < 2; ++t) n_q += tile_on[t] ? 1 : 0;
-      mbar_expect_tx(q_full, static_cast<uint32_t>(n_q) * S::TILE_BYTES);
-      for (int t = 0; t < 2; ++t)
-        if (tile_on[t]) fa_load_tile<D>(smem + S::Q_OFF + t * S::TILE_BYTES, &tmQ, q_full, q_row0[t], q_head[t], b);
-      uint32_t phase = 0;
-      int issued = 0;
+    if (lane == 0) {
+      int kv_cnt = 0;  // K/V tiles loaded so far: stage kv_cnt % 2, fill number kv_cnt / 2
       bool ok = true;
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j % FA_STAGES;
-        if (!mbar_wait(&kv_empty[s], phase ^ 1u, abort_word)) {
-          ok = false;
-          break;
+      int n_item = 0;
+      for (int w = blockIdx.x; ok && w < p.n_items; w += gridDim.x) {
+        const FaItem it = fa_decode_item(p, w);
+        if (it.n_max == 0) continue;  // nothing visible: the softmax warpgroups write zeros on their own
+        // (n_item counts only items with work; items without work touch no barrier in any role)
+        if (n_item > 0 && !mbar_wait(q_free, static_cast<uint32_t>((n_item - 1) & 1), abort_word)) break;
+        int n_q = 0;
+        for (int t = 0; t < 2; ++t) n_q += it.tile_on[t] ? 1 : 0;
+        mbar_expect_tx(q_full, static_cast<uint32_t>(n_q) * S::TILE_BYTES);
+        for (int t = 0; t < 2; ++t)
+          if (it.tile_on[t])
+            fa_load_tile<D>(smem + S::Q_OFF + t * S::TILE_BYTES, &tmQ, q_full, it.q_row0[t], it.q_head[t], it.b);
+        for (int j = 0; j < it.n_max; ++j, ++kv_cnt) {
+          const int s = kv_cnt % FA_STAGES;
+          if (!mbar_wait(&kv_empty[s], static_cast<uint32_t>(((kv_cnt / FA_STAGES) & 1) ^ 1), abort_word)) {
+            ok = false;
+            break;
+          }
+          uint8_t* ks = smem + S::KV_OFF + s * 2 * S::TILE_BYTES;
+          uint8_t* vs = ks + S::TILE_BYTES;
+          mbar_expect_tx(&k_full[s], S::TILE_BYTES);
+          fa_load_tile<D>(ks, &tmK, &k_full[s], j * FA_BN, it.kv_head, it.b);
+          mbar_expect_tx(&v_full[s], S::TILE_BYTES);
+          fa_load_tile<D>(vs, &tmV, &v_full[s], j * FA_BN, it.kv_head, it.b);
         }
-        uint8_t* ks = smem + S::KV_OFF + s * 2 * S::TILE_BYTES;
-        uint8_t* vs = ks + S::TILE_BYTES;
-        mbar_expect_tx(&k_full[s], S::TILE_BYTES);
-        fa_load_tile<D>(ks, &tmK, &k_full[s], j * FA_BN, kv_head, b);
-        mbar_expect_tx(&v_full[s], S::TILE_BYTES);
-        fa_load_tile<D>(vs, &tmV, &v_full[s], j * FA_BN, kv_head, b);
-        ++issued;
-        if (s == FA_STAGES - 1) phase ^= 1u;
+        ++n_item;
       }
       if (!ok) {
         // bounded drain of the copies still in flight
         const long long t0 = clock64();
-        for (int s = 0; s < FA_STAGES && s < issued; ++s)
+        for (int s = 0; s < FA_STAGES && s < kv_cnt; ++s)
           while (!mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1) && clock64() - t0 < 20000000ll) {
           }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_max > 0) {
+    if (lane == 0) {
       const uint32_t q_base = smem_u32(smem + S::Q_OFF);
+      int kv_cnt = 0;
+      int p_cnt[2] = {0, 0};    // P tiles consumed so far per query tile (phase of p_full)
+      int e_cnt[2] = {0, 0};    // items finished per query tile (phase of o_free)
       // S_t = Q_t . K^T : both operands K-major, D/16 steps; 64-element chunks are FA_BM*128 bytes apart
       auto issue_s = [&](int t, int stage) {
         const uint32_t qa = q_base + t * S::TILE_BYTES;
@@ -247,42 +274,58 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                         (accumulate || kk != 0) ? 1u : 0u);
         tc_commit(&o_ready[t]);
       };
-      bool ok = mbar_wait(q_full, 0, abort_word);
-      uint32_t kv_phase = 0;
-      if (ok) ok = mbar_wait(&k_full[0], 0, abort_word);
-      if (ok) {
+      bool ok = true;
+      int n_item = 0;
+      for (int w = blockIdx.x; ok && w < p.n_items; w += gridDim.x) {
+        const FaItem it = fa_decode_item(p, w);
+        if (it.n_max == 0) continue;
+        if (!mbar_wait(q_full, static_cast<uint32_t>(n_item & 1), abort_word)) break;
+        if (!mbar_wait(&k_full[kv_cnt % FA_STAGES], static_cast<uint32_t>((kv_cnt / FA_STAGES) & 1), abort_word)) break;
         tc_fence_after();
-        if (n_tiles[0] > 0) issue_s(0, 0);
-        if (n_tiles[1] > 0) issue_s(1, 0);
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j % FA_STAGES;
-        const int sn = (j + 1) % FA_STAGES;
-        const uint32_t next_phase = (sn == 0) ? (kv_phase ^ 1u) : kv_phase;
-        const uint32_t pj = static_cast<uint32_t>(j & 1);
-        if (!mbar_wait(&v_full[s], kv_phase, abort_word)) break;
+        if (it.n_tiles[0] > 0) issue_s(0, kv_cnt % FA_STAGES);
+        if (it.n_tiles[1] > 0) issue_s(1, kv_cnt % FA_STAGES);
+        if (it.n_max == 1) tc_commit(q_free);
+        for (int j = 0; j < it.n_max && ok; ++j, ++kv_cnt) {
+          const int s = kv_cnt % FA_STAGES;
+          const int sn = (kv_cnt + 1) % FA_STAGES;
+          const uint32_t ph = static_cast<uint32_t>((kv_cnt / FA_STAGES) & 1);
+          const uint32_t ph_next = static_cast<uint32_t>(((kv_cnt + 1) / FA_STAGES) & 1);
+          if (!mbar_wait(&v_full[s], ph, abort_word)) {
+            ok = false;
+            break;
+          }
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (j < n_tiles[t]) {
-            if (!mbar_wait(&p_full[t], pj, abort_word)) {
-              ok = false;
-              break;
+          for (int t = 0; t < 2; ++t) {
+            if (j < it.n_tiles[t]) {
+              if (!mbar_wait(&p_full[t], static_cast<uint32_t>(p_cnt[t] & 1), abort_word)) {
+                ok = false;
+                break;
+              }
+              ++p_cnt[t];
+              if (j == 0 && e_cnt[t] > 0 &&
+                  !mbar_wait(&o_free[t], static_cast<uint32_t>((e_cnt[t] - 1) & 1), abort_word)) {
+                ok = false;  // the first P.V of an item overwrites O_t: the previous epilogue must have read it
+                break;
+              }
+              tc_fence_after();
+              issue_pv(t, s, j > 0);
             }
-            tc_fence_after();
-            issue_pv(t, s, j > 0);
-          }
-          if (j + 1 < n_tiles[t]) {
-            if (!mbar_wait(&k_full[sn], next_phase, abort_word)) {
-              ok = false;
-              break;
+            if (j + 1 < it.n_tiles[t]) {
+              if (!mbar_wait(&k_full[sn], ph_next, abort_word)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              issue_s(t, sn);
             }
-            tc_fence_after();
-            issue_s(t, sn);
           }
+          if (!ok) break;
+          if (j + 2 == it.n_max) tc_commit(q_free);  // the last S MMAs of this item have been issued
+          tc_commit(&kv_empty[s]);  // every MMA that read stage s has been issued before this point
         }
-        if (!ok) break;
-        tc_commit(&kv_empty[s]);  // every MMA that read stage s has been issued before this point
-        if (s == FA_STAGES - 1) kv_phase ^= 1u;
+        for (int t = 0; t < 2; ++t)
+          if (it.n_tiles[t] > 0) ++e_cnt[t];
+        ++n_item;
       }
     }
   } else if (warp >= 4) {
@@ -290,229 +333,247 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     const int t = (warp - 4) >> 2;
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
-    const int row = q_row0[t] + row_in_tile;  // global query row
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const uint32_t ts = t_s[t] + lane_sel, to = t_o[t] + lane_sel;
-    const int nt = n_tiles[t];
-    float m_run = -CUDART_INF_F;  // running maximum, log2 domain
-    float l_run = 0.f;
-    bool ok = true;
     const bool elementwise_mask = (p.mask != nullptr) || (p.bias != nullptr);
+    int s_base = 0;  // S tiles (= P tiles = P.V products) of this query tile in earlier items
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < p.n_items; w += gridDim.x) {
+      const FaItem it = fa_decode_item(p, w);
+      const int* q_row0 = it.q_row0;
+      const int* q_head = it.q_head;
+      const bool* tile_on = it.tile_on;
+      const int b = it.b;
+      const int row = q_row0[t] + row_in_tile;  // global query row
+      const int nt = (it.n_max == 0) ? 0 : it.n_tiles[t];
+      const int o_base = s_base;
+      float m_run = -CUDART_INF_F;  // running maximum, log2 domain
+      float l_run = 0.f;
 
-    for (int j = 0; j < nt; ++j) {
-      if (!mbar_wait(&s_full[t], static_cast<uint32_t>(j & 1), abort_word)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const int key0 = j * FA_BN;
-      // Three kinds of tile: `full` (every key visible to every row), limited (visibility is "key <= per-row
-      // limit": causal diagonal, end of the keys, rows past q_len), general (bool mask or bias present).
-      int row_limit = (row < p.q_len) ? p.kv_len - 1 : -1;
-      if (p.causal && row + p.causal_off < row_limit) row_limit = row + p.causal_off;
-      const int cl = row_limit - key0;  // columns 0..cl of this tile are visible to this thread's row
-      const bool full = !elementwise_mask && (key0 + FA_BN <= p.kv_len) && (q_row0[t] + FA_BM <= p.q_len) &&
-                        (!p.causal || key0 + FA_BN - 1 <= q_row0[t] + p.causal_off);
-      auto score = [&](uint32_t raw, int c) -> float {  // general tiles only
-        float v = __uint_as_float(raw) * p.scale_log2;
-        const int key = key0 + c;
-        bool vis = c <= cl;
-        if (vis && p.mask) vis = p.mask[static_cast<int64_t>(row) * p.mask_rs + key] != 0;
-        if (vis && p.bias) v += p.bias[static_cast<int64_t>(row) * p.bias_rs + key * p.bias_cs] * FA_LOG2E;
-        return vis ? v : -CUDART_INF_F;
-      };
-      // pass 1: row maximum. Without mask / bias the maximum is taken over the raw scores (one instruction per
-      // element, two with the per-row limit) and scaled afterwards; a negative scale flips max into min.
-      float mx = -CUDART_INF_F;
-      if (!elementwise_mask) {
-        const bool pos = p.scale_log2 >= 0.f;
-        const float ident = pos ? -CUDART_INF_F : CUDART_INF_F;
-        float a0 = ident, a1 = ident, a2 = ident, a3 = ident;
+      for (int j = 0; j < nt; ++j) {
+        if (!mbar_wait(&s_full[t], static_cast<uint32_t>((s_base + j) & 1), abort_word)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int key0 = j * FA_BN;
+        // Three kinds of tile: `full` (every key visible to every row), limited (visibility is "key <= per-row
+        // limit": causal diagonal, end of the keys, rows past q_len), general (bool mask or bias present).
+        int row_limit = (row < p.q_len) ? p.kv_len - 1 : -1;
+        if (p.causal && row + p.causal_off < row_limit) row_limit = row + p.causal_off;
+        const int cl = row_limit - key0;  // columns 0..cl of this tile are visible to this thread's row
+        const bool full = !elementwise_mask && (key0 + FA_BN <= p.kv_len) && (q_row0[t] + FA_BM <= p.q_len) &&
+                          (!p.causal || key0 + FA_BN - 1 <= q_row0[t] + p.causal_off);
+        auto score = [&](uint32_t raw, int c) -> float {  // general tiles only
+          float v = __uint_as_float(raw) * p.scale_log2;
+          const int key = key0 + c;
+          bool vis = c <= cl;
+          if (vis && p.mask) vis = p.mask[static_cast<int64_t>(row) * p.mask_rs + key] != 0;
+          if (vis && p.bias) v += p.bias[static_cast<int64_t>(row) * p.bias_rs + key * p.bias_cs] * FA_LOG2E;
+          return vis ? v : -CUDART_INF_F;
+        };
+        // pass 1: row maximum. Without mask / bias the maximum is taken over the raw scores (one instruction per
+        // element, two with the per-row limit) and scaled afterwards; a negative scale flips max into min.
+        float mx = -CUDART_INF_F;
+        if (!elementwise_mask) {
+          const bool pos = p.scale_log2 >= 0.f;
+          const float ident = pos ? -CUDART_INF_F : CUDART_INF_F;
+          float a0 = ident, a1 = ident, a2 = ident, a3 = ident;
 #pragma unroll 1
-        for (int c0 = 0; c0 < FA_BN; c0 += 64) {
-          uint32_t r[64];
-          tmem_ld_32x32b_x64(ts + c0, r);
-          tmem_ld_wait();
-          if (full && pos) {  // the common tile: one three-input max per two elements
+          for (int c0 = 0; c0 < FA_BN; c0 += 64) {
+            uint32_t r[64];
+            tmem_ld_32x32b_x64(ts + c0, r);
+            tmem_ld_wait();
+            if (full && pos) {  // the common tile: one three-input max per two elements
 #pragma unroll
-            for (int e = 0; e < 64; e += 8) {
-              a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
-              a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
-              a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
-              a3 = fmax3(a3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
-            }
-          } else {
-            const int cc = full ? 64 : cl - c0;
+              for (int e = 0; e < 64; e += 8) {
+                a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+                a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+                a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+                a3 = fmax3(a3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+              }
+            } else {
+              const int cc = full ? 64 : cl - c0;
 #pragma unroll
-            for (int e = 0; e < 64; e += 4) {
-              const float v0 = (e <= cc) ? __uint_as_float(r[e]) : ident;
-              const float v1 = (e + 1 <= cc) ? __uint_as_float(r[e + 1]) : ident;
-              const float v2 = (e + 2 <= cc) ? __uint_as_float(r[e + 2]) : ident;
-              const float v3 = (e + 3 <= cc) ? __uint_as_float(r[e + 3]) : ident;
-              if (pos) {
-                a0 = fmaxf(a0, v0); a1 = fmaxf(a1, v1); a2 = fmaxf(a2, v2); a3 = fmaxf(a3, v3);
-              } else {
-                a0 = fminf(a0, v0); a1 = fminf(a1, v1); a2 = fminf(a2, v2); a3 = fminf(a3, v3);
+              for (int e = 0; e < 64; e += 4) {
+                const float v0 = (e <= cc) ? __uint_as_float(r[e]) : ident;
+                const float v1 = (e + 1 <= cc) ? __uint_as_float(r[e + 1]) : ident;
+                const float v2 = (e + 2 <= cc) ? __uint_as_float(r[e + 2]) : ident;
+                const float v3 = (e + 3 <= cc) ? __uint_as_float(r[e + 3]) : ident;
+                if (pos) {
+                  a0 = fmaxf(a0, v0); a1 = fmaxf(a1, v1); a2 = fmaxf(a2, v2); a3 = fmaxf(a3, v3);
+                } else {
+                  a0 = fminf(a0, v0); a1 = fminf(a1, v1); a2 = fminf(a2, v2); a3 = fminf(a3, v3);
+                }
               }
             }
           }
-        }
-        const float ext = pos ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : fminf(fminf(a0, a1), fminf(a2, a3));
-        mx = (ext == ident) ? -CUDART_INF_F : ext * p.scale_log2;
-      } else {
+          const float ext = pos ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : fminf(fminf(a0, a1), fminf(a2, a3));
+          mx = (ext == ident) ? -CUDART_INF_F : ext * p.scale_log2;
+        } else {
 #pragma unroll 1
-        for (int c0 = 0; c0 < FA_BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(ts + c0, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, score(r[e], c0 + e));
-        }
-      }
-      const float m_new = fmaxf(m_run, mx);
-      if (j == 0) {
-        m_run = m_new;
-      } else {
-        const bool grow = (m_new - m_run) > FA_RESCALE_THRESHOLD;  // also true when m_run is -inf and m_new finite
-        if (__any_sync(0xffffffffu, grow)) {
-          // O_t *= 2^(m_run - m_new) for this warp's 32 rows; needs the previous P.V to have landed
-          if (!mbar_wait(&o_ready[t], static_cast<uint32_t>((j - 1) & 1), abort_word)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const float alpha = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_run - m_new);  // m_run == -inf gives 0
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld_32x32b_x16(to + c0, r);
+          for (int c0 = 0; c0 < FA_BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(ts + c0, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-            tmem_st_32x32b_x16(to + c0, r);
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, score(r[e], c0 + e));
           }
-          l_run *= alpha;
+        }
+        const float m_new = fmaxf(m_run, mx);
+        if (j == 0) {
           m_run = m_new;
-        }
-      }
-      const float m_use = (m_run == -CUDART_INF_F) ? 0.f : m_run;
-      // pass 2: P = 2^(s - m), packed to 16 bits, written over the S columns already consumed.
-      // Without mask / bias: one FMA and one ex2.approx per element (plus a select on limited tiles).
-      float l0 = 0.f, l1 = 0.f;
-      const float neg_m = -m_use;
-      auto pack2 = [&](float p0, float p1) -> uint32_t {
-        if (p.is_bf16) {
-          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          return *reinterpret_cast<const uint32_t*>(&h);
-        }
-        const __half2 h = __floats2half2_rn(p0, p1);
-        return *reinterpret_cast<const uint32_t*>(&h);
-      };
-      if (!elementwise_mask) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < FA_BN; c0 += 64) {
-          uint32_t r[64];
-          tmem_ld_32x32b_x64(ts + c0, r);
-          tmem_ld_wait();
-          uint32_t pk[32];
-          if (full) {
-            const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
-            uint64_t lacc = f2_pack(0.f, 0.f);
-#pragma unroll
-            for (int e = 0; e < 64; e += 2) {
-              float t0, t1;
-              f2_unpack(f2_fma(f2_pack(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc2, nm2), t0, t1);
-              const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-              lacc = f2_add(lacc, f2_pack(p0, p1));
-              pk[e >> 1] = pack2(p0, p1);
+        } else {
+          const bool grow = (m_new - m_run) > FA_RESCALE_THRESHOLD;  // also true when m_run is -inf and m_new finite
+          if (__any_sync(0xffffffffu, grow)) {
+            // O_t *= 2^(m_run - m_new) for this warp's 32 rows; needs the previous P.V to have landed
+            if (!mbar_wait(&o_ready[t], static_cast<uint32_t>((o_base + j - 1) & 1), abort_word)) {
+              ok = false;
+              break;
             }
-            float la, lb;
-            f2_unpack(lacc, la, lb);
-            l0 += la;
-            l1 += lb;
-          } else {
-            const int cc = cl - c0;
+            tc_fence_after();
+            const float alpha = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_run - m_new);  // m_run == -inf gives 0
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 16) {
+              uint32_t r[16];
+              tmem_ld_32x32b_x16(to + c0, r);
+              tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 64; e += 2) {
-              float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
-              float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_m));
-              p0 = (e <= cc) ? p0 : 0.f;
-              p1 = (e + 1 <= cc) ? p1 : 0.f;
+              for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+              tmem_st_32x32b_x16(to + c0, r);
+            }
+            l_run *= alpha;
+            m_run = m_new;
+          }
+        }
+        const float m_use = (m_run == -CUDART_INF_F) ? 0.f : m_run;
+        // pass 2: P = 2^(s - m), packed to 16 bits, written over the S columns already consumed.
+        // Without mask / bias: one FMA and one ex2.approx per element (plus a select on limited tiles).
+        float l0 = 0.f, l1 = 0.f;
+        const float neg_m = -m_use;
+        auto pack2 = [&](float p0, float p1) -> uint32_t {
+          if (p.is_bf16) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            return *reinterpret_cast<const uint32_t*>(&h);
+          }
+          const __half2 h = __floats2half2_rn(p0, p1);
+          return *reinterpret_cast<const uint32_t*>(&h);
+        };
+        if (!elementwise_mask) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < FA_BN; c0 += 64) {
+            uint32_t r[64];
+            tmem_ld_32x32b_x64(ts + c0, r);
+            tmem_ld_wait();
+            uint32_t pk[32];
+            if (full) {
+              const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
+              uint64_t lacc = f2_pack(0.f, 0.f);
+#pragma unroll
+              for (int e = 0; e < 64; e += 2) {
+                float t0, t1;
+                f2_unpack(f2_fma(f2_pack(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc2, nm2), t0, t1);
+                const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+                lacc = f2_add(lacc, f2_pack(p0, p1));
+                pk[e >> 1] = pack2(p0, p1);
+              }
+              float la, lb;
+              f2_unpack(lacc, la, lb);
+              l0 += la;
+              l1 += lb;
+            } else {
+              const int cc = cl - c0;
+#pragma unroll
+              for (int e = 0; e < 64; e += 2) {
+                float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
+                float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_m));
+                p0 = (e <= cc) ? p0 : 0.f;
+                p1 = (e + 1 <= cc) ? p1 : 0.f;
+                l0 += p0;
+                l1 += p1;
+                pk[e >> 1] = pack2(p0, p1);
+              }
+            }
+            tmem_st_32x32b_x32(ts + (c0 >> 1), pk);
+          }
+        } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < FA_BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(ts + c0, r);
+            tmem_ld_wait();
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float p0 = fast_exp2(score(r[e], c0 + e) + neg_m);
+              const float p1 = fast_exp2(score(r[e + 1], c0 + e + 1) + neg_m);
               l0 += p0;
               l1 += p1;
               pk[e >> 1] = pack2(p0, p1);
             }
+            tmem_st_32x32b_x16(ts + (c0 >> 1), pk);
           }
-          tmem_st_32x32b_x32(ts + (c0 >> 1), pk);
         }
-      } else {
-#pragma unroll 1
-        for (int c0 = 0; c0 < FA_BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(ts + c0, r);
-          tmem_ld_wait();
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = fast_exp2(score(r[e], c0 + e) + neg_m);
-            const float p1 = fast_exp2(score(r[e + 1], c0 + e + 1) + neg_m);
-            l0 += p0;
-            l1 += p1;
-            pk[e >> 1] = pack2(p0, p1);
-          }
-          tmem_st_32x32b_x16(ts + (c0 >> 1), pk);
-        }
+        l_run += l0 + l1;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t]);
       }
-      l_run += l0 + l1;
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[t]);
-    }
+      if (!ok) break;
 
-    // ---- epilogue: O / l -> global -----------------------------------------------------------
-    if (tile_on[t]) {
-      bool have = false;
-      if (ok && nt > 0) {
-        have = mbar_wait(&o_ready[t], static_cast<uint32_t>((nt - 1) & 1), abort_word);
-        tc_fence_after();
-      }
-      const float inv = (have && l_run > 0.f) ? 1.0f / l_run : 0.f;
-      const bool row_ok = row < p.q_len;
-      char* orow = static_cast<char*>(p.O) +
-                   (static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(q_head[t]) * p.o_sh +
-                    static_cast<int64_t>(row) * p.o_sr) * 2;
-      const bool vec = ((reinterpret_cast<uint64_t>(orow) & 15u) == 0);
+      // ---- epilogue: O / l -> global -----------------------------------------------------------
+      if (tile_on[t]) {
+        bool have = false;
+        if (ok && nt > 0) {
+          have = mbar_wait(&o_ready[t], static_cast<uint32_t>((o_base + nt - 1) & 1), abort_word);
+          tc_fence_after();
+        }
+        const float inv = (have && l_run > 0.f) ? 1.0f / l_run : 0.f;
+        const bool row_ok = row < p.q_len;
+        char* orow = static_cast<char*>(p.O) +
+                     (static_cast<int64_t>(b) * p.o_sb + static_cast<int64_t>(q_head[t]) * p.o_sh +
+                      static_cast<int64_t>(row) * p.o_sr) * 2;
+        const bool vec = ((reinterpret_cast<uint64_t>(orow) & 15u) == 0);
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t r[32];
-        if (have) {
-          tmem_ld_32x32b_x32(to + c0, r);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = 0u;
-        }
-        if (row_ok) {
-          uint32_t w[16];
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float a0 = __uint_as_float(r[e]) * inv, a1 = __uint_as_float(r[e + 1]) * inv;
-            const uint16_t lo = p.is_bf16 ? f32_to_bf16_bits_ref(a0) : f32_to_f16_bits_ref(a0);
-            const uint16_t hi = p.is_bf16 ? f32_to_bf16_bits_ref(a1) : f32_to_f16_bits_ref(a1);
-            w[e >> 1] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-          }
-          if (vec) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) dst[v4] = make_uint4(w[4 * v4], w[4 * v4 + 1], w[4 * v4 + 2], w[4 * v4 + 3]);
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          if (have) {
+            tmem_ld_32x32b_x32(to + c0, r);
+            tmem_ld_wait();
           } else {
-            uint32_t* dst = reinterpret_cast<uint32_t*>(orow + c0 * 2);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) dst[e] = w[e];
+            for (int e = 0; e < 32; ++e) r[e] = 0u;
+          }
+          if (row_ok) {
+            uint32_t w[16];
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float a0 = __uint_as_float(r[e]) * inv, a1 = __uint_as_float(r[e + 1]) * inv;
+              const uint16_t lo = p.is_bf16 ? f32_to_bf16_bits_ref(a0) : f32_to_f16_bits_ref(a0);
+              const uint16_t hi = p.is_bf16 ? f32_to_bf16_bits_ref(a1) : f32_to_f16_bits_ref(a1);
+              w[e >> 1] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+            }
+            if (vec) {
+              uint4* dst = reinterpret_cast<uint4*>(orow + c0 * 2);
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) dst[v4] = make_uint4(w[4 * v4], w[4 * v4 + 1], w[4 * v4 + 2], w[4 * v4 + 3]);
+            } else {
+              uint32_t* dst = reinterpret_cast<uint32_t*>(orow + c0 * 2);
+#pragma unroll
+              for (int e = 0; e < 16; ++e) dst[e] = w[e];
+            }
           }
         }
       }
+
+      if (nt > 0) {
+        // O_t has been read: the MMA warp may overwrite it with the first P.V of the next item
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&o_free[t]);
+      }
+      s_base += nt;
     }
   }
 
@@ -1048,18 +1109,21 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
       set_last_error("ytcuda_flash_attn_fwd: no device status word");
       return YTC_CUDA_ERROR;
     }
-    dim3 grid;
     if (p.pair_heads) {
       p.row_blocks = (q_len + FA_BM - 1) / FA_BM;
-      grid = dim3(p.row_blocks, heads / 2, batch);
+      p.head_slots = heads / 2;
     } else {
       p.row_blocks = (q_len + 2 * FA_BM - 1) / (2 * FA_BM);
-      grid = dim3(p.row_blocks, heads, batch);
+      p.head_slots = heads;
     }
-    if (grid.y > 65535 || grid.z > 65535) {
-      set_last_error("ytcuda_flash_attn_fwd: more than 65535 heads or batch items");
+    const int64_t items = static_cast<int64_t>(p.row_blocks) * p.head_slots * batch;
+    if (items > 0x7fffffffll) {
+      set_last_error("ytcuda_flash_attn_fwd: too many work items");
       return YTC_UNSUPPORTED;
     }
+    p.items_per_row_block = p.head_slots * batch;
+    p.n_items = static_cast<int>(items);
+    const dim3 grid(static_cast<unsigned>(p.n_items < sm_count() ? p.n_items : sm_count()));
     if (head_dim == 128) {
       static bool attr = false;
       if (!attr) {
