@@ -234,6 +234,11 @@ int ytcuda_qwen3_set_allreduce(void* handle, int (*fn)(void* buf, int64_t count,
 /* Qwen3ForCausalLM::reset_kv_cache / get_kv_cache_len (qwen3.cpp:425-435). */
 int ytcuda_qwen3_reset(void* handle);
 int ytcuda_qwen3_cache_len(void* handle);
+/* How a forward of ONE new token per sequence runs: 0 = automatic (one persistent cooperative kernel for the whole
+ * step where it applies: no tensor parallelism, batch <= 8), 1 = one launch per operator as for longer inputs,
+ * 2 = the persistent kernel or YTC_UNSUPPORTED. Both forms compute the operator sequence of
+ * Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has no counterpart in the reference. */
+int ytcuda_qwen3_set_decode_path(void* handle, int path);
 /* ids [batch, len] int32 (device) -> logits of the last position [batch, rank's vocab rows] fp32 (device); appends
  * len tokens to the KV caches (Qwen3ForCausalLM::forward, qwen3.cpp:449-457). */
 int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream);

@@ -55,6 +55,50 @@ def test_small_model_logits_match_reference(Q, qwen3_golden, B):
     m.close()
 
 
+@pytest.mark.parametrize("B", [1, 3, 8])
+def test_single_kernel_decode_step_matches_operator_path(Q, B):
+    """The persistent step kernel and the one-launch-per-operator forward compute the same logits and leave the same
+    KV cache behind: 70 steps after a 40-token prompt (the attention of the step kernel goes from 2 to 4 key chunks),
+    each model fed the other's tokens."""
+    cfg = Q.Qwen3Config(hidden_size=256, num_hidden_layers=3, vocab_size=1000, intermediate_size=384,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=128)
+    w = Q.random_weights(cfg, seed=11, std=0.05)
+    ids = dev_ids(np.random.default_rng(B).integers(0, cfg.vocab_size, (B, 40)))
+    ms = []
+    for path in (1, 2):
+        m = Q.Qwen3ForCausalLM(cfg, batch=B)
+        m.load_weights(w)
+        m.set_decode_path(path)
+        ms.append(m)
+    la, lb = ms[0].forward(ids), ms[1].forward(ids)  # prefill: the same kernels in both
+    assert torch.equal(la, lb)
+    launches = []
+    for step in range(70):
+        tok, _ = ms[0].argmax(la)
+        tok = tok.reshape(B, 1).contiguous()
+        n0 = Q._lib.lib().ytcuda_launch_count()
+        la = ms[0].forward(tok)
+        n1 = Q._lib.lib().ytcuda_launch_count()
+        lb = ms[1].forward(tok)
+        n2 = Q._lib.lib().ytcuda_launch_count()
+        launches.append((n1 - n0, n2 - n1))
+        a, b = la.cpu().numpy(), lb.cpu().numpy()
+        assert normwise(b, a) < 2e-5, f"step {step}"
+    assert all(n[1] == 1 for n in launches) and all(n[0] > 20 for n in launches)
+    assert ms[0].get_kv_cache_len() == ms[1].get_kv_cache_len() == 110
+    assert Q._lib.lib().ytcuda_device_status(None) == 0
+    for m in ms:
+        m.close()
+    if B == 8:  # more sequences than the step kernel holds: forcing it is refused, not silently rerouted
+        m = Q.Qwen3ForCausalLM(cfg, batch=9)
+        m.load_weights(w)
+        m.set_decode_path(2)
+        m.forward(dev_ids(np.zeros((9, 4))))
+        with pytest.raises(Exception):
+            m.forward(dev_ids(np.zeros((9, 1))))
+        m.close()
+
+
 def test_long_prefill_uses_tensor_cores_and_matches_oracle(Q, port):
     """More than 32 rows: activations are split into two bf16 planes and multiplied on tcgen05."""
     cfg = Q.Qwen3Config(**SMALL)

@@ -1,0 +1,723 @@
+// One decode step (one new token per sequence) of the Qwen3-shape decoder as ONE persistent cooperative kernel.
+//
+// The operator-per-launch forward needs about 340 launches of kernels that each move a few MB; at batch 1 the step
+// is then bound by launch and ramp latency, not by the 1.2 GB of weights it has to stream. Here one CTA per SM stays
+// resident for the whole step and walks the same operator sequence (reference example/qwen3/src/qwen3.cpp:237-283,
+// 365-457) as phases separated by a grid-wide barrier:
+//
+//   embedding | per layer: [rmsNorm -> qkv linear] | [per-head rmsNorm + RoPE + KV append + attention over the
+//   cache, split over key chunks, last chunk merges] | [o projection + residual] | [rmsNorm -> gate/up linear ->
+//   swish(gate) * up] | [down projection + residual] | final rmsNorm -> vocabulary projection
+//
+// In a linear phase every warp of the grid owns whole weight rows (bf16, streamed once with 128-bit loads) and the
+// few activation rows sit in shared memory as fp32, so the arithmetic (fp32 FMA chains along k, lane partials
+// combined by shuffles) is the same as in skinny_linear_kernel. A warp requests its first weights BEFORE the
+// activations are staged (the weights do not depend on them), and at the start of every phase it asks the L2 to fetch
+// the rows it will own in the next phase, so HBM keeps streaming across the barriers. Activations that cross a
+// barrier are read with ld.global.cg: another SM wrote them, so this SM's L1 may not be used.
+//
+// Attention: a unit is (sequence, kv head, chunk of 128 keys or more) and belongs to one CTA; a warp takes 32 keys at
+// a time with coalesced row loads: 8 lanes share a key for the dot products with the query heads of the group, the
+// warp takes maximum and sum once per 32 keys, and P.V runs with the value dimension across lanes and the
+// probabilities broadcast by shuffles. The 16 warps combine through shared memory and leave one partial (m, l, o)
+// per chunk and head in global memory; the o-projection phase combines the chunks while it stages its input. The
+// K / V rows of a unit are requested from HBM into the L2 one phase earlier.
+//
+// The barrier is a counter in global memory (one arrival per CTA, acquire loads while waiting). The launch is
+// cooperative, so all CTAs are resident; the wait is still bounded: when the cycle budget runs out the CTA raises
+// the device status word and every CTA leaves at its next barrier.
+#pragma once
+
+#include <math_constants.h>
+
+#include "ytc_common.cuh"
+
+namespace ytk {
+
+constexpr int DS_THREADS = 256;
+constexpr int DS_WARPS = DS_THREADS / 32;
+constexpr int DS_MAX_B = 8;        // sequences per step (activation rows kept in shared memory)
+constexpr int DS_MAX_G = 4;        // query heads per kv head
+// attention scratch of a CTA: q of the group, and per warp (m, l, o[128]) for every head of the group
+constexpr int DS_ATT_FLOATS = DS_MAX_G * 128 + 2 * DS_WARPS * DS_MAX_G + DS_WARPS * DS_MAX_G * 128;  // for G = DS_MAX_G
+constexpr long long DS_WAIT_CYCLES = 2000000000ll;
+
+struct DsLayer {
+  const uint16_t *qkv, *o, *gate_up, *down;
+  const float *q_norm, *k_norm, *norm1, *norm2;
+};
+
+struct DecodeStepParams {
+  int B, hidden, layers, heads, kv_heads, inter, vocab_rows, vocab, max_pos, pos;
+  float eps, scale;
+  const int32_t* ids;
+  const uint16_t* embed;
+  const uint16_t* lm_head;
+  const float* final_norm;
+  const DsLayer* lw;  // device array [layers]
+  const float *cos_t, *sin_t;
+  float *k_cache, *v_cache;
+  size_t cache_layer;  // elements per layer
+  float *x, *qkv, *attn, *act, *logits, *part;
+  unsigned int* sync;  // grid barrier counter
+  int chunks, keys_per_chunk;
+  int* status;
+};
+
+__device__ __forceinline__ float ds_ldcg(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ float4 ds_ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+
+// Grid-wide barrier; false when the wait gave up (the caller returns).
+__device__ __forceinline__ bool ds_grid_sync(const DecodeStepParams& p, unsigned int& epoch) {
+  __syncthreads();
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    epoch += gridDim.x;
+    // release: the CTA's writes (ordered before this by the barrier above) are visible to whoever reads the count
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
+    const long long t0 = clock64();
+    unsigned int v;
+    while (true) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sync) : "memory");
+      if (v >= epoch) break;  // also true once any CTA has set the give-up bit
+      if (clock64() - t0 > DS_WAIT_CYCLES) {
+        atomicExch(p.status, YTC_TIMEOUT);
+        atomicOr(p.sync, 0x80000000u);  // releases every waiting CTA at once
+        v = 0x80000000u;
+        break;
+      }
+    }
+    if (v & 0x80000000u) ok = 0;
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// Asks the L2 for the rows n = gw, gw + GW, ... < N of W (K bf16 each); nothing is held in registers.
+__device__ __forceinline__ void ds_prefetch_rows(const uint16_t* W, int N, int K, int gw, int GW, int lane) {
+  const int lines = (K * 2 + 127) / 128;
+  for (int n = gw; n < N; n += GW) {
+    const char* row = reinterpret_cast<const char*>(W + static_cast<int64_t>(n) * K);
+    for (int i = lane; i < lines; i += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + i * 128));
+  }
+}
+
+// 8 bf16 weights (one 128-bit load) times 8 activations, added to s.
+__device__ __forceinline__ float ds_dot8(const uint4& w, const float4& xa, const float4& xb, float s) {
+  s = fmaf(xa.x, __uint_as_float(w.x << 16), s);
+  s = fmaf(xa.y, __uint_as_float(w.x & 0xFFFF0000u), s);
+  s = fmaf(xa.z, __uint_as_float(w.y << 16), s);
+  s = fmaf(xa.w, __uint_as_float(w.y & 0xFFFF0000u), s);
+  s = fmaf(xb.x, __uint_as_float(w.z << 16), s);
+  s = fmaf(xb.y, __uint_as_float(w.z & 0xFFFF0000u), s);
+  s = fmaf(xb.z, __uint_as_float(w.w << 16), s);
+  s = fmaf(xb.w, __uint_as_float(w.w & 0xFFFF0000u), s);
+  return s;
+}
+
+// xs[b][:] = rmsNorm(src[b][:]) * w for b < B (src in global memory, read around L1). One warp per row takes the
+// sum of squares with all its loads in flight at once; meanwhile every thread has requested its piece of w, so the
+// whole staging costs about one trip to the L2.
+__device__ __forceinline__ void ds_stage_rmsnorm(float* xs, const float* src, const float* w, int B, int H, float eps,
+                                                 int warp, int lane) {
+  __shared__ float row_inv[DS_MAX_B];
+  const int n4 = H / 4;
+  float4 wreg[2];  // this thread's columns of w: float4 index threadIdx.x and threadIdx.x + DS_THREADS (H <= 4096)
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int c4 = threadIdx.x + i * DS_THREADS;
+    wreg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c4 < n4) wreg[i] = __ldg(reinterpret_cast<const float4*>(w) + c4);
+  }
+  for (int b = warp; b < B; b += DS_WARPS) {
+    float ss = 0.f;
+    for (int c0 = 0; c0 < H; c0 += 1024) {
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = c0 + i * 128 + lane * 4;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < H) v[i] = ds_ldcg4(src + static_cast<int64_t>(b) * H + c);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = c0 + i * 128 + lane * 4;
+        if (c < H) *reinterpret_cast<float4*>(&xs[b * H + c]) = v[i];
+        ss = fmaf(v[i].x, v[i].x, ss);
+        ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss);
+        ss = fmaf(v[i].w, v[i].w, ss);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) row_inv[b] = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(H)) + eps);
+  }
+  __syncthreads();
+  for (int b = 0; b < B; ++b) {
+    const float inv = row_inv[b];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c4 = threadIdx.x + i * DS_THREADS;
+      if (c4 < n4) {
+        float4 v = *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]);
+        v.x = v.x * inv * wreg[i].x;
+        v.y = v.y * inv * wreg[i].y;
+        v.z = v.z * inv * wreg[i].z;
+        v.w = v.w * inv * wreg[i].w;
+        *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]) = v;
+      }
+    }
+    for (int c4 = threadIdx.x + 2 * DS_THREADS; c4 < n4; c4 += DS_THREADS) {  // hidden sizes above 4096
+      float4 v = *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]);
+      const float4 g = __ldg(reinterpret_cast<const float4*>(w) + c4);
+      v.x = v.x * inv * g.x;
+      v.y = v.y * inv * g.y;
+      v.z = v.z * inv * g.z;
+      v.w = v.w * inv * g.w;
+      *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]) = v;
+    }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ void ds_stage_copy(float* xs, const float* src, int B, int K) {
+  const int n4 = B * K / 4;
+  for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * DS_THREADS) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * DS_THREADS;
+      if (i < n4) v[u] = ds_ldcg4(src + static_cast<int64_t>(i) * 4);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * DS_THREADS;
+      if (i < n4) *reinterpret_cast<float4*>(&xs[i * 4]) = v[u];
+    }
+  }
+  __syncthreads();
+}
+
+// xs[b][head * 128 + d] = attention output, combined from the per-chunk partials (m, l, o[128]) the attention phase
+// left in global memory: o = sum_c e^(m_c - m) o_c / sum_c e^(m_c - m) l_c. Every CTA combines for itself while it
+// stages, so the chunks need no finishing step of their own.
+__device__ __forceinline__ void ds_stage_attention(float* xs, const float* part, int B, int heads, int kv_heads,
+                                                   int chunks) {
+  constexpr int D = 128;
+  const int G = heads / kv_heads;
+  const int per_row = heads * (D / 4);
+  for (int i = threadIdx.x; i < B * per_row; i += DS_THREADS) {
+    const int b = i / per_row, r = i - b * per_row;
+    const int head = r / (D / 4), d4 = r - head * (D / 4);
+    const int kvh = head / G, g = head - kvh * G;
+    const float* base = part + ((static_cast<int64_t>(b) * kv_heads + kvh) * chunks * G + g) * (4 + D);
+    const int64_t cs = static_cast<int64_t>(G) * (4 + D);  // chunk stride
+    // eight chunks at a time with all their loads in flight; the running combination is an online softmax over chunks
+    float m = -CUDART_INF_F, lsum = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = 0; c0 < chunks; c0 += 8) {
+      float mc[8], lc[8];
+      float4 oc[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        mc[u] = -CUDART_INF_F;
+        lc[u] = 0.f;
+        oc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c0 + u < chunks) {
+          mc[u] = ds_ldcg(base + (c0 + u) * cs);
+          lc[u] = ds_ldcg(base + (c0 + u) * cs + 1);
+          oc[u] = ds_ldcg4(base + (c0 + u) * cs + 4 + d4 * 4);
+        }
+      }
+      float m_new = m;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) m_new = fmaxf(m_new, mc[u]);
+      const float alpha = (m == -CUDART_INF_F) ? 0.f : __expf(m - m_new);
+      lsum *= alpha;
+      o.x *= alpha;
+      o.y *= alpha;
+      o.z *= alpha;
+      o.w *= alpha;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float f = (mc[u] == -CUDART_INF_F) ? 0.f : __expf(mc[u] - m_new);
+        lsum = fmaf(lc[u], f, lsum);
+        o.x = fmaf(oc[u].x, f, o.x);
+        o.y = fmaf(oc[u].y, f, o.y);
+        o.z = fmaf(oc[u].z, f, o.z);
+        o.w = fmaf(oc[u].w, f, o.w);
+      }
+      m = m_new;
+    }
+    const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+    o.x *= inv;
+    o.y *= inv;
+    o.z *= inv;
+    o.w *= inv;
+    *reinterpret_cast<float4*>(&xs[b * heads * D + head * D + d4 * 4]) = o;
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ float ds_swish(float v) {  // x * sigmoid(x), two-branch stable sigmoid
+  float sig;
+  if (v >= 0.f) {
+    const float z = expf(-v);
+    sig = 1.0f / (1.0f + z);
+  } else {
+    const float z = expf(v);
+    sig = z / (1.0f + z);
+  }
+  return v * sig;
+}
+
+// Per-head rmsNorm (weight wn) and rotate-half RoPE of the 128 values this warp holds as x[i] = element lane + 32 i.
+__device__ __forceinline__ void ds_norm_rope(float (&x)[4], const float* wn, const float* cr, const float* sr,
+                                             float eps, int lane) {
+  float wv[4], cv[2], sv[2];  // requested before the reduction so that they overlap it
+#pragma unroll
+  for (int i = 0; i < 4; ++i) wv[i] = __ldg(wn + lane + 32 * i);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    cv[i] = __ldg(cr + lane + 32 * i);
+    sv[i] = __ldg(sr + lane + 32 * i);
+  }
+  float ss = x[0] * x[0];
+  ss = fmaf(x[1], x[1], ss);
+  ss = fmaf(x[2], x[2], ss);
+  ss = fmaf(x[3], x[3], ss);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float denom = sqrtf(ss * (1.0f / 128.f) + eps);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) x[i] = (x[i] / denom) * wv[i];
+  float y[4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float c = cv[i], s = sv[i];
+    const float re = x[i], im = x[i + 2];
+    y[i] = re * c - im * s;
+    y[i + 2] = im * c + re * s;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) x[i] = y[i];
+}
+
+__device__ __forceinline__ float ds_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float ds_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+constexpr int DS_KB = 8;  // keys a warp takes per step of the attention phase (two groups of four)
+constexpr int DS_UN = 6;  // 256-column trips requested together per weight row slot
+
+// One linear phase, described at run time so that its code exists once in the kernel (the step walks five of them
+// per layer; a copy per call site made the kernel larger than the instruction cache).
+struct DsLinear {
+  const uint16_t* W;    // [N (or 2 N when epi == 2)][K] bf16
+  int N, K;
+  int stage;            // 0: xs = rmsNorm(src) * norm_w, 1: xs = src, 2: xs = attention output from the partials in src
+  int heads, kv_heads, chunks;  // for stage == 2
+  const float* src;     // [B][K] fp32 in global memory
+  const float* norm_w;
+  int epi;              // 0: dst[m][n] = y, 1: dst[m][n] += y, 2: dst[m][n] = swish(y[n]) * y[N + n]
+  float* dst;
+  int ld;               // row stride of dst
+  // requests for later phases, issued behind this phase's own first loads
+  const uint16_t* pf_w[2];
+  int pf_n[2], pf_k[2];
+  const char *pf_k_rows, *pf_v_rows;  // K / V rows of this CTA's next attention unit (or null)
+  int pf_lines;
+};
+
+// y[b][n] = sum_k xs[b][k] * W[n][k] for the rows this warp owns (n = gw, gw + GW, ...).
+// Two "slots" of DS_UN 128-bit loads per lane are in flight at once: two rows when the warp owns several, the two
+// halves of one row when it owns at most one, rows n and N + n of a fused gate / up weight when epi == 2. The
+// activations are staged into shared memory after the first loads have been issued.
+template <int MT>
+__device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * DS_WARPS + warp;
+  const int GW = gridDim.x * DS_WARPS;
+  const int K = L.K, N = L.N;
+  const bool pair = L.epi == 2;
+  const bool split_k = !pair && N <= GW;  // at most one row per warp: the slots take the two halves of the row
+  const int trips = (K + 255) / 256;
+  const int half = (trips + 1) / 2;
+  const int step = (pair || split_k) ? GW : 2 * GW;
+  bool staged = false;
+  for (int n0 = gw; n0 < N || !staged; n0 += step) {
+    const bool have = n0 < N;
+    const int n1 = n0 + GW;
+    const bool two = have && !pair && !split_k && n1 < N;
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
+    const uint16_t* w0 = L.W + static_cast<int64_t>(have ? n0 : 0) * K;
+    const uint16_t* w1 = pair      ? L.W + static_cast<int64_t>(N + (have ? n0 : 0)) * K
+                         : split_k ? w0 + half * 256
+                                   : L.W + static_cast<int64_t>(two ? n1 : 0) * K;
+    const int k1_off = split_k ? half * 256 : 0;         // column offset of slot 1 within the row
+    const int t0_end = split_k ? half : trips;           // trips of slot 0
+    const int t1_end = split_k ? trips - half : trips;   // trips of slot 1
+    const bool use1 = have && (pair || split_k || two);
+    for (int t = 0; t < t0_end || !staged; t += DS_UN) {
+      uint4 a[DS_UN], b[DS_UN];
+#pragma unroll
+      for (int u = 0; u < DS_UN; ++u) {
+        const int kk = (t + u) * 256 + lane * 8;
+        a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (have && t + u < t0_end && kk < K) a[u] = __ldg(reinterpret_cast<const uint4*>(w0 + kk));
+        if (use1 && t + u < t1_end && k1_off + kk < K) b[u] = __ldg(reinterpret_cast<const uint4*>(w1 + kk));
+      }
+      if (!staged) {
+        for (int i = 0; i < 2; ++i)
+          if (L.pf_w[i]) ds_prefetch_rows(L.pf_w[i], L.pf_n[i], L.pf_k[i], gw, GW, lane);
+        if (L.pf_k_rows)
+          for (int i = threadIdx.x; i < L.pf_lines; i += DS_THREADS) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_k_rows + i * 128));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_v_rows + i * 128));
+          }
+        if (L.stage == 0) ds_stage_rmsnorm(xs, L.src, L.norm_w, B, K, eps, warp, lane);
+        else if (L.stage == 1) ds_stage_copy(xs, L.src, B, K);
+        else ds_stage_attention(xs, L.src, B, L.heads, L.kv_heads, L.chunks);
+        staged = true;
+      }
+      if (!have) break;
+#pragma unroll
+      for (int u = 0; u < DS_UN; ++u) {
+        const int kk = (t + u) * 256 + lane * 8;
+        const int kk1 = k1_off + kk;
+        const bool on0 = t + u < t0_end && kk < K;
+        const bool on1 = use1 && t + u < t1_end && kk1 < K;
+        if (!on0 && !on1) continue;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          if (on0) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[m * K + kk]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[m * K + kk + 4]);
+            acc0[m] = ds_dot8(a[u], xa, xb, acc0[m]);
+          }
+          if (on1) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[m * K + kk1]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[m * K + kk1 + 4]);
+            acc1[m] = ds_dot8(b[u], xa, xb, acc1[m]);
+          }
+        }
+      }
+    }
+    if (!have) break;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      if (split_k) acc0[m] += acc1[m];
+      acc0[m] = ds_warp_sum(acc0[m]);
+      if (!split_k) acc1[m] = ds_warp_sum(acc1[m]);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m >= B) break;
+        float* d0 = L.dst + static_cast<int64_t>(m) * L.ld + n0;
+        if (L.epi == 0) {
+          *d0 = acc0[m];
+          if (two) d0[GW] = acc1[m];
+        } else if (L.epi == 1) {  // this warp is the only writer of these elements
+          *d0 = acc0[m] + ds_ldcg(d0);
+          if (two) d0[GW] = acc1[m] + ds_ldcg(d0 + GW);
+        } else {
+          *d0 = ds_swish(acc0[m]) * acc1[m];
+        }
+      }
+    }
+  }
+}
+
+// The attention phase of one layer (see the file header). G = query heads per kv head.
+template <int G>
+__device__ __noinline__ void ds_attention_phase(const DecodeStepParams& p, const DsLayer& W, float* kc, float* vc,
+                                                float* xs) {
+  constexpr int D = 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int B = p.B;
+  const int qkv_w = (p.heads + 2 * p.kv_heads) * D;
+  const int units = B * p.kv_heads * p.chunks;
+  const int n_keys = p.pos + 1;
+  const float* cr = p.cos_t + static_cast<int64_t>(p.pos) * D;
+  const float* sr = p.sin_t + static_cast<int64_t>(p.pos) * D;
+  float* qs = xs;                 // [G][128] query heads of the group, normalised and rotated
+  float* pm = qs + G * D;         // [DS_WARPS][G] running maxima of the warps
+  float* pl = pm + DS_WARPS * G;  // sums
+  float* po = pl + DS_WARPS * G;  // [DS_WARPS][G][128] unnormalised outputs
+  for (int u = blockIdx.x; u < units; u += gridDim.x) {
+    const int chunk = u % p.chunks;
+    const int bk = u / p.chunks;
+    const int b = bk / p.kv_heads, kvh = bk - b * p.kv_heads;
+    const float* row = p.qkv + static_cast<int64_t>(b) * qkv_w;
+    const int k_begin = chunk * p.keys_per_chunk;
+    int k_end = k_begin + p.keys_per_chunk;
+    if (k_end > n_keys) k_end = n_keys;
+    if (warp < G) {
+      float x[4];
+      const float* src = row + (kvh * G + warp) * D;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = ds_ldcg(src + lane + 32 * i);
+      ds_norm_rope(x, W.q_norm, cr, sr, p.eps, lane);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qs[warp * D + lane + 32 * i] = x[i];
+    } else if (warp == G && k_begin <= p.pos && p.pos < k_end) {  // this unit holds the token of this step
+      float x[4], y[4];
+      const float* ksrc = row + (p.heads + kvh) * D;
+      const float* vsrc = row + (p.heads + p.kv_heads + kvh) * D;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x[i] = ds_ldcg(ksrc + lane + 32 * i);
+        y[i] = ds_ldcg(vsrc + lane + 32 * i);
+      }
+      ds_norm_rope(x, W.k_norm, cr, sr, p.eps, lane);
+      float* kdst = kc + ((static_cast<int64_t>(b) * p.kv_heads + kvh) * p.max_pos + p.pos) * D;
+      float* vdst = vc + ((static_cast<int64_t>(b) * p.kv_heads + kvh) * p.max_pos + p.pos) * D;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        kdst[lane + 32 * i] = x[i];
+        vdst[lane + 32 * i] = y[i];
+      }
+    }
+    __syncthreads();
+    const float* kb = kc + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.max_pos * D;
+    const float* vb = vc + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.max_pos * D;
+    float m_run[G], l_run[G];
+    float4 acc[G];  // value columns 4 lane .. 4 lane + 3
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m_run[g] = -CUDART_INF_F;
+      l_run[g] = 0.f;
+      acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // Scores: 8 lanes share a key (16 of its 128 values each), so one load instruction covers 4 whole K rows
+    // (4 x 512 contiguous bytes) and a dot product is finished by 3 shuffles; a warp takes DS_KB keys per step, so
+    // that the keys of a chunk spread over all 16 warps.
+    const int j8 = lane & 7, kq = lane >> 3;
+    float4 qreg[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qreg[g][i] = *reinterpret_cast<const float4*>(&qs[g * D + (j8 + 8 * i) * 4]);
+    for (int key0 = k_begin + warp * DS_KB; key0 < k_end; key0 += DS_WARPS * DS_KB) {
+      // (The row of this step's token was stored by a warp of this CTA before the barrier above: plain loads.)
+      float sc[G][DS_KB / 4];
+#pragma unroll
+      for (int kg = 0; kg < DS_KB / 4; ++kg) {
+        const int key = key0 + kg * 4 + kq;
+        const bool valid = key < k_end;
+        const float4* krow = reinterpret_cast<const float4*>(kb + static_cast<int64_t>(valid ? key : k_begin) * D);
+        float4 kv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) kv[i] = krow[j8 + 8 * i];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float d = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            d = fmaf(qreg[g][i].x, kv[i].x, d);
+            d = fmaf(qreg[g][i].y, kv[i].y, d);
+            d = fmaf(qreg[g][i].z, kv[i].z, d);
+            d = fmaf(qreg[g][i].w, kv[i].w, d);
+          }
+          d += __shfl_xor_sync(0xffffffffu, d, 1);
+          d += __shfl_xor_sync(0xffffffffu, d, 2);
+          d += __shfl_xor_sync(0xffffffffu, d, 4);
+          sc[g][kg] = valid ? d * p.scale : -CUDART_INF_F;
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float mx = sc[g][0];
+#pragma unroll
+        for (int kg = 1; kg < DS_KB / 4; ++kg) mx = fmaxf(mx, sc[g][kg]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_run[g], mx);       // finite: every step has a valid key
+        const float alpha = __expf(m_run[g] - m_new);  // 0 on the first step (m_run = -inf)
+        float sum = 0.f;
+#pragma unroll
+        for (int kg = 0; kg < DS_KB / 4; ++kg) {
+          sc[g][kg] = __expf(sc[g][kg] - m_new);  // probabilities from here on; 0 for keys past the end
+          sum += sc[g][kg];
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 8);  // over the 4 key slots; the 8 lanes of a key hold copies
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+        l_run[g] = l_run[g] * alpha + sum;
+        m_run[g] = m_new;
+        acc[g].x *= alpha;
+        acc[g].y *= alpha;
+        acc[g].z *= alpha;
+        acc[g].w *= alpha;
+      }
+      // P.V: value columns across lanes (one coalesced row per key), probabilities broadcast key by key
+#pragma unroll
+      for (int kg = 0; kg < DS_KB / 4; ++kg) {
+        float4 vv[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int key = key0 + kg * 4 + t;
+          vv[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (key < k_end) vv[t] = *(reinterpret_cast<const float4*>(vb + static_cast<int64_t>(key) * D) + lane);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float pt = __shfl_sync(0xffffffffu, sc[g][kg], t * 8);
+            acc[g].x = fmaf(pt, vv[t].x, acc[g].x);
+            acc[g].y = fmaf(pt, vv[t].y, acc[g].y);
+            acc[g].z = fmaf(pt, vv[t].z, acc[g].z);
+            acc[g].w = fmaf(pt, vv[t].w, acc[g].w);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (lane == 0) {
+        pm[warp * G + g] = m_run[g];
+        pl[warp * G + g] = l_run[g];
+      }
+      *reinterpret_cast<float4*>(&po[(warp * G + g) * D + lane * 4]) = acc[g];
+    }
+    __syncthreads();
+    if (warp < G) {
+      // warp g combines the 16 warps' results of query head g
+      const int g = warp;
+      const float mw = lane < DS_WARPS ? pm[lane * G + g] : -CUDART_INF_F;
+      const float lw = lane < DS_WARPS ? pl[lane * G + g] : 0.f;
+      const float m = ds_warp_max(mw);
+      const float fw = (mw == -CUDART_INF_F) ? 0.f : __expf(mw - m);
+      const float lsum = ds_warp_sum(lw * fw);
+      float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int w = 0; w < DS_WARPS; ++w) {
+        const float f = __shfl_sync(0xffffffffu, fw, w);
+        const float4 ow = *reinterpret_cast<const float4*>(&po[(w * G + g) * D + lane * 4]);
+        o.x = fmaf(ow.x, f, o.x);
+        o.y = fmaf(ow.y, f, o.y);
+        o.z = fmaf(ow.z, f, o.z);
+        o.w = fmaf(ow.w, f, o.w);
+      }
+      // partial of this chunk: m, l, unnormalised o; the o-projection phase combines the chunks while it stages
+      float* dst = p.part + ((static_cast<int64_t>(bk) * p.chunks + chunk) * G + g) * (4 + D);
+      if (lane == 0) {
+        dst[0] = m;
+        dst[1] = lsum;
+      }
+      *reinterpret_cast<float4*>(dst + 4 + lane * 4) = o;
+    }
+    __syncthreads();  // the scratch is reused by this CTA's next unit
+  }
+}
+
+template <int MT, int G>
+__global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DecodeStepParams p) {
+  extern __shared__ __align__(16) float xs[];  // [MT][max K]; the attention phase uses it as scratch
+  constexpr int D = 128;
+  const int B = p.B, H = p.hidden;
+  const int qkv_w = (p.heads + 2 * p.kv_heads) * D;
+  const int attn_w = p.heads * D;
+  unsigned int epoch = 0;
+
+  // ---- embedding gather: x[b, :] = float(embed[ids[b], :])
+  {
+    const int per_row = H / 4;
+    for (int i = blockIdx.x * DS_THREADS + threadIdx.x; i < B * per_row; i += gridDim.x * DS_THREADS) {
+      const int b = i / per_row, c = (i - b * per_row) * 4;
+      int id = p.ids[b];
+      id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(p.embed + static_cast<int64_t>(id) * H + c));
+      float4 o;
+      o.x = __uint_as_float(w.x << 16);
+      o.y = __uint_as_float(w.x & 0xFFFF0000u);
+      o.z = __uint_as_float(w.y << 16);
+      o.w = __uint_as_float(w.y & 0xFFFF0000u);
+      *reinterpret_cast<float4*>(p.x + static_cast<int64_t>(b) * H + c) = o;
+    }
+  }
+  if (!ds_grid_sync(p, epoch)) return;
+
+  // K / V rows of this CTA's first attention unit (a CTA has more than one only with very many sequences or
+  // very long contexts; the others are then fetched on demand)
+  const char *kv_k = nullptr, *kv_v = nullptr;
+  int kv_lines = 0;
+  int64_t kv_off = 0;
+  if (static_cast<int>(blockIdx.x) < B * p.kv_heads * p.chunks) {
+    const int chunk = blockIdx.x % p.chunks, bk = blockIdx.x / p.chunks;
+    const int k_begin = chunk * p.keys_per_chunk;
+    int k_end = k_begin + p.keys_per_chunk;
+    if (k_end > p.pos) k_end = p.pos;
+    kv_off = (static_cast<int64_t>(bk) * p.max_pos + k_begin) * D;
+    kv_lines = k_end > k_begin ? (k_end - k_begin) * 4 : 0;
+  }
+
+  for (int l = 0; l < p.layers; ++l) {
+    const DsLayer W = p.lw[l];
+    float* kc = p.k_cache + static_cast<size_t>(l) * p.cache_layer;
+    float* vc = p.v_cache + static_cast<size_t>(l) * p.cache_layer;
+    if (kv_lines > 0) {
+      kv_k = reinterpret_cast<const char*>(kc + kv_off);
+      kv_v = reinterpret_cast<const char*>(vc + kv_off);
+    }
+    DsLinear L;
+
+    // ---- qkv = rmsNorm(x) . Wqkv^T
+    L = DsLinear{W.qkv, qkv_w, H, 0, 0, 0, 0, p.x, W.norm1, 0, p.qkv, qkv_w, {W.o, nullptr}, {H, 0}, {attn_w, 0},
+                 kv_k, kv_v, kv_lines};
+    ds_linear_phase<MT>(L, xs, B, p.eps);
+    if (!ds_grid_sync(p, epoch)) return;
+
+    // ---- attention over the cache (+ per-head rmsNorm, RoPE, KV append); the gate / up rows are requested here
+    {
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+      const int gw = blockIdx.x * DS_WARPS + warp, GW = gridDim.x * DS_WARPS;
+      ds_prefetch_rows(W.gate_up, p.inter, H, gw, GW, lane);
+      ds_prefetch_rows(W.gate_up + static_cast<int64_t>(p.inter) * H, p.inter, H, gw, GW, lane);
+    }
+    ds_attention_phase<G>(p, W, kc, vc, xs);
+    if (!ds_grid_sync(p, epoch)) return;
+
+    // ---- x += attn . Wo^T
+    L = DsLinear{W.o, H, attn_w, 2, p.heads, p.kv_heads, p.chunks, p.part, nullptr, 1, p.x, H, {W.down, nullptr},
+                 {H, 0}, {p.inter, 0}, nullptr, nullptr, 0};
+    ds_linear_phase<MT>(L, xs, B, p.eps);
+    if (!ds_grid_sync(p, epoch)) return;
+
+    // ---- act = swish(gate) * up, gate / up = rmsNorm(x) . Wgu^T (rows i and inter + i of the fused weight)
+    {
+      const bool last = l + 1 == p.layers;
+      const int4 nxt = last ? make_int4(p.vocab_rows < 4 * static_cast<int>(gridDim.x) * DS_WARPS
+                                            ? p.vocab_rows
+                                            : 4 * static_cast<int>(gridDim.x) * DS_WARPS, H, 0, 0)
+                            : make_int4(qkv_w, H, 0, 0);
+      L = DsLinear{W.gate_up, p.inter, H, 0, 0, 0, 0, p.x, W.norm2, 2, p.act, p.inter,
+                   {last ? p.lm_head : p.lw[l + 1].qkv, nullptr}, {nxt.x, 0}, {nxt.y, 0}, nullptr, nullptr, 0};
+    }
+    ds_linear_phase<MT>(L, xs, B, p.eps);
+    if (!ds_grid_sync(p, epoch)) return;
+
+    // ---- x += act . Wdown^T
+    L = DsLinear{W.down, H, p.inter, 1, 0, 0, 0, p.act, nullptr, 1, p.x, H, {nullptr, nullptr}, {0, 0}, {0, 0},
+                 nullptr, nullptr, 0};
+    ds_linear_phase<MT>(L, xs, B, p.eps);
+    if (!ds_grid_sync(p, epoch)) return;
+  }
+
+  // ---- logits = rmsNorm(x) . Wvocab^T
+  DsLinear L{p.lm_head, p.vocab_rows, H, 0, 0, 0, 0, p.x, p.final_norm, 0, p.logits, p.vocab_rows, {nullptr, nullptr},
+             {0, 0}, {0, 0}, nullptr, nullptr, 0};
+  ds_linear_phase<MT>(L, xs, B, p.eps);
+}
+
+}  // namespace ytk

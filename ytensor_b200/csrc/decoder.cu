@@ -19,6 +19,7 @@
 #include <string>
 #include <vector>
 
+#include "decode_step.cuh"
 #include "ytc_common.cuh"
 
 namespace ytk {
@@ -261,6 +262,13 @@ struct Qwen3Model {
   int64_t act_rows = 0;
   AllReduceFn allreduce = nullptr;
   void* allreduce_user = nullptr;
+  // single-kernel decode step (decode_step.cuh)
+  int decode_path = 0;              // 0 automatic, 1 one launch per operator, 2 the persistent step kernel or fail
+  DsLayer* ds_lw = nullptr;         // device copy of the per-layer weight pointers
+  bool ds_lw_stale = true;
+  float* ds_part = nullptr;         // attention partials
+  unsigned int* ds_sync = nullptr;  // barrier counter + per (sequence, kv head) chunk counters
+  int ds_smem_set = 0;
   std::vector<void*> owned;
 };
 
@@ -467,6 +475,7 @@ int ytcuda_qwen3_set_weight(void* handle, const char* name, int layer, const voi
   YTC_REQUIRE(m && name && dptr, "ytcuda_qwen3_set_weight: null argument");
   YTC_REQUIRE((reinterpret_cast<uint64_t>(dptr) & 15) == 0, "ytcuda_qwen3_set_weight: weights must be 16-byte aligned");
   const std::string n(name);
+  m->ds_lw_stale = true;
   if (n == "embed") { m->embed = static_cast<const uint16_t*>(dptr); return YTC_OK; }
   if (n == "lm_head") { m->lm_head = static_cast<const uint16_t*>(dptr); return YTC_OK; }
   if (n == "norm") { m->final_norm = static_cast<const float*>(dptr); return YTC_OK; }
@@ -503,6 +512,15 @@ int ytcuda_qwen3_reset(void* handle) {
   m->cur_len = 0;
   return YTC_OK;
 }
+// 0: automatic (the persistent step kernel where it applies), 1: always one launch per operator, 2: the persistent
+// step kernel or YTC_UNSUPPORTED.
+int ytcuda_qwen3_set_decode_path(void* handle, int path) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m, "ytcuda_qwen3_set_decode_path: null handle");
+  YTC_REQUIRE(path >= 0 && path <= 2, "ytcuda_qwen3_set_decode_path: path must be 0, 1 or 2");
+  m->decode_path = path;
+  return YTC_OK;
+}
 int ytcuda_qwen3_cache_len(void* handle) {
   auto* m = static_cast<Qwen3Model*>(handle);
   return m ? m->cur_len : -1;
@@ -532,6 +550,85 @@ static int ensure_activations(Qwen3Model* m, int64_t rows) {
   return YTC_OK;
 }
 
+constexpr int DS_MAX_CHUNKS = 64;
+
+// Whether the persistent step kernel covers this model (one new token per sequence is checked by the caller).
+static bool decode_step_supported(const Qwen3Model* m) {
+  const int groups = m->heads / m->kv_heads;
+  return m->tp_world == 1 && m->batch <= DS_MAX_B && m->head_dim == 128 && (groups == 1 || groups == 2 || groups == 4) &&
+         m->hidden % 8 == 0 && m->inter % 8 == 0;
+}
+
+// One decode step as one cooperative launch; activations must have been allocated for `batch` rows.
+static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, cudaStream_t st) {
+  const int B = m->batch, D = m->head_dim;
+  const int groups = m->heads / m->kv_heads;
+  const size_t sync_words = 1;
+  if (!m->ds_part) {
+    int s;
+    const size_t part = static_cast<size_t>(B) * m->kv_heads * DS_MAX_CHUNKS * groups * (4 + D) * sizeof(float);
+    if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->ds_part), part)) != YTC_OK) return s;
+    if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->ds_sync), sync_words * sizeof(unsigned int))) != YTC_OK) return s;
+    if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->ds_lw), m->layers * sizeof(DsLayer))) != YTC_OK) return s;
+  }
+  if (m->ds_lw_stale) {
+    std::vector<DsLayer> h(m->layers);
+    for (int l = 0; l < m->layers; ++l) {
+      const LayerW& L = m->lw[l];
+      h[l] = DsLayer{L.qkv, L.o, L.gate_up, L.down, L.q_norm, L.k_norm, L.norm1, L.norm2};
+    }
+    YTC_CUDA(cudaMemcpyAsync(m->ds_lw, h.data(), h.size() * sizeof(DsLayer), cudaMemcpyHostToDevice, st));
+    YTC_CUDA(cudaStreamSynchronize(st));  // `h` leaves scope
+    m->ds_lw_stale = false;
+  }
+  int kmax = m->hidden > m->inter ? m->hidden : m->inter;
+  if (m->heads * D > kmax) kmax = m->heads * D;
+  // the kernel is instantiated for 1, 2, 4 or 8 activation rows and reads that many rows of shared memory
+  const int mt = B == 1 ? 1 : (B == 2 ? 2 : (B <= 4 ? 4 : 8));
+  int smem = mt * kmax * static_cast<int>(sizeof(float));
+  const int att = DS_ATT_FLOATS * static_cast<int>(sizeof(float));  // the attention phase's scratch
+  if (smem < att) smem = att;
+  DecodeStepParams p{};
+  p.B = B; p.hidden = m->hidden; p.layers = m->layers; p.heads = m->heads; p.kv_heads = m->kv_heads;
+  p.inter = m->inter; p.vocab_rows = m->l_vocab; p.vocab = m->vocab; p.max_pos = m->max_pos; p.pos = m->cur_len;
+  p.eps = m->eps; p.scale = 1.0f / std::sqrt(static_cast<float>(D));
+  p.ids = ids; p.embed = m->embed; p.lm_head = m->lm_head; p.final_norm = m->final_norm; p.lw = m->ds_lw;
+  p.cos_t = m->cos_t; p.sin_t = m->sin_t; p.k_cache = m->k_cache; p.v_cache = m->v_cache;
+  p.cache_layer = static_cast<size_t>(B) * m->kv_heads * m->max_pos * D;
+  p.x = m->x; p.qkv = m->qkv; p.attn = m->attn; p.act = m->act; p.logits = logits; p.part = m->ds_part;
+  p.sync = m->ds_sync; p.status = device_status_word();
+  const int keys = m->cur_len + 1;
+  // Key chunks of 128 keys (8 per warp), fewer and longer ones when that would be more units than CTAs or more
+  // than DS_MAX_CHUNKS chunks.
+  int n_chunks = (keys + 127) / 128;
+  const int fit = sm_count() / (B * m->kv_heads);
+  if (n_chunks > fit) n_chunks = fit > 0 ? fit : 1;
+  if (n_chunks > DS_MAX_CHUNKS) n_chunks = DS_MAX_CHUNKS;
+  int per = (keys + n_chunks - 1) / n_chunks;
+  per = (per + 31) / 32 * 32;  // whole blocks of 32 keys
+  p.keys_per_chunk = per;
+  p.chunks = (keys + per - 1) / per;
+  YTC_CUDA(cudaMemsetAsync(m->ds_sync, 0, sync_words * sizeof(unsigned int), st));
+  void* args[] = {&p};
+  const void* fn = nullptr;
+#define DS_PICK(MT)                                                                       \
+  fn = groups == 1   ? reinterpret_cast<const void*>(decode_step_kernel<MT, 1>)           \
+       : groups == 2 ? reinterpret_cast<const void*>(decode_step_kernel<MT, 2>)           \
+                     : reinterpret_cast<const void*>(decode_step_kernel<MT, 4>)
+  if (mt == 1) DS_PICK(1);
+  else if (mt == 2) DS_PICK(2);
+  else if (mt == 4) DS_PICK(4);
+  else DS_PICK(8);
+#undef DS_PICK
+  if (m->ds_smem_set < smem) {
+    YTC_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    m->ds_smem_set = smem;
+  }
+  YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(DS_THREADS), args, smem, st));
+  count_launch();
+  return YTC_OK;
+}
+
 // ids [batch, len] (device int32) -> logits [batch, this rank's vocab rows] (device fp32) of the LAST position;
 // appends `len` tokens to the KV caches (qwen3::Qwen3ForCausalLM::forward, reference qwen3.cpp:449-457).
 int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream) {
@@ -555,6 +652,16 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   if (s != YTC_OK) return s;
   const int pos0 = m->cur_len;
   const int kv_len = pos0 + len;
+  if (len == 1 && m->decode_path != 1 && decode_step_supported(m)) {
+    if ((s = decode_step_launch(m, ids, logits, st)) != YTC_OK) return s;
+    m->cur_len = kv_len;
+    return YTC_OK;
+  }
+  if (len == 1 && m->decode_path == 2) {
+    set_last_error("ytcuda_qwen3_forward: the single-kernel decode step needs batch <= %d, no tensor "
+                   "parallelism and 1, 2 or %d query heads per kv head", DS_MAX_B, DS_MAX_G);
+    return YTC_UNSUPPORTED;
+  }
   const int qkv_w = (m->l_heads + 2 * m->l_kv_heads) * D;
   const int groups = m->heads / m->kv_heads;
   const float scale = 1.0f / std::sqrt(static_cast<float>(D));

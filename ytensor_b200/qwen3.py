@@ -174,6 +174,10 @@ class Qwen3ForCausalLM:
     def reset_kv_cache(self) -> None:
         check(self.L.ytcuda_qwen3_reset(self.h))
 
+    def set_decode_path(self, path: int) -> None:
+        """0: automatic, 1: one launch per operator, 2: the single persistent kernel per decode step (or an error)."""
+        check(self.L.ytcuda_qwen3_set_decode_path(self.h, int(path)))
+
     def get_kv_cache_len(self) -> int:
         return self.L.ytcuda_qwen3_cache_len(self.h)
 
