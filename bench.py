@@ -472,7 +472,8 @@ def decode_arm(args) -> None:
                        "l2": "weights (1.19 GB) larger than L2"},
             "prefill_tokens_per_s": B * prompt_len / (prefill_ms * 1e-3), "prefill_ms": prefill_ms,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "skinny_linear_kernel",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "kernel": "decode_step_kernel" if (world == 1 and B <= 8) else "skinny_linear_kernel",
                          "peak_source": f"{peaks['source']} (copy bandwidth)",
                          "algorithmic_bytes_per_launch": bytes_per_step,
                          "note": "bytes of this rank's bf16 weights streamed once per decode step / step time"},

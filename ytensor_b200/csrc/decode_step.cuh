@@ -314,7 +314,7 @@ __device__ __forceinline__ float ds_warp_sum(float v) {
   return v;
 }
 
-constexpr int DS_KB = 8;  // keys a warp takes per step of the attention phase (two groups of four)
+constexpr int DS_KB = 16;  // keys a warp takes per step of the attention phase (four groups of four)
 constexpr int DS_UN = 6;  // 256-column trips requested together per weight row slot
 
 // One linear phase, described at run time so that its code exists once in the kernel (the step walks five of them
@@ -511,23 +511,34 @@ __device__ __noinline__ void ds_attention_phase(const DecodeStepParams& p, const
     for (int key0 = k_begin + warp * DS_KB; key0 < k_end; key0 += DS_WARPS * DS_KB) {
       // (The row of this step's token was stored by a warp of this CTA before the barrier above: plain loads.)
       float sc[G][DS_KB / 4];
+      float4 vv[DS_KB];  // V rows of the step, requested before the scores are formed
+#pragma unroll
+      for (int t = 0; t < DS_KB; ++t) {
+        vv[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (key0 + t < k_end) vv[t] = *(reinterpret_cast<const float4*>(vb + static_cast<int64_t>(key0 + t) * D) + lane);
+      }
+      float4 kvr[DS_KB / 4][4];
+#pragma unroll
+      for (int kg = 0; kg < DS_KB / 4; ++kg) {
+        const int key = key0 + kg * 4 + kq;
+        const float4* krow =
+            reinterpret_cast<const float4*>(kb + static_cast<int64_t>(key < k_end ? key : k_begin) * D);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) kvr[kg][i] = krow[j8 + 8 * i];
+      }
 #pragma unroll
       for (int kg = 0; kg < DS_KB / 4; ++kg) {
         const int key = key0 + kg * 4 + kq;
         const bool valid = key < k_end;
-        const float4* krow = reinterpret_cast<const float4*>(kb + static_cast<int64_t>(valid ? key : k_begin) * D);
-        float4 kv[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) kv[i] = krow[j8 + 8 * i];
 #pragma unroll
         for (int g = 0; g < G; ++g) {
           float d = 0.f;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            d = fmaf(qreg[g][i].x, kv[i].x, d);
-            d = fmaf(qreg[g][i].y, kv[i].y, d);
-            d = fmaf(qreg[g][i].z, kv[i].z, d);
-            d = fmaf(qreg[g][i].w, kv[i].w, d);
+            d = fmaf(qreg[g][i].x, kvr[kg][i].x, d);
+            d = fmaf(qreg[g][i].y, kvr[kg][i].y, d);
+            d = fmaf(qreg[g][i].z, kvr[kg][i].z, d);
+            d = fmaf(qreg[g][i].w, kvr[kg][i].w, d);
           }
           d += __shfl_xor_sync(0xffffffffu, d, 1);
           d += __shfl_xor_sync(0xffffffffu, d, 2);
@@ -562,22 +573,15 @@ __device__ __noinline__ void ds_attention_phase(const DecodeStepParams& p, const
       // P.V: value columns across lanes (one coalesced row per key), probabilities broadcast key by key
 #pragma unroll
       for (int kg = 0; kg < DS_KB / 4; ++kg) {
-        float4 vv[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int key = key0 + kg * 4 + t;
-          vv[t] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (key < k_end) vv[t] = *(reinterpret_cast<const float4*>(vb + static_cast<int64_t>(key) * D) + lane);
-        }
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
 #pragma unroll
           for (int g = 0; g < G; ++g) {
             const float pt = __shfl_sync(0xffffffffu, sc[g][kg], t * 8);
-            acc[g].x = fmaf(pt, vv[t].x, acc[g].x);
-            acc[g].y = fmaf(pt, vv[t].y, acc[g].y);
-            acc[g].z = fmaf(pt, vv[t].z, acc[g].z);
-            acc[g].w = fmaf(pt, vv[t].w, acc[g].w);
+            acc[g].x = fmaf(pt, vv[kg * 4 + t].x, acc[g].x);
+            acc[g].y = fmaf(pt, vv[kg * 4 + t].y, acc[g].y);
+            acc[g].z = fmaf(pt, vv[kg * 4 + t].z, acc[g].z);
+            acc[g].w = fmaf(pt, vv[kg * 4 + t].w, acc[g].w);
           }
         }
       }
