@@ -87,6 +87,16 @@ int ytcuda_gemm_host(int dtype_in, int dtype_out, const void* A, const void* B, 
                      float alpha, float beta, int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc,
                      int64_t csc, int64_t batch, int64_t bsa, int64_t bsb, int64_t bsc);
 
+/* C[b][i][j] = (A[b] . B[b])[i][j] where mask[i][j] != 0, masked_value elsewhere; mask is a bool / uint8 matrix
+ * [m, n] (row stride in bytes = elements) shared by every batch item. Replaces YTensor::masked_matmul with a bool
+ * mask (src/ytensor_math.inl:318-366, 1053-1090; yt::kernel::avx2::sgemm_masked, src/kernel/avx2/sgemm.inl:342-584).
+ * The product runs as ytcuda_gemm does (alpha 1, beta 0), a second pass writes masked_value; a predicate mask is
+ * materialised by the caller. */
+int ytcuda_gemm_masked(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
+                       int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc, int64_t batch,
+                       int64_t bsa, int64_t bsb, int64_t bsc, const void* mask, int64_t mask_row_stride,
+                       float masked_value, void* stream);
+
 /* ---------------------------------------------------------------- reductions over axes
  * All N-d entry points take `ndim` (1..8) extents and ELEMENT strides; `axes` lists the reduced axes
  * (negative values count from the end). The reduced elements of one output position are walked

@@ -232,6 +232,18 @@ class PortOracle(_Backend):
         self.lib.yto_matmul_f32(_opt(a3), _opt(b), _opt(c), batch, m, n, k, bb)
         return c.reshape(a.shape[:-1] + (n,))
 
+    def masked_matmul(self, a, b, mask, masked_value=0.0):
+        """a [batch,m,k] . b [k,n] or [batch,k,n] where mask [m,n] (bool), masked_value elsewhere; fp32."""
+        a, b = _f32(a), _f32(b)
+        a3 = a.reshape((-1,) + a.shape[-2:])
+        batch, m, k = a3.shape
+        n = b.shape[-1]
+        mk = np.ascontiguousarray(mask, np.uint8)
+        c = np.empty((batch, m, n), np.float32)
+        self.lib.yto_masked_matmul_f32(_opt(a3), _opt(b), _opt(mk), C.c_float(masked_value), _opt(c), batch, m, n, k,
+                                       int(b.ndim == 3))
+        return c.reshape(a.shape[:-1] + (n,))
+
     def matmul_16(self, a_bits, b_bits, dtype):
         """bf16 (dtype=1) / fp16 (dtype=2) storage, fp32 compute; uint16 bit patterns in and out."""
         a = np.ascontiguousarray(a_bits, np.uint16)
@@ -280,6 +292,18 @@ class RefOracle(_Backend):
         n = b.shape[-1]
         c = np.empty((batch, m, n), np.float32)
         rc = self.lib.ytref_matmul_f32(_opt(a3), _opt(b), _opt(c), batch, m, n, k, int(b.ndim == 3), backend)
+        assert rc == 0, rc
+        return c.reshape(a.shape[:-1] + (n,))
+
+    def masked_matmul(self, a, b, mask, masked_value=0.0, backend=2):
+        a, b = _f32(a), _f32(b)
+        a3 = a.reshape((-1,) + a.shape[-2:])
+        batch, m, k = a3.shape
+        n = b.shape[-1]
+        mk = np.ascontiguousarray(mask, np.uint8)
+        c = np.empty((batch, m, n), np.float32)
+        rc = self.lib.ytref_masked_matmul_f32(_opt(a3), _opt(b), _opt(mk), C.c_float(masked_value), _opt(c), batch, m,
+                                              n, k, int(b.ndim == 3), backend)
         assert rc == 0, rc
         return c.reshape(a.shape[:-1] + (n,))
 

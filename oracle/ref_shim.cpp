@@ -77,6 +77,32 @@ int ytref_matmul_f32(const float* A, const float* B, float* C, int batch, int m,
   }
 }
 
+// YTensor::masked_matmul with a bool mask [m,n] shared by every batch item (src/ytensor_math.inl:318-366).
+// backend: 0 = Naive, 2 = AVX2.
+int ytref_masked_matmul_f32(const float* A, const float* B, const unsigned char* mask, float masked_value, float* C,
+                            int batch, int m, int n, int k, int b_batched, int backend) {
+  try {
+    const int as[3] = {batch, m, k};
+    auto a = make<3>(A, as);
+    yt::YTensor<bool, 2> mk(m, n);
+    for (int i = 0; i < m; ++i)
+      for (int j = 0; j < n; ++j) mk.at(i, j) = mask[static_cast<size_t>(i) * n + j] != 0;
+    const auto be = static_cast<yt::infos::MatmulBackend>(backend);
+    if (b_batched) {
+      const int bs[3] = {batch, k, n};
+      auto b = make<3>(B, bs);
+      dump(a.masked_matmul(b, mk, masked_value, be), C);
+    } else {
+      const int bs[2] = {k, n};
+      auto b = make<2>(B, bs);
+      dump(a.masked_matmul(b, mk, masked_value, be), C);
+    }
+    return 0;
+  } catch (const std::exception&) {
+    return 1;
+  }
+}
+
 // yt::function::linear: x [rows,k] . W[n,k]^T (+ bias[n])
 int ytref_linear_f32(const float* X, const float* W, const float* bias, float* Y, int rows, int n, int k) {
   try {

@@ -131,6 +131,16 @@ def main() -> None:
     g["att_q_one"] = q1
     g["att_decode"] = R.sdpa(q1, k, v, causal=True)
 
+    # ---- masked matmul (appended last so that the draws above stay what they were) -------------
+    a, b2, b3 = N(2, 37, 45), N(45, 26), N(2, 45, 26)
+    mk = np.random.default_rng(77).random((37, 26)) < 0.6
+    mk[5, :] = False   # a row with nothing kept
+    mk[:, 7] = True    # a column kept everywhere
+    g["mmask_a"], g["mmask_b2"], g["mmask_b3"], g["mmask_mask"] = a, b2, b3, mk
+    g["mmask_c_shared"] = R.masked_matmul(a, b2, mk, -1.5)
+    g["mmask_c_batched"] = R.masked_matmul(a, b3, mk, 0.0)
+    g["mmask_c_shared_naive"] = R.masked_matmul(a, b2, mk, -1.5, backend=0)
+
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 

@@ -210,6 +210,32 @@ def test_alpha_beta_bf16(L, api, port):
     assert normwise(out.cpu().numpy(), want) < 1e-5
 
 
+def test_masked_matmul_golden_and_16bit(L, api, port, golden):
+    """YTensor::masked_matmul: products where the mask holds, the fill value elsewhere (mask shared by the batch)."""
+    a, mk = golden["mmask_a"], golden["mmask_mask"]
+    tm = dev(mk)
+    got = api.masked_matmul(dev(a), dev(golden["mmask_b2"]), tm, -1.5).cpu().numpy()
+    assert normwise(got, golden["mmask_c_shared"]) < F32_TOL and np.all(got[:, ~mk] == -1.5)
+    got = api.masked_matmul(dev(a), dev(golden["mmask_b3"]), tm, 0.0).cpu().numpy()
+    assert normwise(got, golden["mmask_c_batched"]) < F32_TOL and np.all(got[:, ~mk] == 0.0)
+    # bf16 on the tensor-core path, a strided mask view, fill value rounded as the reference rounds
+    rng = np.random.default_rng(5)
+    m, n, k = 256, 264, 128
+    A = torch.from_numpy(rng.standard_normal((3, m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    B = torch.from_numpy(rng.standard_normal((k, n)).astype(np.float32)).cuda().to(torch.bfloat16)
+    wide = torch.from_numpy(rng.random((m, 2 * n)) < 0.5).cuda()
+    mask = wide[:, :n]
+    out = api.masked_matmul(A, B, mask, 0.3).float().cpu().numpy()
+    want = port.masked_matmul(A.float().cpu().numpy(), B.float().cpu().numpy(), mask.cpu().numpy(), 0.3)
+    keep = mask.cpu().numpy()
+    assert normwise(out[:, keep], want[:, keep]) < H_TOL
+    fill = port.bf16_to_f32(port.f32_to_bf16(np.array([0.3], np.float32)))[0]
+    assert np.all(out[:, ~keep] == fill)
+    with pytest.raises(ValueError):
+        api.masked_matmul(A, B, mask[:, :-1], 0.0)
+    status_ok(L)
+
+
 def test_empty_and_invalid(L, api):
     from ytensor_b200 import _lib
     n0 = L.ytcuda_launch_count()

@@ -39,6 +39,17 @@ def test_doc_matmul_known_answer(golden, port):
     assert np.array_equal(port.matmul(golden["doc_matmul_a"], golden["doc_matmul_b"]), want)
 
 
+def test_masked_matmul(golden, port):
+    a, mk = golden["mmask_a"], golden["mmask_mask"]
+    assert np.array_equal(port.masked_matmul(a, golden["mmask_b2"], mk, -1.5), golden["mmask_c_shared"])
+    assert np.array_equal(port.masked_matmul(a, golden["mmask_b3"], mk, 0.0), golden["mmask_c_batched"])
+    # masked-out entries hold the fill value, masked-in ones the plain product; the two backends agree to round-off
+    c = golden["mmask_c_shared"]
+    assert np.all(c[:, ~mk] == -1.5) and np.all(np.delete(c[:, 5, :], 7, axis=1) == -1.5)
+    assert np.array_equal(c[:, mk], port.matmul(a, golden["mmask_b2"])[:, mk])
+    assert normwise(golden["mmask_c_shared_naive"], c) < 1e-6
+
+
 def test_matmul(golden, port):
     a = golden["mm_a"]
     assert np.array_equal(port.matmul(a, golden["mm_b2"]), golden["mm_c_shared"])

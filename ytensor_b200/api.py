@@ -92,6 +92,42 @@ def matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *,
     return out
 
 
+def masked_matmul(a: torch.Tensor, b: torch.Tensor, mask: torch.Tensor, masked_value: float = 0.0, *,
+                  out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """C[..., i, j] = (A . B)[..., i, j] where mask[i, j], masked_value elsewhere; mask is bool [m, n].
+
+    Mirrors YTensor<T,dim>::masked_matmul with a bool mask (reference src/ytensor_math.inl:318-366): a mask of
+    another shape is refused as the reference refuses it (std::invalid_argument, here ValueError).
+    """
+    _require_cuda(a, b, mask)
+    if a.dim() < 2 or b.dim() < 2:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "masked_matmul: operands must have at least 2 dims")
+    if a.shape[-1] != b.shape[-2]:
+        raise _lib.YtCudaInvalidArgument(
+            _lib.INVALID_ARG, f"masked_matmul: inner dims differ ({a.shape[-1]} vs {b.shape[-2]})")
+    m, k = a.shape[-2:]
+    n = b.shape[-1]
+    if mask.dtype != torch.bool or tuple(mask.shape) != (m, n):
+        raise _lib.YtCudaInvalidArgument(
+            _lib.INVALID_ARG, f"masked_matmul: mask must be bool [{m}, {n}], got {mask.dtype} {tuple(mask.shape)}")
+    if mask.stride(1) != 1:
+        mask = mask.contiguous()
+    bshape = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    ae, be = a.expand(*bshape, m, k), b.expand(*bshape, k, n)
+    out = torch.empty(*bshape, m, n, dtype=out_dtype or a.dtype, device=a.device)
+    av, bv, ov = _batch_view(ae), _batch_view(be), _batch_view(out)
+    if av is None or bv is None or ov is None:
+        for idx in range(bshape[0]):
+            out[idx] = masked_matmul(ae[idx], be[idx], mask, masked_value, out_dtype=out_dtype)
+        return out
+    batch = builtins.max(av[0], bv[0], ov[0])
+    check(lib().ytcuda_gemm_masked(_dt(ae), _dt(out), ae.data_ptr(), be.data_ptr(), out.data_ptr(), m, n, k,
+                                   ae.stride(-2), ae.stride(-1), be.stride(-2), be.stride(-1), out.stride(-2),
+                                   out.stride(-1), batch, av[1], bv[1], ov[1], mask.data_ptr(), mask.stride(0),
+                                   float(masked_value), _stream()))
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """x . weight^T (+ bias), weight [out_features, in_features] (reference src/function/ops.inl:84-105)."""
     y = matmul(x, weight.transpose(-1, -2))

@@ -862,6 +862,22 @@ static int launch_simt(int dtype_in, int dtype_out, const void* A, const void* B
   return YTC_OK;
 }
 
+// C[b][i][j] = masked_value wherever mask[i][j] == 0 (the mask is shared by every batch item); the second half of
+// YTensor::masked_matmul (reference src/ytensor_math.inl:1053-1090 fills the output with maskedValue and lets
+// sgemm_masked write the masked-in products only).
+__global__ void __launch_bounds__(256) gemm_apply_mask_kernel(void* C, int dt, int m, int n, int64_t rsc, int64_t csc,
+                                                              int64_t batch, int64_t bsc, const uint8_t* mask,
+                                                              int64_t mask_rs, float masked_value) {
+  const int64_t per = static_cast<int64_t>(m) * n;
+  const int64_t total = per * batch;
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t b = t / per, r = t - b * per;
+    const int i = static_cast<int>(r / n), j = static_cast<int>(r - static_cast<int64_t>(i) * n);
+    if (mask[static_cast<int64_t>(i) * mask_rs + j] == 0) store_from_f32(C, b * bsc + i * rsc + j * csc, masked_value, dt);
+  }
+}
+
 // Which kernel ytcuda_gemm picks: 0 = automatic, 1 = force FFMA, 2 = require tcgen05.
 static int g_gemm_path = 0;
 
@@ -991,6 +1007,29 @@ static int grow(void** buf, size_t* cap, size_t need) {
 static int64_t span_of(int64_t r, int64_t c, int64_t rs, int64_t cs) { return (r - 1) * rs + (c - 1) * cs + 1; }
 
 }  // namespace ytk
+
+int ytcuda_gemm_masked(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
+                       int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc, int64_t batch,
+                       int64_t bsa, int64_t bsb, int64_t bsc, const void* mask, int64_t mask_row_stride,
+                       float masked_value, void* stream) {
+  YTC_REQUIRE(m >= 0 && n >= 0 && k >= 0 && batch >= 0, "ytcuda_gemm_masked: negative extent");
+  if (m == 0 || n == 0 || batch == 0) return YTC_OK;
+  YTC_REQUIRE(mask != nullptr, "ytcuda_gemm_masked: mask is null");
+  YTC_REQUIRE(mask_row_stride >= n, "ytcuda_gemm_masked: mask row stride %lld shorter than n = %d",
+              (long long)mask_row_stride, n);
+  const int s = ytcuda_gemm(dtype_in, dtype_out, A, B, C, m, n, k, 1.0f, 0.0f, rsa, csa, rsb, csb, rsc, csc, batch, bsa,
+                            bsb, bsc, stream);
+  if (s != YTC_OK) return s;
+  const int64_t total = static_cast<int64_t>(m) * n * batch;
+  const int64_t blocks = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  gemm_apply_mask_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      C, dtype_out, m, n, rsc, csc, batch, bsc, static_cast<const uint8_t*>(mask), mask_row_stride, masked_value);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
 
 extern "C" int ytcuda_gemm_host(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
                                 float alpha, float beta, int64_t rsa, int64_t csa, int64_t rsb, int64_t csb,
