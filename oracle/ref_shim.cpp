@@ -103,6 +103,64 @@ int ytref_masked_matmul_f32(const float* A, const float* B, const unsigned char*
   }
 }
 
+// yt::io::YTensorIO (include/ytensor_io.hpp:90-140): appends one 2-D tensor to a .yt file (created when `append`
+// is 0). dtype: 0 = float32, 1 = bfloat16 (bit patterns), 3 = int32. compress: "" or "zlib".
+int ytref_yt_save(const char* path, int append, const char* name, int dtype, const void* data, int rows, int cols,
+                  const char* compress) {
+  try {
+    yt::io::compressMethod = compress ? compress : "";
+    yt::io::YTensorIO io;
+    if (!io.open(path, append ? yt::io::Append : yt::io::Write)) return 2;
+    bool ok = false;
+    const size_t n = static_cast<size_t>(rows) * cols;
+    if (dtype == 0) {
+      YTensor<float, 2> t(rows, cols);
+      std::memcpy(t.data(), data, n * 4);
+      ok = io.save(t, name);
+    } else if (dtype == 1) {
+      YTensor<yt::bfloat16, 2> t(rows, cols);
+      std::memcpy(t.data(), data, n * 2);
+      ok = io.save(t, name);
+    } else if (dtype == 3) {
+      YTensor<int32_t, 2> t(rows, cols);
+      std::memcpy(t.data(), data, n * 4);
+      ok = io.save(t, name);
+    }
+    io.close();
+    yt::io::compressMethod = "";
+    return ok ? 0 : 3;
+  } catch (const std::exception&) {
+    return 1;
+  }
+}
+
+// Reads a tensor back as float32 (float32 and bfloat16 tensors, as qwen3.cpp:16-44 widens them); returns the
+// element count or a negative error.
+long long ytref_yt_load_f32(const char* path, const char* name, float* out, long long capacity, int* shape2) {
+  try {
+    yt::io::YTensorIO io;
+    if (!io.open(path, yt::io::Read)) return -2;
+    yt::YTensorBase base;
+    if (!io.load(base, name)) return -3;
+    io.close();
+    const long long n = static_cast<long long>(base.size());
+    if (n > capacity || base.shape().size() != 2) return -4;
+    shape2[0] = base.shape()[0];
+    shape2[1] = base.shape()[1];
+    if (base.dtype() == "float32") {
+      std::memcpy(out, base.data<float>(), static_cast<size_t>(n) * 4);
+    } else if (base.dtype() == "bfloat16") {
+      const yt::bfloat16* src = base.data<yt::bfloat16>();
+      for (long long i = 0; i < n; ++i) out[i] = static_cast<float>(src[i]);
+    } else {
+      return -5;
+    }
+    return n;
+  } catch (const std::exception&) {
+    return -1;
+  }
+}
+
 // yt::function::linear: x [rows,k] . W[n,k]^T (+ bias[n])
 int ytref_linear_f32(const float* X, const float* W, const float* bias, float* Y, int rows, int n, int k) {
   try {

@@ -57,6 +57,22 @@ int main() {
     }
     report("matmul shape mismatch throws invalid_argument", threw ? 0.0 : 1.0, 0.5);
   }
+  {  // masked_matmul with a bool mask: products where it holds, the fill value elsewhere
+    auto a = randn<3>({2, 37, 45});
+    auto b = randn<2>({45, 26});
+    YTensor<bool, 2> mask(37, 26);
+    for (int i = 0; i < 37; ++i)
+      for (int j = 0; j < 26; ++j) mask.at(i, j) = ((i * 31 + j * 17) % 5) != 0 && i != 4;
+    report("masked_matmul (bool mask, fill -1.5)", normwise(yt::cuda::masked_matmul(a, b, mask, -1.5f),
+                                                              a.masked_matmul(b, mask, -1.5f)), 1e-5);
+    bool threw = false;
+    try {
+      yt::cuda::masked_matmul(a, b, YTensor<bool, 2>(37, 25), 0.f);
+    } catch (const std::invalid_argument&) {
+      threw = true;
+    }
+    report("masked_matmul mask shape mismatch throws", threw ? 0.0 : 1.0, 0.5);
+  }
   {  // bf16 storage: device accumulates in fp32; the CPU recipe is widen -> fp32 matmul -> narrow
     auto af = randn<2>({128, 256});
     auto bf = randn<2>({256, 192}, 0.0625f);

@@ -5,7 +5,7 @@
 //
 //   #include "ytensor.hpp"
 //   #include "ytensor_cuda.hpp"
-//   auto c = yt::cuda::matmul(a, b);                       // YTensor::matmul
+//   auto c = yt::cuda::matmul(a, b);                       // YTensor::matmul (masked_matmul likewise)
 //   auto o = yt::cuda::scaledDotProductAttention(q, k, v, 0.f, yt::cuda::Causal{kv_len - q_len});
 #pragma once
 #include <cstdint>
@@ -101,6 +101,29 @@ auto matmul(const yt::YTensor<T, dim0>& a, const yt::YTensor<T, dim1>& b) {
   check(ytcuda_gemm_host(dtype_of<T>(), dtype_of<T>(), ac.data(), bc.data(), out.data(), m, n, k, 1.0f, 0.0f,
                          ac.stride_(-2), ac.stride_(-1), bc.stride_(-2), bc.stride_(-1), n, 1, batch,
                          static_cast<int64_t>(m) * k, bsb, static_cast<int64_t>(m) * n));
+  return out;
+}
+
+// YTensor<T, dim>::masked_matmul with a bool mask (reference src/ytensor_math.inl:318-366): products where the mask
+// holds, maskedValue elsewhere; a [..., m, k] with b [k, n], mask [m, n] shared by every batch item.
+template <typename T, int dim0>
+yt::YTensor<T, dim0> masked_matmul(const yt::YTensor<T, dim0>& a, const yt::YTensor<T, 2>& b,
+                                   const yt::YTensor<bool, 2>& mask, const T& maskedValue = T{}) {
+  static_assert(dim0 >= 2, "masked_matmul needs a rank >= 2 left operand");
+  if (a.shape(-1) != b.shape(-2)) throw std::invalid_argument("masked_matmul: inner dimensions do not match");
+  const int m = a.shape(-2), k = a.shape(-1), n = b.shape(-1);
+  if (mask.shape(0) != m || mask.shape(1) != n) throw std::invalid_argument("masked_matmul: mask shape not match");
+  DeviceBuffer da = detail::to_device(a), db = detail::to_device(b), dm = detail::to_device(mask);
+  std::vector<int> oshape = a.shape();
+  oshape[dim0 - 1] = n;
+  yt::YTensor<T, dim0> out(oshape);
+  DeviceBuffer dc(out.size() * sizeof(T));
+  int64_t batch = 1;
+  for (int d = 0; d < dim0 - 2; ++d) batch *= a.shape(d);
+  check(ytcuda_gemm_masked(dtype_of<T>(), dtype_of<T>(), da.get(), db.get(), dc.get(), m, n, k, k, 1, n, 1, n, 1, batch,
+                           static_cast<int64_t>(m) * k, 0, static_cast<int64_t>(m) * n, dm.get(), n,
+                           static_cast<float>(maskedValue), nullptr));
+  dc.download(out.data());
   return out;
 }
 
