@@ -349,6 +349,59 @@ def attention_arm(args) -> None:
         "gpu_launches": int(launches), "clocks": clocks}))
 
 
+def gemm32_arm(args) -> None:
+    """BASELINE configs[0]: fp32 GEMM 1024 x 1024 x 1024 (the reference's own CPU-runnable case). The device forms
+    the product on the tensor cores from three bf16 planes per operand (six partial products side by side along k, one
+    GEMM launch); the L2 is flushed
+    between steps because the 12.6 MB of operands would otherwise stay cached. Single GPU; one JSON line."""
+    import torch
+
+    from ytensor_b200 import _lib, api
+
+    torch.cuda.set_device(0)
+    L = _lib.lib()
+    n = 1024
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn(n, n, device="cuda", generator=g)
+    b = torch.randn(n, n, device="cuda", generator=g)
+    c = torch.empty(n, n, device="cuda")
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
+    flops = 2.0 * n * n * n
+    res = {}
+    for name, mode in (("tensor cores (3 x bf16 planes, 6 products)", 0), ("FFMA kernel", 1)):
+        L.ytcuda_gemm_set_f32_mode(mode)
+        for _ in range(max(args.warmup, 3)):
+            api.matmul(a, b, c)
+        ts = []
+        n0 = L.ytcuda_launch_count()
+        for _ in range(args.steps):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            api.matmul(a, b, c)
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        res[name] = (statistics.median(ts), (L.ytcuda_launch_count() - n0) // args.steps)
+    L.ytcuda_gemm_set_f32_mode(0)
+    _lib.check(L.ytcuda_device_status(None))
+    peaks = measured_peaks()
+    ms, launches = res["tensor cores (3 x bf16 planes, 6 products)"]
+    val = flops / (ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"] / 6.0
+    print(json.dumps({
+        "metric": "fp32_gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (three bf16 planes per operand, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": "configs[0]: fp32 GEMM 1024 x 1024 x 1024", "l2": "flushed between steps (192 MB write)"},
+        "roofline": {"bound": "tensor", "achieved": val, "peak": peak, "unit": "TFLOP/s", "frac": val / peak,
+                     "traffic": None, "kernel": "gemm_tc_kernel over k' = 6 k + gemm_split3_kernel (two launches)",
+                     "peak_source": f"{peaks['source']} (burst cuBLAS bf16 / 6 partial products)",
+                     "algorithmic_flops_per_launch": flops},
+        "ffma_kernel": {"ms_per_step": res["FFMA kernel"][0], "tflops": flops / (res["FFMA kernel"][0] * 1e-3) / 1e12},
+        "gpu_launches": int(launches * args.steps), "clocks": None}))
+
+
 def chain_arm(args) -> None:
     """BASELINE configs[3]: y = bf16(softmax(rmsNorm(x, w, -1, 1e-6) + r, -1)) on x [32,4096,4096] fp32 with the
     residual [1,4096,4096] shared by the batch. `--batch` shrinks the batch for profiling captures."""
@@ -493,14 +546,17 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "attn", "chain", "decode"],
-                    help="gemm (default) is the headline bench line; attn and chain measure configs[2] and configs[3]")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "gemm32", "attn", "chain", "decode"],
+                    help="gemm (default) is the headline bench line; gemm32, attn, chain and decode measure "
+                         "configs[0], [2], [3] and [4]")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-clock-sampling", action="store_true", help="decode workload: do not run nvidia-smi beside it")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling captures only)")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="batch items per step; anything but 64 is a profiling case, not a bench line")
     args = ap.parse_args()
+    if args.workload == "gemm32":
+        return gemm32_arm(args)
     if args.workload == "attn":
         return attention_arm(args)
     if args.workload == "chain":

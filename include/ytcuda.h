@@ -66,6 +66,11 @@ int ytcuda_gemm(int dtype_in, int dtype_out, const void* A, const void* B, void*
  * kernel, 2 = tcgen05 or YTC_UNSUPPORTED. The counterpart of the per-call `backend` argument of
  * YTensor::matmul (include/ytensor_math.hpp:70-73); process-wide, meant for tests. */
 int ytcuda_gemm_set_path(int path);
+/* fp32 products (sgemm, include/kernel/avx2/sgemm.hpp:51-63) on the tensor cores: each operand is split into three
+ * bfloat16 planes (24 mantissa bits) and the six partial products that matter at fp32 precision are laid side by
+ * side along k and accumulated in fp32 by one bf16 GEMM (finite inputs; an infinity gives NaN). 0 = automatic (m, n, k >= 256 with n and k multiples of 8), 1 = never (FFMA kernel), 2 = whenever n and k
+ * are multiples of 8. Process-wide, meant for tests; no counterpart in the reference. */
+int ytcuda_gemm_set_f32_mode(int mode);
 
 /* Tuning knobs of the tcgen05 kernel. a_prefetch_kblocks: how many 64-wide k-blocks an L2 prefetch of the
  * streamed A operand runs ahead of the shared-memory ring (0 = off, the default: it measured slower).

@@ -210,6 +210,57 @@ def test_alpha_beta_bf16(L, api, port):
     assert normwise(out.cpu().numpy(), want) < 1e-5
 
 
+@pytest.mark.parametrize("m,n,k,batch", [(1024, 1024, 1024, 1), (300, 264, 520, 3), (129, 8, 8, 1), (512, 768, 2048, 2)])
+def test_fp32_on_tensor_cores_vs_oracle(L, api, port, m, n, k, batch):
+    """fp32 operands split into three bf16 planes, six tcgen05 products accumulated in fp32: the result keeps fp32
+    accuracy (same 1e-5 bound as the FFMA kernel), with alpha / beta and a shared or batched right operand."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((batch, m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n) if batch != 3 else (batch, k, n)).astype(np.float32)
+    want = port.matmul(a, b)
+    L.ytcuda_gemm_set_f32_mode(2)
+    try:
+        n0 = L.ytcuda_launch_count()
+        got = api.matmul(dev(a), dev(b))
+        launches = L.ytcuda_launch_count() - n0
+        assert normwise(got.cpu().numpy(), want) < F32_TOL
+        assert launches == 3  # two splits and one product over k' = 6 k
+        c0 = rng.standard_normal((batch, m, n)).astype(np.float32)
+        out = dev(c0)
+        api.matmul(dev(a), dev(b), out, alpha=0.5, beta=-2.0)
+        assert normwise(out.cpu().numpy(), 0.5 * want - 2.0 * c0) < F32_TOL
+        # a transposed view of the left operand goes through the same path (the split reads any strides)
+        at = dev(np.ascontiguousarray(a.transpose(0, 2, 1)))
+        assert normwise(api.matmul(at.transpose(1, 2), dev(b)).cpu().numpy(), want) < F32_TOL
+    finally:
+        L.ytcuda_gemm_set_f32_mode(0)
+    # the FFMA kernel on the same inputs, for the record of both paths
+    L.ytcuda_gemm_set_f32_mode(1)
+    try:
+        assert normwise(api.matmul(dev(a), dev(b)).cpu().numpy(), want) < F32_TOL
+    finally:
+        L.ytcuda_gemm_set_f32_mode(0)
+    status_ok(L)
+
+
+def test_fp32_split_keeps_extreme_values(L, api):
+    """Values far apart in magnitude and 24-bit integers: the three-plane split must not lose them. (Non-finite
+    inputs are outside the contract of this path: an infinity times the zero low planes of the other operand gives
+    NaN where fp32 arithmetic gives infinity; what is checked is that the result is still not finite.)"""
+    L.ytcuda_gemm_set_f32_mode(2)
+    try:
+        a = np.zeros((256, 256), np.float32)
+        b = np.eye(256, dtype=np.float32)
+        a[0, :4] = [1.0, 2.0 ** -20, 16777215.0, 3.0e38]
+        a[1, 0] = np.inf
+        a[2, :3] = [1.0 + 2.0 ** -23, -(1.0 + 2.0 ** -23), 1e-30]
+        got = api.matmul(dev(a), dev(b)).cpu().numpy()
+        assert np.array_equal(got[0, :4], a[0, :4]) and not np.isfinite(got[1, 0]) and np.array_equal(got[2, :3], a[2, :3])
+        assert np.all(got[3:] == 0)
+    finally:
+        L.ytcuda_gemm_set_f32_mode(0)
+
+
 def test_masked_matmul_golden_and_16bit(L, api, port, golden):
     """YTensor::masked_matmul: products where the mask holds, the fill value elsewhere (mask shared by the batch)."""
     a, mk = golden["mmask_a"], golden["mmask_mask"]

@@ -29,6 +29,7 @@ SIGNATURES = {
     "ytcuda_gemm": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4 + [_vp]),
     "ytcuda_gemm_masked": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i] + [_i64] * 6 + [_i64] * 4 + [_vp, _i64, _f, _vp]),
     "ytcuda_gemm_set_path": (_i, [_i]),
+    "ytcuda_gemm_set_f32_mode": (_i, [_i]),
     "ytcuda_gemm_set_tuning": (_i, [_i, _i]),
     "ytcuda_gemm_set_pair_mode": (_i, [_i]),
     "ytcuda_gemm_host": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4),

@@ -729,7 +729,8 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
   CUtensorMap tmA, tmB;
   const int a_bcast = (batch > 1 && bsa == 0) ? 1 : 0;
   const int b_bcast = (batch > 1 && bsb == 0) ? 1 : 0;
-  const int BN = (n <= 128) ? 128 : 256;
+  // 256-wide tiles unless the problem is narrow or would leave most SMs without a tile
+  const int BN = (n <= 128 || static_cast<int64_t>((m + 127) / 128) * ((n + 255) / 256) * batch < sm_count() / 2) ? 128 : 256;
   // CTA pairs pay off on large problems; small ones keep one CTA per tile (more tiles to spread over the SMs)
   const bool pair = g_tc_pair != 2 && (g_tc_pair == 1 || (m >= 512 && n >= 256 && k >= 256 &&
                                                         static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) * batch >= 74));
@@ -862,6 +863,54 @@ static int launch_simt(int dtype_in, int dtype_out, const void* A, const void* B
   return YTC_OK;
 }
 
+// x (fp32) = h + m + l with h = bf16(x), m = bf16(x - h), l = bf16(x - h - m): three 16-bit values that together
+// carry the 24 mantissa bits of x (the differences are exact in fp32). The six partial products of an fp32 GEMM
+// that matter, (l,h) (m,m) (h,l) (m,h) (h,m) (h,h) smallest first, are laid side by side along k so that ONE
+// bf16 GEMM with k' = 6 k forms their sum in its fp32 accumulator:
+//   left operand  (is_b == 0, x is [rows = m][cols = k]): out[b][i][c k + j] = plane_a(c) of x[b][i][j]
+//   right operand (is_b == 1, x is [rows = k][cols = n]): out[b][c k + i][j] = plane_b(c) of x[b][i][j]
+// with plane_a = l m h m h h and plane_b = h m l h m h. Non-finite values keep m = l = 0.
+__global__ void __launch_bounds__(256) gemm_split3_kernel(const float* x, int64_t rs, int64_t cs, int64_t bs, int rows,
+                                                          int cols, int64_t batch, int is_b, __nv_bfloat16* out) {
+  const int64_t per = static_cast<int64_t>(rows) * cols;
+  const int64_t total = per * batch;
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t b = t / per, r = t - b * per;
+    const int i = static_cast<int>(r / cols), j = static_cast<int>(r - static_cast<int64_t>(i) * cols);
+    const float v = x[b * bs + i * rs + j * cs];
+    __nv_bfloat16 p[3];  // h, m, l
+    p[0] = __float2bfloat16_rn(v);
+    p[1] = p[2] = __float2bfloat16_rn(0.f);
+    const float fh = __bfloat162float(p[0]);
+    if (isfinite(fh)) {
+      const float r1 = v - fh;
+      p[1] = __float2bfloat16_rn(r1);
+      p[2] = __float2bfloat16_rn(r1 - __bfloat162float(p[1]));
+    }
+    __nv_bfloat16* o = out + b * per * 6;
+    if (is_b) {
+      // chunks h m l h m h
+      const int64_t at = static_cast<int64_t>(i) * cols + j;
+      o[at] = p[0];
+      o[per + at] = p[1];
+      o[2 * per + at] = p[2];
+      o[3 * per + at] = p[0];
+      o[4 * per + at] = p[1];
+      o[5 * per + at] = p[0];
+    } else {
+      // chunks l m h m h h
+      __nv_bfloat16* row = o + static_cast<int64_t>(i) * cols * 6 + j;
+      row[0] = p[2];
+      row[cols] = p[1];
+      row[2 * cols] = p[0];
+      row[3 * cols] = p[1];
+      row[4 * cols] = p[0];
+      row[5 * cols] = p[0];
+    }
+  }
+}
+
 // C[b][i][j] = masked_value wherever mask[i][j] == 0 (the mask is shared by every batch item); the second half of
 // YTensor::masked_matmul (reference src/ytensor_math.inl:1053-1090 fills the output with maskedValue and lets
 // sgemm_masked write the masked-in products only).
@@ -881,6 +930,57 @@ __global__ void __launch_bounds__(256) gemm_apply_mask_kernel(void* C, int dt, i
 // Which kernel ytcuda_gemm picks: 0 = automatic, 1 = force FFMA, 2 = require tcgen05.
 static int g_gemm_path = 0;
 
+// fp32 GEMM on the tensor cores (see gemm_split3_kernel): 0 = automatic (large problems), 1 = never,
+// 2 = whenever the shapes allow.
+static int g_f32_split = 0;
+
+static bool f32_split_ok(int m, int n, int k, int64_t rsc, int64_t csc, int64_t bsc) {
+  if (g_f32_split == 1) return false;
+  if (k % 8 || n % 8 || rsc < 0 || csc < 0 || bsc < 0) return false;
+  if (g_f32_split == 2) return m >= 1 && n >= 8 && k >= 8;
+  return m >= 256 && n >= 256 && k >= 256;
+}
+
+static int launch_f32_split(const float* A, const float* B, float* C, int m, int n, int k, float alpha, float beta,
+                            int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc, int64_t batch,
+                            int64_t bsa, int64_t bsb, int64_t bsc, cudaStream_t st) {
+  const bool b_shared = batch > 1 && bsb == 0;
+  const int64_t a_per = static_cast<int64_t>(m) * k * 6, b_per = static_cast<int64_t>(k) * n * 6;  // bf16 elements
+  // batch items per pass so that the expanded operands stay below about 2 GiB
+  int64_t chunk = batch;
+  const int64_t per_item = 2 * (a_per + (b_shared ? 0 : b_per));
+  const int64_t budget = (int64_t{2} << 30) - (b_shared ? 2 * b_per : 0);
+  if (per_item * chunk > budget) chunk = budget / per_item > 0 ? budget / per_item : 1;
+  const size_t a_bytes = (static_cast<size_t>(2) * a_per * chunk + 255) / 256 * 256;
+  const size_t b_bytes = static_cast<size_t>(2) * b_per * (b_shared ? 1 : chunk);
+  char* ws = static_cast<char*>(device_workspace(a_bytes + b_bytes));
+  if (!ws) {
+    set_last_error("ytcuda_gemm: could not allocate %zu bytes for the bf16 form of an fp32 product", a_bytes + b_bytes);
+    return YTC_CUDA_ERROR;
+  }
+  __nv_bfloat16* a6 = reinterpret_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* b6 = reinterpret_cast<__nv_bfloat16*>(ws + a_bytes);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  auto split = [&](const float* x, int64_t rs, int64_t cs, int64_t bs, int rows, int cols, int64_t nb, int is_b,
+                   __nv_bfloat16* out) {
+    const int64_t blocks = (static_cast<int64_t>(rows) * cols * nb + 255) / 256;
+    gemm_split3_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, rs, cs, bs, rows, cols, nb,
+                                                                                            is_b, out);
+    count_launch();
+  };
+  if (b_shared) split(B, rsb, csb, 0, k, n, 1, 1, b6);
+  for (int64_t b0 = 0; b0 < batch; b0 += chunk) {
+    const int64_t nb = batch - b0 < chunk ? batch - b0 : chunk;
+    split(A + b0 * bsa, rsa, csa, bsa, m, k, nb, 0, a6);
+    if (!b_shared) split(B + b0 * bsb, rsb, csb, bsb, k, n, nb, 1, b6);
+    YTC_CUDA(cudaGetLastError());
+    const int s = launch_tc(YTC_BF16, YTC_F32, a6, b6, C + b0 * bsc, m, n, 6 * k, alpha, beta, /*a_mn=*/0, 6 * k,
+                            /*b_mn=*/1, n, rsc, csc, nb, a_per, b_shared ? 0 : b_per, bsc, st);
+    if (s != YTC_OK) return s;
+  }
+  return YTC_OK;
+}
+
 }  // namespace ytk
 
 using namespace ytk;
@@ -897,6 +997,12 @@ int ytcuda_gemm_set_tuning(int a_prefetch_kblocks, int split_loads) {
   YTC_REQUIRE(a_prefetch_kblocks >= 0 && a_prefetch_kblocks <= 64, "ytcuda_gemm_set_tuning: prefetch distance outside [0, 64]");
   g_tc_a_prefetch = a_prefetch_kblocks;
   g_tc_split_loads = split_loads ? 1 : 0;
+  return YTC_OK;
+}
+
+int ytcuda_gemm_set_f32_mode(int mode) {
+  YTC_REQUIRE(mode >= 0 && mode <= 2, "ytcuda_gemm_set_f32_mode: mode must be 0, 1 or 2");
+  g_f32_split = mode;
   return YTC_OK;
 }
 
@@ -929,6 +1035,9 @@ int ytcuda_gemm(int dtype_in, int dtype_out, const void* A, const void* B, void*
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;
   }
+  if (dtype_in == YTC_F32 && dtype_out == YTC_F32 && g_gemm_path != 1 && f32_split_ok(m, n, k, rsc, csc, bsc))
+    return launch_f32_split(static_cast<const float*>(A), static_cast<const float*>(B), static_cast<float*>(C), m, n, k,
+                            alpha, beta, rsa, csa, rsb, csb, rsc, csc, batch, bsa, bsb, bsc, st);
   int a_mn = 0, b_mn = 0;
   bool tc = (dtype_in != YTC_F32) && g_gemm_path != 1;
   if (tc) {
