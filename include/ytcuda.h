@@ -250,10 +250,19 @@ int ytcuda_qwen3_set_allreduce(void* handle, int (*fn)(void* buf, int64_t count,
 int ytcuda_qwen3_reset(void* handle);
 int ytcuda_qwen3_cache_len(void* handle);
 /* How a forward of ONE new token per sequence runs: 0 = automatic (one persistent cooperative kernel for the whole
- * step where it applies: no tensor parallelism, batch <= 8), 1 = one launch per operator as for longer inputs,
+ * step where it applies: batch <= 8, and under tensor parallelism connected exchange buffers, see
+ * ytcuda_qwen3_tp_export), 1 = one launch per operator as for longer inputs,
  * 2 = the persistent kernel or YTC_UNSUPPORTED. Both forms compute the operator sequence of
  * Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has no counterpart in the reference. */
 int ytcuda_qwen3_set_decode_path(void* handle, int path);
+/* Tensor-parallel decode steps without a host-side collective: every rank exports the CUDA IPC handle (64 bytes) of
+ * its exchange buffer, the caller distributes the handles (one all-gather at start-up), and every rank imports its
+ * peers'. From then on a forward of one token per sequence (batch <= 8) is ONE kernel per rank that all-reduces the
+ * partial sums of the o and down projections itself, by loads from the peers' buffers over NVLink. All ranks must
+ * call forward the same number of times. The all-reduce callback is still used for longer inputs. No counterpart in
+ * the reference (single process). */
+int ytcuda_qwen3_tp_export(void* handle, void* ipc_handle_64);
+int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64);
 /* ids [batch, len] int32 (device) -> logits of the last position [batch, rank's vocab rows] fp32 (device); appends
  * len tokens to the KV caches (Qwen3ForCausalLM::forward, qwen3.cpp:449-457). */
 int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream);

@@ -1,5 +1,6 @@
 """GPU (2 devices): the tensor-parallel decoder gives the reference's logits and greedy tokens.
-Two child processes, one per GPU, NCCL all-reduce after the attention output and down projections.
+Two child processes, one per GPU; the partial sums after the attention output and down projections are reduced by NCCL
+(prefill, and decode with one launch per operator) or inside the persistent decode-step kernel over peer memory.
 Skipped when fewer than two devices are visible."""
 import os
 import sys
@@ -27,23 +28,31 @@ def _worker(rank, world, port, ret):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         g = np.load(ROOT / "tests" / "golden" / "golden_qwen3.npz")
-        # small model: full logits against the reference, every rank holding its vocabulary rows
+        # small model: full logits against the reference, every rank holding its vocabulary rows; first with the
+        # decode steps as one kernel per rank (all-reduce inside it, through the peers' exchange buffers), then with
+        # one launch per operator and the NCCL all-reduce callback
         cfg = Q.Qwen3Config(**SMALL)
-        m = Q.Qwen3ForCausalLM(cfg, batch=2, tp_rank=rank, tp_world=world)
-        m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
         want = g["small_logits_b2"]
         ids = torch.from_numpy(g["small_ids_b2"]).cuda()
-        logits = m.forward(ids)
-        for step in range(6):
-            got = logits.cpu().numpy()
-            ref = want[step][:, m.v0:m.v1]
-            err = np.abs(got - ref).max() / np.abs(want[step]).max()
-            assert err < 1e-4, (step, err)
-            tok, _ = m.argmax(logits)
-            assert np.array_equal(tok.cpu().numpy(), want[step].argmax(1))
-            if step < 5:
-                logits = m.forward(tok.reshape(2, 1).contiguous())
-        m.close()
+        for path in (2, 1):
+            m = Q.Qwen3ForCausalLM(cfg, batch=2, tp_rank=rank, tp_world=world)
+            m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
+            m.set_decode_path(path)
+            logits = m.forward(ids)
+            for step in range(6):
+                got = logits.cpu().numpy()
+                ref = want[step][:, m.v0:m.v1]
+                err = np.abs(got - ref).max() / np.abs(want[step]).max()
+                assert err < 1e-4, (path, step, err)
+                tok, _ = m.argmax(logits)
+                assert np.array_equal(tok.cpu().numpy(), want[step].argmax(1))
+                if step < 5:
+                    n0 = Q._lib.lib().ytcuda_launch_count()
+                    logits = m.forward(tok.reshape(2, 1).contiguous())
+                    launched = Q._lib.lib().ytcuda_launch_count() - n0
+                    assert (launched == 1) if path == 2 else (launched > 10), (path, launched)
+            assert Q._lib.lib().ytcuda_device_status(None) == 0
+            m.close()
         # Qwen3-0.6B shape: the first 16 greedy tokens of the reference
         cfg = Q.Qwen3Config(max_position_embeddings=768)
         m = Q.Qwen3ForCausalLM(cfg, batch=1, tp_rank=rank, tp_world=world)

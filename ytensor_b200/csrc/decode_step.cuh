@@ -23,6 +23,11 @@
 // per chunk and head in global memory; the o-projection phase combines the chunks while it stages its input. The
 // K / V rows of a unit are requested from HBM into the L2 one phase earlier.
 //
+// Tensor parallelism: every rank runs this kernel on its share of the heads, FFN columns and vocabulary rows. The
+// partial sums of the o and down projections are all-reduced inside the kernel: each rank writes its partial vector
+// into a mailbox in its own memory, a barrier over the local CTAs and the peers (flag words written with system-scope
+// release stores over NVLink) follows, and then every rank adds the mailboxes of all ranks in rank order.
+//
 // The barrier is a counter in global memory (one arrival per CTA, acquire loads while waiting). The launch is
 // cooperative, so all CTAs are resident; the wait is still bounded: when the cycle budget runs out the CTA raises
 // the device status word and every CTA leaves at its next barrier.
@@ -38,6 +43,7 @@ constexpr int DS_THREADS = 256;
 constexpr int DS_WARPS = DS_THREADS / 32;
 constexpr int DS_MAX_B = 8;        // sequences per step (activation rows kept in shared memory)
 constexpr int DS_MAX_G = 4;        // query heads per kv head
+constexpr int DS_MAX_TP = 8;       // tensor-parallel ranks (one GPU each, peers reached by NVLink loads / stores)
 // attention scratch of a CTA: q of the group, and per warp (m, l, o[128]) for every head of the group
 constexpr int DS_ATT_FLOATS = DS_MAX_G * 128 + 2 * DS_WARPS * DS_MAX_G + DS_WARPS * DS_MAX_G * 128;  // for G = DS_MAX_G
 constexpr long long DS_WAIT_CYCLES = 2000000000ll;
@@ -62,6 +68,16 @@ struct DecodeStepParams {
   unsigned int* sync;  // grid barrier counter
   int chunks, keys_per_chunk;
   int* status;
+  // Tensor parallelism (tp_world > 1): heads, kv_heads, inter and vocab_rows above are this rank's share. The partial
+  // sums of the o and down projections are exchanged through "mailboxes" in peer-visible device memory:
+  //   mail[r]   rank r's mailbox, two slots of [DS_MAX_B][hidden] floats (slot = exchange number & 1)
+  //   flags[r]  rank r's arrival words: flags[r][q] = number of the last exchange rank q has finished writing
+  //   go        this rank's release word for its own CTAs
+  int tp_rank, tp_world;
+  float* mail[DS_MAX_TP];
+  unsigned int* flags[DS_MAX_TP];
+  unsigned int* go;
+  unsigned int ar_base;  // exchanges completed before this launch
 };
 
 __device__ __forceinline__ float ds_ldcg(const float* p) { return __ldcg(p); }
@@ -90,6 +106,86 @@ __device__ __forceinline__ bool ds_grid_sync(const DecodeStepParams& p, unsigned
     if (v & 0x80000000u) ok = 0;
   }
   return __syncthreads_and(ok) != 0;
+}
+
+// Grid-wide barrier that also waits for every tensor-parallel peer: exchange number `seq` is complete on all ranks
+// (their mailbox writes are visible) when it returns true. CTA 0 collects the local arrivals, tells every peer by a
+// system-scope release store into the peer's flag words, waits for the peers' words in its own memory, and then
+// releases the other CTAs of this GPU through `go`. All waits are bounded.
+__device__ __forceinline__ bool ds_cross_sync(const DecodeStepParams& p, unsigned int& epoch, unsigned int seq) {
+  __syncthreads();
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    epoch += gridDim.x;
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
+    const long long t0 = clock64();
+    unsigned int v;
+    if (blockIdx.x == 0) {
+      while (true) {  // every CTA of this GPU has written its part of the mailbox
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sync) : "memory");
+        if (v >= epoch) break;
+        if (clock64() - t0 > DS_WAIT_CYCLES) {
+          v = 0x80000000u;
+          break;
+        }
+      }
+      if (!(v & 0x80000000u)) {
+        __threadfence_system();
+        for (int q = 0; q < p.tp_world; ++q)
+          if (q != p.tp_rank)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[q] + p.tp_rank), "r"(seq) : "memory");
+        for (int q = 0; q < p.tp_world && !(v & 0x80000000u); ++q) {
+          if (q == p.tp_rank) continue;
+          while (true) {
+            unsigned int f;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(p.flags[p.tp_rank] + q) : "memory");
+            if (f >= seq) break;
+            if (clock64() - t0 > DS_WAIT_CYCLES) {
+              v = 0x80000000u;
+              break;
+            }
+          }
+        }
+      }
+      if (v & 0x80000000u) {
+        atomicExch(p.status, YTC_TIMEOUT);
+        atomicOr(p.sync, 0x80000000u);
+        ok = 0;
+      } else {
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.go), "r"(seq) : "memory");
+      }
+    } else {
+      while (true) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.go) : "memory");
+        if (v >= seq) break;
+        unsigned int c;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(p.sync) : "memory");
+        if ((c & 0x80000000u) || clock64() - t0 > DS_WAIT_CYCLES) {
+          atomicExch(p.status, YTC_TIMEOUT);
+          atomicOr(p.sync, 0x80000000u);
+          ok = 0;
+          break;
+        }
+      }
+    }
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// x[b][:] += sum over ranks of the partial sums in slot `slot` of every rank's mailbox, in rank order (every rank
+// forms bitwise the same sum); the elements are spread over the threads of the grid.
+__device__ __forceinline__ void ds_reduce_mailboxes(const DecodeStepParams& p, int slot) {
+  const int n = p.B * p.hidden;
+  const int64_t off = static_cast<int64_t>(slot) * DS_MAX_B * p.hidden;
+  for (int e = blockIdx.x * DS_THREADS + threadIdx.x; e < n; e += gridDim.x * DS_THREADS) {
+    float s = ds_ldcg(p.x + e);
+    for (int r = 0; r < p.tp_world; ++r) {
+      float v;
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p.mail[r] + off + e) : "memory");
+      s += v;
+    }
+    p.x[e] = s;
+  }
 }
 
 // Asks the L2 for the rows n = gw, gw + GW, ... < N of W (K bf16 each); nothing is held in registers.
@@ -633,6 +729,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
   const int qkv_w = (p.heads + 2 * p.kv_heads) * D;
   const int attn_w = p.heads * D;
   unsigned int epoch = 0;
+  unsigned int ar = 0;  // exchanges between the tensor-parallel ranks done in this launch
 
   // ---- embedding gather: x[b, :] = float(embed[ids[b], :])
   {
@@ -695,7 +792,16 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
     // ---- x += attn . Wo^T
     L = DsLinear{W.o, H, attn_w, 2, p.heads, p.kv_heads, p.chunks, p.part, nullptr, 1, p.x, H, {W.down, nullptr},
                  {H, 0}, {p.inter, 0}, nullptr, nullptr, 0};
+    if (p.tp_world > 1) {  // partial sums over this rank's heads go to the mailbox, the ranks' sums to x
+      L.epi = 0;
+      L.dst = p.mail[p.tp_rank] + static_cast<int64_t>((p.ar_base + ar) & 1) * DS_MAX_B * H;
+    }
     ds_linear_phase<MT>(L, xs, B, p.eps);
+    if (p.tp_world > 1) {
+      if (!ds_cross_sync(p, epoch, p.ar_base + ar + 1)) return;
+      ds_reduce_mailboxes(p, (p.ar_base + ar) & 1);
+      ++ar;
+    }
     if (!ds_grid_sync(p, epoch)) return;
 
     // ---- act = swish(gate) * up, gate / up = rmsNorm(x) . Wgu^T (rows i and inter + i of the fused weight)
@@ -714,7 +820,16 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
     // ---- x += act . Wdown^T
     L = DsLinear{W.down, H, p.inter, 1, 0, 0, 0, p.act, nullptr, 1, p.x, H, {nullptr, nullptr}, {0, 0}, {0, 0},
                  nullptr, nullptr, 0};
+    if (p.tp_world > 1) {
+      L.epi = 0;
+      L.dst = p.mail[p.tp_rank] + static_cast<int64_t>((p.ar_base + ar) & 1) * DS_MAX_B * H;
+    }
     ds_linear_phase<MT>(L, xs, B, p.eps);
+    if (p.tp_world > 1) {
+      if (!ds_cross_sync(p, epoch, p.ar_base + ar + 1)) return;
+      ds_reduce_mailboxes(p, (p.ar_base + ar) & 1);
+      ++ar;
+    }
     if (!ds_grid_sync(p, epoch)) return;
   }
 

@@ -16,6 +16,7 @@
 #include <math_constants.h>
 
 #include <cmath>
+#include <cstring>
 #include <string>
 #include <vector>
 
@@ -269,8 +270,21 @@ struct Qwen3Model {
   float* ds_part = nullptr;         // attention partials
   unsigned int* ds_sync = nullptr;  // barrier counter + per (sequence, kv head) chunk counters
   int ds_smem_set = 0;
+  // exchange buffers of the tensor-parallel step kernel: this rank's (mailbox, flag words, release word) and the
+  // peers' buffers opened through CUDA IPC
+  char* tp_comm = nullptr;
+  char* tp_peer[DS_MAX_TP] = {};
+  bool tp_ready = false;
+  unsigned int ar_seq = 0;  // exchanges completed so far (the same on every rank)
   std::vector<void*> owned;
 };
+
+// Layout of a rank's exchange buffer: two mailbox slots of [DS_MAX_B][hidden] floats, then (256-byte aligned) the
+// DS_MAX_TP flag words the peers write and, 64 bytes further, the release word of this rank's own CTAs.
+static size_t tp_flags_offset(int hidden) {
+  return (static_cast<size_t>(2) * DS_MAX_B * hidden * sizeof(float) + 255) / 256 * 256;
+}
+static size_t tp_comm_bytes(int hidden) { return tp_flags_offset(hidden) + 256; }
 
 static int dev_alloc(Qwen3Model* m, void** p, size_t bytes) {
   YTC_CUDA(cudaMalloc(p, bytes));
@@ -462,6 +476,8 @@ void* ytcuda_qwen3_create(int hidden, int layers, int vocab, int inter, int head
 void ytcuda_qwen3_destroy(void* handle) {
   auto* m = static_cast<Qwen3Model*>(handle);
   if (!m) return;
+  for (char* peer : m->tp_peer)
+    if (peer) cudaIpcCloseMemHandle(peer);
   for (void* p : m->owned) cudaFree(p);
   delete m;
 }
@@ -512,6 +528,45 @@ int ytcuda_qwen3_reset(void* handle) {
   m->cur_len = 0;
   return YTC_OK;
 }
+// Allocates this rank's exchange buffer for the tensor-parallel step kernel and returns its CUDA IPC handle
+// (64 bytes) for the other ranks to open.
+int ytcuda_qwen3_tp_export(void* handle, void* ipc_handle_64) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m && ipc_handle_64, "ytcuda_qwen3_tp_export: null argument");
+  YTC_REQUIRE(m->tp_world > 1 && m->tp_world <= DS_MAX_TP, "ytcuda_qwen3_tp_export: needs 2..%d ranks", DS_MAX_TP);
+  if (!m->tp_comm) {
+    const size_t bytes = tp_comm_bytes(m->hidden);
+    int s = dev_alloc(m, reinterpret_cast<void**>(&m->tp_comm), bytes);
+    if (s != YTC_OK) return s;
+    YTC_CUDA(cudaMemset(m->tp_comm, 0, bytes));
+  }
+  cudaIpcMemHandle_t h;
+  YTC_CUDA(cudaIpcGetMemHandle(&h, m->tp_comm));
+  static_assert(sizeof(h) == 64, "CUDA IPC handles are 64 bytes");
+  std::memcpy(ipc_handle_64, &h, sizeof(h));
+  return YTC_OK;
+}
+
+// Opens rank `rank`'s exchange buffer (its own rank is accepted and ignored). Once every peer is open, decode
+// steps of batch <= 8 run as the single persistent kernel with the all-reduces inside it.
+int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m && ipc_handle_64, "ytcuda_qwen3_tp_import: null argument");
+  YTC_REQUIRE(m->tp_comm, "ytcuda_qwen3_tp_import: call ytcuda_qwen3_tp_export first");
+  YTC_REQUIRE(rank >= 0 && rank < m->tp_world, "ytcuda_qwen3_tp_import: rank %d out of range", rank);
+  if (rank != m->tp_rank && !m->tp_peer[rank]) {
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, ipc_handle_64, sizeof(h));
+    void* ptr = nullptr;
+    YTC_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    m->tp_peer[rank] = static_cast<char*>(ptr);
+  }
+  bool all = true;
+  for (int r = 0; r < m->tp_world; ++r) all = all && (r == m->tp_rank || m->tp_peer[r]);
+  m->tp_ready = all;
+  return YTC_OK;
+}
+
 // 0: automatic (the persistent step kernel where it applies), 1: always one launch per operator, 2: the persistent
 // step kernel or YTC_UNSUPPORTED.
 int ytcuda_qwen3_set_decode_path(void* handle, int path) {
@@ -552,10 +607,11 @@ static int ensure_activations(Qwen3Model* m, int64_t rows) {
 
 constexpr int DS_MAX_CHUNKS = 64;
 
+
 // Whether the persistent step kernel covers this model (one new token per sequence is checked by the caller).
 static bool decode_step_supported(const Qwen3Model* m) {
   const int groups = m->heads / m->kv_heads;
-  return m->tp_world == 1 && m->batch <= DS_MAX_B && m->head_dim == 128 && (groups == 1 || groups == 2 || groups == 4) &&
+  return (m->tp_world == 1 || m->tp_ready) && m->batch <= DS_MAX_B && m->head_dim == 128 && (groups == 1 || groups == 2 || groups == 4) &&
          m->hidden % 8 == 0 && m->inter % 8 == 0;
 }
 
@@ -566,7 +622,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   const size_t sync_words = 1;
   if (!m->ds_part) {
     int s;
-    const size_t part = static_cast<size_t>(B) * m->kv_heads * DS_MAX_CHUNKS * groups * (4 + D) * sizeof(float);
+    const size_t part = static_cast<size_t>(B) * m->l_kv_heads * DS_MAX_CHUNKS * groups * (4 + D) * sizeof(float);
     if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->ds_part), part)) != YTC_OK) return s;
     if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->ds_sync), sync_words * sizeof(unsigned int))) != YTC_OK) return s;
     if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->ds_lw), m->layers * sizeof(DsLayer))) != YTC_OK) return s;
@@ -581,27 +637,37 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
     YTC_CUDA(cudaStreamSynchronize(st));  // `h` leaves scope
     m->ds_lw_stale = false;
   }
-  int kmax = m->hidden > m->inter ? m->hidden : m->inter;
-  if (m->heads * D > kmax) kmax = m->heads * D;
+  int kmax = m->hidden > m->l_inter ? m->hidden : m->l_inter;
+  if (m->l_heads * D > kmax) kmax = m->l_heads * D;
   // the kernel is instantiated for 1, 2, 4 or 8 activation rows and reads that many rows of shared memory
   const int mt = B == 1 ? 1 : (B == 2 ? 2 : (B <= 4 ? 4 : 8));
   int smem = mt * kmax * static_cast<int>(sizeof(float));
   const int att = DS_ATT_FLOATS * static_cast<int>(sizeof(float));  // the attention phase's scratch
   if (smem < att) smem = att;
   DecodeStepParams p{};
-  p.B = B; p.hidden = m->hidden; p.layers = m->layers; p.heads = m->heads; p.kv_heads = m->kv_heads;
-  p.inter = m->inter; p.vocab_rows = m->l_vocab; p.vocab = m->vocab; p.max_pos = m->max_pos; p.pos = m->cur_len;
+  p.B = B; p.hidden = m->hidden; p.layers = m->layers; p.heads = m->l_heads; p.kv_heads = m->l_kv_heads;
+  p.inter = m->l_inter; p.vocab_rows = m->l_vocab; p.vocab = m->vocab; p.max_pos = m->max_pos; p.pos = m->cur_len;
   p.eps = m->eps; p.scale = 1.0f / std::sqrt(static_cast<float>(D));
   p.ids = ids; p.embed = m->embed; p.lm_head = m->lm_head; p.final_norm = m->final_norm; p.lw = m->ds_lw;
   p.cos_t = m->cos_t; p.sin_t = m->sin_t; p.k_cache = m->k_cache; p.v_cache = m->v_cache;
-  p.cache_layer = static_cast<size_t>(B) * m->kv_heads * m->max_pos * D;
+  p.cache_layer = static_cast<size_t>(B) * m->l_kv_heads * m->max_pos * D;
+  p.tp_rank = m->tp_rank; p.tp_world = m->tp_world; p.ar_base = m->ar_seq;
+  if (m->tp_world > 1) {
+    const size_t flags_at = tp_flags_offset(m->hidden);
+    for (int r = 0; r < m->tp_world; ++r) {
+      char* base = r == m->tp_rank ? m->tp_comm : m->tp_peer[r];
+      p.mail[r] = reinterpret_cast<float*>(base);
+      p.flags[r] = reinterpret_cast<unsigned int*>(base + flags_at);
+    }
+    p.go = reinterpret_cast<unsigned int*>(m->tp_comm + flags_at) + 16;
+  }
   p.x = m->x; p.qkv = m->qkv; p.attn = m->attn; p.act = m->act; p.logits = logits; p.part = m->ds_part;
   p.sync = m->ds_sync; p.status = device_status_word();
   const int keys = m->cur_len + 1;
   // Key chunks of 128 keys (8 per warp), fewer and longer ones when that would be more units than CTAs or more
   // than DS_MAX_CHUNKS chunks.
   int n_chunks = (keys + 127) / 128;
-  const int fit = sm_count() / (B * m->kv_heads);
+  const int fit = sm_count() / (B * m->l_kv_heads);
   if (n_chunks > fit) n_chunks = fit > 0 ? fit : 1;
   if (n_chunks > DS_MAX_CHUNKS) n_chunks = DS_MAX_CHUNKS;
   int per = (keys + n_chunks - 1) / n_chunks;
@@ -626,6 +692,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   }
   YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(DS_THREADS), args, smem, st));
   count_launch();
+  if (m->tp_world > 1) m->ar_seq += 2u * static_cast<unsigned int>(m->layers);
   return YTC_OK;
 }
 
@@ -644,7 +711,8 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   for (const LayerW& L : m->lw)
     YTC_REQUIRE(L.qkv && L.o && L.gate_up && L.down && L.q_norm && L.k_norm && L.norm1 && L.norm2,
                 "ytcuda_qwen3_forward: a layer weight is not set");
-  YTC_REQUIRE(m->tp_world == 1 || m->allreduce, "ytcuda_qwen3_forward: tensor parallel needs an all-reduce callback");
+  YTC_REQUIRE(m->tp_world == 1 || m->allreduce || (len == 1 && m->tp_ready && m->decode_path != 1),
+              "ytcuda_qwen3_forward: tensor parallel needs an all-reduce callback");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int B = m->batch, D = m->head_dim, Hd = m->hidden;
   const int64_t rows = static_cast<int64_t>(B) * len;
@@ -658,8 +726,8 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     return YTC_OK;
   }
   if (len == 1 && m->decode_path == 2) {
-    set_last_error("ytcuda_qwen3_forward: the single-kernel decode step needs batch <= %d, no tensor "
-                   "parallelism and 1, 2 or %d query heads per kv head", DS_MAX_B, DS_MAX_G);
+    set_last_error("ytcuda_qwen3_forward: the single-kernel decode step needs batch <= %d, 1, 2 or %d query heads "
+                   "per kv head and, under tensor parallelism, connected exchange buffers", DS_MAX_B, DS_MAX_G);
     return YTC_UNSUPPORTED;
   }
   const int qkv_w = (m->l_heads + 2 * m->l_kv_heads) * D;

@@ -106,7 +106,8 @@ _ALLREDUCE_T = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64, C.c_void_p)
 class Qwen3ForCausalLM:
     """Device model for `batch` sequences; rank `tp_rank` of `tp_world` tensor-parallel ranks."""
 
-    def __init__(self, cfg: Qwen3Config, batch: int = 1, tp_rank: int = 0, tp_world: int = 1, group=None):
+    def __init__(self, cfg: Qwen3Config, batch: int = 1, tp_rank: int = 0, tp_world: int = 1, group=None,
+                 connect_peers: bool = True):
         import torch
         self.torch = torch
         self.cfg, self.batch, self.tp_rank, self.tp_world, self.group = cfg, batch, tp_rank, tp_world, group
@@ -138,6 +139,21 @@ class Qwen3ForCausalLM:
 
             self._cb = _ALLREDUCE_T(allreduce)
             check(self.L.ytcuda_qwen3_set_allreduce(self.h, C.cast(self._cb, C.c_void_p), None))
+            if batch <= 8 and connect_peers:
+                self._connect_peers()
+
+    def _connect_peers(self) -> None:
+        """Exchange the CUDA IPC handles of the ranks' exchange buffers (one all-gather) so that decode steps can run
+        as one kernel per rank with the all-reduces inside it (ytcuda_qwen3_tp_export / _import)."""
+        import torch.distributed as dist
+        mine = (C.c_char * 64)()
+        check(self.L.ytcuda_qwen3_tp_export(self.h, C.cast(mine, C.c_void_p)))
+        handles = [None] * self.tp_world
+        dist.all_gather_object(handles, bytes(mine.raw), group=self.group)
+        for r, hb in enumerate(handles):
+            buf = (C.c_char * 64).from_buffer_copy(hb)
+            check(self.L.ytcuda_qwen3_tp_import(self.h, r, C.cast(buf, C.c_void_p)))
+        dist.barrier(group=self.group)
 
     def _wrap(self, ptr: int, count: int):
         """A torch view of `count` floats of device memory owned by the model handle (for NCCL)."""
