@@ -218,8 +218,9 @@ int ytcuda_embedding(const void* table_bf16, const int32_t* ids, float* out, int
                      void* stream);
 
 /* y[m, n] (+)= x[m, k] . W[n, k]^T with fp32 x, y and bf16 W [n, k] row-major: yt::function::linear
- * (src/function/ops.inl:84-91) with the weight left in its storage type. Up to 32 rows: one pass over W with FFMA
- * (decode). More rows: x is split into two bf16 planes (hi + lo) and multiplied on tcgen05; `hi_lo_scratch` must then
+ * (src/function/ops.inl:84-91) with the weight left in its storage type. Up to 8 rows: one pass over W with FFMA
+ * (decode). More rows: x is split into two bf16 planes (hi + lo) and multiplied on tcgen05 (up to 128 rows with the
+ * k range cut into pieces that run side by side, partial sums added in a fixed order); `hi_lo_scratch` must then
  * hold 4*m*k bytes of device memory. */
 int ytcuda_linear_w16(const float* x, int64_t x_row_stride, const void* w_bf16, float* y, int64_t y_row_stride,
                       int64_t m, int n, int k, int accumulate, void* hi_lo_scratch, void* stream);

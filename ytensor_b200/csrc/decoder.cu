@@ -56,6 +56,11 @@ constexpr int SK_WARPS = 4;
 constexpr int SK_ROWS = 2;
 constexpr int SK_KC = 1024;
 constexpr int SK_UNROLL = 4;  // 256-column trips fetched together per lane
+// Rows up to which the FFMA kernel is used; above, the activations are split into two bf16 planes and the tensor
+// cores do the product (the FFMA kernel's time grows with the rows, the tensor-core GEMM's hardly does).
+#ifndef SK_MAX_ROWS
+#define SK_MAX_ROWS 8
+#endif
 
 template <int MT>
 __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(const float* __restrict__ x, int64_t x_rs,
@@ -141,6 +146,19 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(const floa
           *dst = accumulate ? *dst + acc[r][m] : acc[r][m];
         }
     }
+  }
+}
+
+// y[r][c] (+)= sum over p of part[p][r][c] (partials of [rows][cols] floats, added in index order).
+__global__ void __launch_bounds__(256) sum_partials_kernel(const float* part, int n_part, int64_t mn, float* y,
+                                                           int64_t y_rs, int cols, int accumulate) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < mn;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float s = 0.f;
+    for (int p = 0; p < n_part; ++p) s += part[p * mn + i];
+    const int64_t r = i / cols, c = i - r * cols;
+    float* dst = y + r * y_rs + c;
+    *dst = accumulate ? *dst + s : s;
   }
 }
 
@@ -296,7 +314,7 @@ static int dev_alloc(Qwen3Model* m, void** p, size_t bytes) {
 static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_t* W, float* y, int64_t y_rs, int64_t M,
                       int N, int K, bool accumulate, cudaStream_t st) {
   if (M <= 0 || N <= 0) return YTC_OK;
-  if (M <= 32) {
+  if (M <= SK_MAX_ROWS) {
     const int blocks = (N + SK_WARPS * SK_ROWS - 1) / (SK_WARPS * SK_ROWS);
     const int Mi = static_cast<int>(M);
 #define SK_LAUNCH(MT)                                                                                          \
@@ -335,6 +353,35 @@ static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_
   split_hi_lo_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, x_rs, m->hi, m->lo, M, K);
   count_launch();
   YTC_CUDA(cudaGetLastError());
+  // Few rows (decode with a larger batch): there are only N / 128 output tiles, too few to keep the SMs busy and the
+  // weight stream at bandwidth. The k range is cut into pieces that run as "batch" items of one GEMM launch (a k
+  // offset is a plain pointer offset for both K-major operands), each writing its own partial result, and a small
+  // kernel adds the partials of both planes in a fixed order.
+  if (M <= 128 && K % 128 == 0 && K >= 256) {
+    int splits = K / 128;
+    const int tiles = (N + 127) / 128;
+    while (splits > 1 && (splits % 2 == 0) && tiles * (splits / 2) >= 2 * sm_count()) splits /= 2;
+    const int kc = K / splits;
+    const size_t part_elems = static_cast<size_t>(2) * splits * M * N;
+    float* part = static_cast<float*>(device_workspace(part_elems * sizeof(float)));
+    if (!part) {
+      set_last_error("linear: cannot allocate %zu bytes for split-k partial sums", part_elems * sizeof(float));
+      return YTC_CUDA_ERROR;
+    }
+    const int64_t mn = M * N;
+    int s = ytcuda_gemm(YTC_BF16, YTC_F32, m->hi, W, part, static_cast<int>(M), N, kc, 1.f, 0.f, K, 1, 1, K, N, 1,
+                        splits, kc, kc, mn, st);
+    if (s != YTC_OK) return s;
+    s = ytcuda_gemm(YTC_BF16, YTC_F32, m->lo, W, part + static_cast<size_t>(splits) * mn, static_cast<int>(M), N, kc,
+                    1.f, 0.f, K, 1, 1, K, N, 1, splits, kc, kc, mn, st);
+    if (s != YTC_OK) return s;
+    const int64_t blocks = (mn / 4 + 255) / 256 + 1;
+    sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(part, 2 * splits, mn, y, y_rs,
+                                                                                             N, accumulate ? 1 : 0);
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
+  }
   int s = ytcuda_gemm(YTC_BF16, YTC_F32, m->hi, W, y, static_cast<int>(M), N, K, 1.f, accumulate ? 1.f : 0.f, K, 1, 1,
                       K, y_rs, 1, 1, 0, 0, 0, st);
   if (s != YTC_OK) return s;
@@ -400,8 +447,8 @@ int ytcuda_linear_w16(const float* x, int64_t x_row_stride, const void* w_bf16, 
                   (reinterpret_cast<uint64_t>(w_bf16) & 15) == 0,
               "ytcuda_linear_w16: k must be a multiple of 8 and x / W 16-byte aligned");
   Qwen3Model tmp{};
-  if (m > 32) {
-    YTC_REQUIRE(hi_lo_scratch != nullptr, "ytcuda_linear_w16: more than 32 rows need a scratch of 4*m*k bytes");
+  if (m > SK_MAX_ROWS) {
+    YTC_REQUIRE(hi_lo_scratch != nullptr, "ytcuda_linear_w16: more than %d rows need a scratch of 4*m*k bytes", SK_MAX_ROWS);
     tmp.hi = static_cast<uint16_t*>(hi_lo_scratch);
     tmp.lo = tmp.hi + m * k;
   }

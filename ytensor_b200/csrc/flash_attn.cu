@@ -831,6 +831,168 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnD
   }
 }
 
+// Decode attention for the common case (fp32, one query row per head, head / value dim 128, no mask or bias, rows
+// of K and V contiguous): one CTA of 8 warps per (sequence, kv head, key split). A warp takes 16 keys per step with
+// coalesced row loads: 8 lanes share a key for the dot products with the G query heads of the group (3 shuffles
+// finish one), maximum and sum are taken once per 16 keys, and P.V runs with the value dim across lanes and the
+// probabilities broadcast by shuffles. The V rows of a step are requested together with its K rows. The warps
+// combine through shared memory and leave (m, l, o) per split for attn_decode_merge_kernel.
+constexpr int DF_WARPS = 8;
+constexpr int DF_KB = 16;
+
+template <int G>
+__global__ void __launch_bounds__(DF_WARPS * 32) attn_decode_fast_kernel(const AttnDecodeParams dp) {
+  const AttnSimtParams& p = dp.a;
+  constexpr int D = 128;
+  __shared__ __align__(16) float qs[G * D];
+  __shared__ float pm[DF_WARPS * G], pl[DF_WARPS * G];
+  __shared__ __align__(16) float po[DF_WARPS * G * D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x;
+  const int bk = blockIdx.y;
+  const int b = bk / p.kv_heads, kvh = bk - b * p.kv_heads;
+  const float* Q = static_cast<const float*>(p.Q);
+  const float* kb = static_cast<const float*>(p.K) + b * p.k_sb + kvh * p.k_sh;
+  const float* vb = static_cast<const float*>(p.V) + b * p.v_sb + kvh * p.v_sh;
+  int n_keys = p.kv_len;
+  if (p.causal && p.causal_off + 1 < n_keys) n_keys = p.causal_off + 1;  // the single query row sees keys <= offset
+  const int k_begin = split * dp.keys_per_split;
+  int k_end = k_begin + dp.keys_per_split;
+  if (k_end > n_keys) k_end = n_keys;
+  for (int i = threadIdx.x; i < G * D; i += DF_WARPS * 32) {
+    const int g = i / D, c = i - g * D;
+    qs[i] = Q[b * p.q_sb + (kvh * G + g) * p.q_sh + c];
+  }
+  __syncthreads();
+  const int j8 = lane & 7, kq = lane >> 3;
+  float4 qreg[G][4];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qreg[g][i] = *reinterpret_cast<const float4*>(&qs[g * D + (j8 + 8 * i) * 4]);
+  float m_run[G], l_run[G];
+  float4 acc[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m_run[g] = -CUDART_INF_F;
+    l_run[g] = 0.f;
+    acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int key0 = k_begin + warp * DF_KB; key0 < k_end; key0 += DF_WARPS * DF_KB) {
+    float sc[G][DF_KB / 4];
+    float4 vv[DF_KB];
+#pragma unroll
+    for (int t = 0; t < DF_KB; ++t) {
+      vv[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (key0 + t < k_end) vv[t] = *(reinterpret_cast<const float4*>(vb + static_cast<int64_t>(key0 + t) * p.v_sr) + lane);
+    }
+    float4 kvr[DF_KB / 4][4];
+#pragma unroll
+    for (int kg = 0; kg < DF_KB / 4; ++kg) {
+      const int key = key0 + kg * 4 + kq;
+      const float4* krow = reinterpret_cast<const float4*>(kb + static_cast<int64_t>(key < k_end ? key : k_begin) * p.k_sr);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kvr[kg][i] = krow[j8 + 8 * i];
+    }
+#pragma unroll
+    for (int kg = 0; kg < DF_KB / 4; ++kg) {
+      const bool valid = key0 + kg * 4 + kq < k_end;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          d = fmaf(qreg[g][i].x, kvr[kg][i].x, d);
+          d = fmaf(qreg[g][i].y, kvr[kg][i].y, d);
+          d = fmaf(qreg[g][i].z, kvr[kg][i].z, d);
+          d = fmaf(qreg[g][i].w, kvr[kg][i].w, d);
+        }
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        sc[g][kg] = valid ? d * p.scale : -CUDART_INF_F;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mx = sc[g][0];
+#pragma unroll
+      for (int kg = 1; kg < DF_KB / 4; ++kg) mx = fmaxf(mx, sc[g][kg]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run[g], mx);       // finite: every step has a valid key
+      const float alpha = __expf(m_run[g] - m_new);  // 0 on the first step (m_run = -inf)
+      float sum = 0.f;
+#pragma unroll
+      for (int kg = 0; kg < DF_KB / 4; ++kg) {
+        sc[g][kg] = __expf(sc[g][kg] - m_new);
+        sum += sc[g][kg];
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      l_run[g] = l_run[g] * alpha + sum;
+      m_run[g] = m_new;
+      acc[g].x *= alpha;
+      acc[g].y *= alpha;
+      acc[g].z *= alpha;
+      acc[g].w *= alpha;
+    }
+#pragma unroll
+    for (int kg = 0; kg < DF_KB / 4; ++kg)
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float pt = __shfl_sync(0xffffffffu, sc[g][kg], t * 8);
+          acc[g].x = fmaf(pt, vv[kg * 4 + t].x, acc[g].x);
+          acc[g].y = fmaf(pt, vv[kg * 4 + t].y, acc[g].y);
+          acc[g].z = fmaf(pt, vv[kg * 4 + t].z, acc[g].z);
+          acc[g].w = fmaf(pt, vv[kg * 4 + t].w, acc[g].w);
+        }
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      pm[warp * G + g] = m_run[g];
+      pl[warp * G + g] = l_run[g];
+    }
+    *reinterpret_cast<float4*>(&po[(warp * G + g) * D + lane * 4]) = acc[g];
+  }
+  __syncthreads();
+  if (warp < G) {
+    const int g = warp;
+    const float mw = lane < DF_WARPS ? pm[lane * G + g] : -CUDART_INF_F;
+    const float lw = lane < DF_WARPS ? pl[lane * G + g] : 0.f;
+    float m = mw;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float fw = (mw == -CUDART_INF_F) ? 0.f : __expf(mw - m);
+    float lsum = lw * fw;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < DF_WARPS; ++w) {
+      const float f = __shfl_sync(0xffffffffu, fw, w);
+      const float4 ow = *reinterpret_cast<const float4*>(&po[(w * G + g) * D + lane * 4]);
+      o4.x = fmaf(ow.x, f, o4.x);
+      o4.y = fmaf(ow.y, f, o4.y);
+      o4.z = fmaf(ow.z, f, o4.z);
+      o4.w = fmaf(ow.w, f, o4.w);
+    }
+    // the layout attn_decode_merge_kernel reads: [m, l, o[dv]] per (kv head, split, row); row = g (q_len == 1)
+    float* dst = dp.part + ((static_cast<int64_t>(bk) * dp.splits + split) * G + g) * (2 + D);
+    if (lane == 0) {
+      dst[0] = m;
+      dst[1] = lsum;
+    }
+    float2* d2 = reinterpret_cast<float2*>(dst + 2 + lane * 4);
+    d2[0] = make_float2(o4.x, o4.y);
+    d2[1] = make_float2(o4.z, o4.w);
+  }
+}
+
+
 // Combines the per-slice partials: O = sum_s O_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m); rows that saw no key -> 0.
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const AttnDecodeParams dp) {
   const AttnSimtParams& p = dp.a;
@@ -1184,7 +1346,16 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
       set_last_error("ytcuda_flash_attn_fwd: cannot allocate %zu bytes of scratch", need);
       return YTC_CUDA_ERROR;
     }
-    attn_decode_kernel<<<dim3(dp.splits, bk), DEC_WARPS * 32, 0, st>>>(dp);
+    const bool fast = dtype == YTC_F32 && q_len == 1 && head_dim == 128 && value_dim == 128 && !mptr && !bias &&
+                      (groups == 1 || groups == 2 || groups == 4) && q_strides[1] % 4 == 0 && q_strides[0] % 4 == 0 &&
+                      (reinterpret_cast<uint64_t>(Q) & 15) == 0 && g_attn_path != 1;
+    if (fast) {
+      if (groups == 1) attn_decode_fast_kernel<1><<<dim3(dp.splits, bk), DF_WARPS * 32, 0, st>>>(dp);
+      else if (groups == 2) attn_decode_fast_kernel<2><<<dim3(dp.splits, bk), DF_WARPS * 32, 0, st>>>(dp);
+      else attn_decode_fast_kernel<4><<<dim3(dp.splits, bk), DF_WARPS * 32, 0, st>>>(dp);
+    } else {
+      attn_decode_kernel<<<dim3(dp.splits, bk), DEC_WARPS * 32, 0, st>>>(dp);
+    }
     attn_decode_merge_kernel<<<bk, 128, 0, st>>>(dp);
     count_launch(2);
     YTC_CUDA(cudaGetLastError());
