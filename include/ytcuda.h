@@ -251,10 +251,10 @@ int ytcuda_qwen3_set_allreduce(void* handle, int (*fn)(void* buf, int64_t count,
 int ytcuda_qwen3_reset(void* handle);
 int ytcuda_qwen3_cache_len(void* handle);
 /* How a forward of ONE new token per sequence runs: 0 = automatic (one persistent cooperative kernel for the whole
- * step where it applies: batch <= 8, and under tensor parallelism connected exchange buffers, see
- * ytcuda_qwen3_tp_export), 1 = one launch per operator as for longer inputs,
- * 2 = the persistent kernel or YTC_UNSUPPORTED. Both forms compute the operator sequence of
- * Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has no counterpart in the reference. */
+ * step for batch <= 8; under tensor parallelism it needs connected exchange buffers, see ytcuda_qwen3_tp_export),
+ * 1 = one launch per operator as for longer inputs, 2 = the persistent kernel (batch <= 32) or YTC_UNSUPPORTED.
+ * Both forms compute the operator sequence of Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has
+ * no counterpart in the reference. */
 int ytcuda_qwen3_set_decode_path(void* handle, int path);
 /* Tensor-parallel decode steps without a host-side collective: every rank exports the CUDA IPC handle (64 bytes) of
  * its exchange buffer, the caller distributes the handles (one all-gather at start-up), and every rank imports its

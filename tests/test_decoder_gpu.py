@@ -55,12 +55,14 @@ def test_small_model_logits_match_reference(Q, qwen3_golden, B):
     m.close()
 
 
-@pytest.mark.parametrize("B", [1, 3, 8])
+@pytest.mark.parametrize("B", [1, 3, 8, 13, 32])
 def test_single_kernel_decode_step_matches_operator_path(Q, B):
     """The persistent step kernel and the one-launch-per-operator forward compute the same logits and leave the same
     KV cache behind: 70 steps after a 40-token prompt (the attention of the step kernel goes from 2 to 4 key chunks),
     each model fed the other's tokens."""
-    cfg = Q.Qwen3Config(hidden_size=256, num_hidden_layers=3, vocab_size=1000, intermediate_size=384,
+    # (the FFN width is larger than what fits shared memory at once for 16 and 32 rows: the down projection then
+    # stages its input in pieces)
+    cfg = Q.Qwen3Config(hidden_size=256, num_hidden_layers=3, vocab_size=1000, intermediate_size=2816,
                         num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=128)
     w = Q.random_weights(cfg, seed=11, std=0.05)
     ids = dev_ids(np.random.default_rng(B).integers(0, cfg.vocab_size, (B, 40)))
@@ -89,13 +91,13 @@ def test_single_kernel_decode_step_matches_operator_path(Q, B):
     assert Q._lib.lib().ytcuda_device_status(None) == 0
     for m in ms:
         m.close()
-    if B == 8:  # more sequences than the step kernel holds: forcing it is refused, not silently rerouted
-        m = Q.Qwen3ForCausalLM(cfg, batch=9)
+    if B == 32:  # more sequences than the step kernel holds: forcing it is refused, not silently rerouted
+        m = Q.Qwen3ForCausalLM(cfg, batch=33)
         m.load_weights(w)
         m.set_decode_path(2)
-        m.forward(dev_ids(np.zeros((9, 4))))
+        m.forward(dev_ids(np.zeros((33, 4))))
         with pytest.raises(Exception):
-            m.forward(dev_ids(np.zeros((9, 1))))
+            m.forward(dev_ids(np.zeros((33, 1))))
         m.close()
 
 

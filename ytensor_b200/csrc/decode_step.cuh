@@ -41,7 +41,7 @@ namespace ytk {
 
 constexpr int DS_THREADS = 256;
 constexpr int DS_WARPS = DS_THREADS / 32;
-constexpr int DS_MAX_B = 8;        // sequences per step (activation rows kept in shared memory)
+constexpr int DS_MAX_B = 32;       // sequences per step (activation rows kept in shared memory)
 constexpr int DS_MAX_G = 4;        // query heads per kv head
 constexpr int DS_MAX_TP = 8;       // tensor-parallel ranks (one GPU each, peers reached by NVLink loads / stores)
 // attention scratch of a CTA: q of the group, and per warp (m, l, o[128]) for every head of the group
@@ -67,6 +67,7 @@ struct DecodeStepParams {
   float *x, *qkv, *attn, *act, *logits, *part;
   unsigned int* sync;  // grid barrier counter
   int chunks, keys_per_chunk;
+  int xs_cols;  // activation columns that fit shared memory at once (a multiple of 256, at most 3072)
   int* status;
   // Tensor parallelism (tp_world > 1): heads, kv_heads, inter and vocab_rows above are this rank's share. The partial
   // sums of the o and down projections are exchanged through "mailboxes" in peer-visible device memory:
@@ -276,19 +277,27 @@ __device__ __forceinline__ void ds_stage_rmsnorm(float* xs, const float* src, co
   __syncthreads();
 }
 
-__device__ __forceinline__ void ds_stage_copy(float* xs, const float* src, int B, int K) {
-  const int n4 = B * K / 4;
+// xs[b][0 .. kc) = src[b][c0 .. c0 + kc) for b < B (src rows of K floats)
+__device__ __forceinline__ void ds_stage_copy(float* xs, int xs_ld, const float* src, int B, int K, int c0, int kc) {
+  const int per_row = kc / 4;
+  const int n4 = B * per_row;
   for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * DS_THREADS) {
     float4 v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = i0 + u * DS_THREADS;
-      if (i < n4) v[u] = ds_ldcg4(src + static_cast<int64_t>(i) * 4);
+      if (i < n4) {
+        const int b = i / per_row, c = (i - b * per_row) * 4;
+        v[u] = ds_ldcg4(src + static_cast<int64_t>(b) * K + c0 + c);
+      }
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = i0 + u * DS_THREADS;
-      if (i < n4) *reinterpret_cast<float4*>(&xs[i * 4]) = v[u];
+      if (i < n4) {
+        const int b = i / per_row, c = (i - b * per_row) * 4;
+        *reinterpret_cast<float4*>(&xs[b * xs_ld + c]) = v[u];
+      }
     }
   }
   __syncthreads();
@@ -297,14 +306,15 @@ __device__ __forceinline__ void ds_stage_copy(float* xs, const float* src, int B
 // xs[b][head * 128 + d] = attention output, combined from the per-chunk partials (m, l, o[128]) the attention phase
 // left in global memory: o = sum_c e^(m_c - m) o_c / sum_c e^(m_c - m) l_c. Every CTA combines for itself while it
 // stages, so the chunks need no finishing step of their own.
-__device__ __forceinline__ void ds_stage_attention(float* xs, const float* part, int B, int heads, int kv_heads,
-                                                   int chunks) {
+// Columns c0 .. c0 + kc (whole heads) of the rows go to xs[b][0 .. kc).
+__device__ __forceinline__ void ds_stage_attention(float* xs, int xs_ld, const float* part, int B, int heads,
+                                                   int kv_heads, int chunks, int c0, int kc) {
   constexpr int D = 128;
   const int G = heads / kv_heads;
-  const int per_row = heads * (D / 4);
+  const int per_row = kc / 4;
   for (int i = threadIdx.x; i < B * per_row; i += DS_THREADS) {
     const int b = i / per_row, r = i - b * per_row;
-    const int head = r / (D / 4), d4 = r - head * (D / 4);
+    const int head = c0 / D + r / (D / 4), d4 = r % (D / 4);
     const int kvh = head / G, g = head - kvh * G;
     const float* base = part + ((static_cast<int64_t>(b) * kv_heads + kvh) * chunks * G + g) * (4 + D);
     const int64_t cs = static_cast<int64_t>(G) * (4 + D);  // chunk stride
@@ -350,7 +360,7 @@ __device__ __forceinline__ void ds_stage_attention(float* xs, const float* part,
     o.y *= inv;
     o.z *= inv;
     o.w *= inv;
-    *reinterpret_cast<float4*>(&xs[b * heads * D + head * D + d4 * 4]) = o;
+    *reinterpret_cast<float4*>(&xs[b * xs_ld + r * 4]) = o;
   }
   __syncthreads();
 }
@@ -420,6 +430,7 @@ struct DsLinear {
   int N, K;
   int stage;            // 0: xs = rmsNorm(src) * norm_w, 1: xs = src, 2: xs = attention output from the partials in src
   int heads, kv_heads, chunks;  // for stage == 2
+  int xs_cols;                  // see DecodeStepParams
   const float* src;     // [B][K] fp32 in global memory
   const float* norm_w;
   int epi;              // 0: dst[m][n] = y, 1: dst[m][n] += y, 2: dst[m][n] = swish(y[n]) * y[N + n]
@@ -434,8 +445,8 @@ struct DsLinear {
 
 // y[b][n] = sum_k xs[b][k] * W[n][k] for the rows this warp owns (n = gw, gw + GW, ...).
 // Two "slots" of DS_UN 128-bit loads per lane are in flight at once: two rows when the warp owns several, the two
-// halves of one row when it owns at most one, rows n and N + n of a fused gate / up weight when epi == 2. The
-// activations are staged into shared memory after the first loads have been issued.
+// halves of a piece of one row when it owns at most one, rows n and N + n of a fused gate / up weight when
+// epi == 2. The activations are staged into shared memory after the first loads have been issued.
 template <int MT>
 __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B, float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -444,25 +455,92 @@ __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B
   const int K = L.K, N = L.N;
   const bool pair = L.epi == 2;
   const bool split_k = !pair && N <= GW;  // at most one row per warp: the slots take the two halves of the row
+  auto prefetch_later_phases = [&]() {
+    for (int i = 0; i < 2; ++i)
+      if (L.pf_w[i]) ds_prefetch_rows(L.pf_w[i], L.pf_n[i], L.pf_k[i], gw, GW, lane);
+    if (L.pf_k_rows)
+      for (int i = threadIdx.x; i < L.pf_lines; i += DS_THREADS) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_k_rows + i * 128));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_v_rows + i * 128));
+      }
+  };
+  if (split_k) {
+    // One row per warp at most. The activations are staged in pieces of xs_cols columns (all of them at once when
+    // they fit); within a piece slot 0 takes the first half of the columns and slot 1 the second.
+    const int n0 = gw;
+    const bool have = n0 < N;
+    const int XC = K < L.xs_cols ? K : L.xs_cols;
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
+    const uint16_t* wrow = L.W + static_cast<int64_t>(have ? n0 : 0) * K;
+    for (int c0 = 0; c0 < K; c0 += XC) {
+      const int kc = K - c0 < XC ? K - c0 : XC;
+      const int hc = ((kc + 255) / 256 + 1) / 2;  // trips of slot 0 (at most DS_UN: xs_cols <= 3072)
+      uint4 a[DS_UN], b[DS_UN];
+#pragma unroll
+      for (int u = 0; u < DS_UN; ++u) {
+        const int k0 = u * 256 + lane * 8, k1 = (hc + u) * 256 + lane * 8;
+        a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (have && u < hc && k0 < kc) a[u] = __ldg(reinterpret_cast<const uint4*>(wrow + c0 + k0));
+        if (have && u < hc && k1 < kc) b[u] = __ldg(reinterpret_cast<const uint4*>(wrow + c0 + k1));
+      }
+      if (c0 == 0) prefetch_later_phases();
+      else __syncthreads();  // every warp has finished with the previous piece
+      if (L.stage == 0) ds_stage_rmsnorm(xs, L.src, L.norm_w, B, K, eps, warp, lane);  // (K <= xs_cols: one piece)
+      else if (L.stage == 1) ds_stage_copy(xs, XC, L.src, B, K, c0, kc);
+      else ds_stage_attention(xs, XC, L.src, B, L.heads, L.kv_heads, L.chunks, c0, kc);
+      if (!have) continue;
+#pragma unroll
+      for (int u = 0; u < DS_UN; ++u) {
+        const int k0 = u * 256 + lane * 8, k1 = (hc + u) * 256 + lane * 8;
+        const bool on0 = u < hc && k0 < kc, on1 = u < hc && k1 < kc;
+        if (!on0 && !on1) continue;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          if (on0) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[m * XC + k0]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[m * XC + k0 + 4]);
+            acc0[m] = ds_dot8(a[u], xa, xb, acc0[m]);
+          }
+          if (on1) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[m * XC + k1]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[m * XC + k1 + 4]);
+            acc1[m] = ds_dot8(b[u], xa, xb, acc1[m]);
+          }
+        }
+      }
+    }
+    if (!have) return;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc0[m] = ds_warp_sum(acc0[m] + acc1[m]);
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m >= B) break;
+        float* d0 = L.dst + static_cast<int64_t>(m) * L.ld + n0;
+        *d0 = L.epi == 1 ? acc0[m] + ds_ldcg(d0) : acc0[m];  // (epi 1: this warp is the only writer of the element)
+      }
+    }
+    return;
+  }
+  // Several rows per warp: the whole activation rows are in shared memory (K <= xs_cols).
   const int trips = (K + 255) / 256;
-  const int half = (trips + 1) / 2;
-  const int step = (pair || split_k) ? GW : 2 * GW;
+  const int step = pair ? GW : 2 * GW;
   bool staged = false;
   for (int n0 = gw; n0 < N || !staged; n0 += step) {
     const bool have = n0 < N;
     const int n1 = n0 + GW;
-    const bool two = have && !pair && !split_k && n1 < N;
+    const bool two = have && !pair && n1 < N;
     float acc0[MT], acc1[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
     const uint16_t* w0 = L.W + static_cast<int64_t>(have ? n0 : 0) * K;
-    const uint16_t* w1 = pair      ? L.W + static_cast<int64_t>(N + (have ? n0 : 0)) * K
-                         : split_k ? w0 + half * 256
-                                   : L.W + static_cast<int64_t>(two ? n1 : 0) * K;
-    const int k1_off = split_k ? half * 256 : 0;         // column offset of slot 1 within the row
-    const int t0_end = split_k ? half : trips;           // trips of slot 0
-    const int t1_end = split_k ? trips - half : trips;   // trips of slot 1
-    const bool use1 = have && (pair || split_k || two);
+    const uint16_t* w1 = pair ? L.W + static_cast<int64_t>(N + (have ? n0 : 0)) * K
+                              : L.W + static_cast<int64_t>(two ? n1 : 0) * K;
+    const int k1_off = 0;
+    const int t0_end = trips, t1_end = trips;
+    const bool use1 = have && (pair || two);
     for (int t = 0; t < t0_end || !staged; t += DS_UN) {
       uint4 a[DS_UN], b[DS_UN];
 #pragma unroll
@@ -473,16 +551,10 @@ __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B
         if (use1 && t + u < t1_end && k1_off + kk < K) b[u] = __ldg(reinterpret_cast<const uint4*>(w1 + kk));
       }
       if (!staged) {
-        for (int i = 0; i < 2; ++i)
-          if (L.pf_w[i]) ds_prefetch_rows(L.pf_w[i], L.pf_n[i], L.pf_k[i], gw, GW, lane);
-        if (L.pf_k_rows)
-          for (int i = threadIdx.x; i < L.pf_lines; i += DS_THREADS) {
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_k_rows + i * 128));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_v_rows + i * 128));
-          }
+        prefetch_later_phases();
         if (L.stage == 0) ds_stage_rmsnorm(xs, L.src, L.norm_w, B, K, eps, warp, lane);
-        else if (L.stage == 1) ds_stage_copy(xs, L.src, B, K);
-        else ds_stage_attention(xs, L.src, B, L.heads, L.kv_heads, L.chunks);
+        else if (L.stage == 1) ds_stage_copy(xs, K, L.src, B, K, 0, K);
+        else ds_stage_attention(xs, K, L.src, B, L.heads, L.kv_heads, L.chunks, 0, K);
         staged = true;
       }
       if (!have) break;
@@ -511,9 +583,8 @@ __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B
     if (!have) break;
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-      if (split_k) acc0[m] += acc1[m];
       acc0[m] = ds_warp_sum(acc0[m]);
-      if (!split_k) acc1[m] = ds_warp_sum(acc1[m]);
+      acc1[m] = ds_warp_sum(acc1[m]);
     }
     if (lane == 0) {
 #pragma unroll
@@ -774,7 +845,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
     DsLinear L;
 
     // ---- qkv = rmsNorm(x) . Wqkv^T
-    L = DsLinear{W.qkv, qkv_w, H, 0, 0, 0, 0, p.x, W.norm1, 0, p.qkv, qkv_w, {W.o, nullptr}, {H, 0}, {attn_w, 0},
+    L = DsLinear{W.qkv, qkv_w, H, 0, 0, 0, 0, p.xs_cols, p.x, W.norm1, 0, p.qkv, qkv_w, {W.o, nullptr}, {H, 0}, {attn_w, 0},
                  kv_k, kv_v, kv_lines};
     ds_linear_phase<MT>(L, xs, B, p.eps);
     if (!ds_grid_sync(p, epoch)) return;
@@ -790,7 +861,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
     if (!ds_grid_sync(p, epoch)) return;
 
     // ---- x += attn . Wo^T
-    L = DsLinear{W.o, H, attn_w, 2, p.heads, p.kv_heads, p.chunks, p.part, nullptr, 1, p.x, H, {W.down, nullptr},
+    L = DsLinear{W.o, H, attn_w, 2, p.heads, p.kv_heads, p.chunks, p.xs_cols, p.part, nullptr, 1, p.x, H, {W.down, nullptr},
                  {H, 0}, {p.inter, 0}, nullptr, nullptr, 0};
     if (p.tp_world > 1) {  // partial sums over this rank's heads go to the mailbox, the ranks' sums to x
       L.epi = 0;
@@ -811,14 +882,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
                                             ? p.vocab_rows
                                             : 4 * static_cast<int>(gridDim.x) * DS_WARPS, H, 0, 0)
                             : make_int4(qkv_w, H, 0, 0);
-      L = DsLinear{W.gate_up, p.inter, H, 0, 0, 0, 0, p.x, W.norm2, 2, p.act, p.inter,
+      L = DsLinear{W.gate_up, p.inter, H, 0, 0, 0, 0, p.xs_cols, p.x, W.norm2, 2, p.act, p.inter,
                    {last ? p.lm_head : p.lw[l + 1].qkv, nullptr}, {nxt.x, 0}, {nxt.y, 0}, nullptr, nullptr, 0};
     }
     ds_linear_phase<MT>(L, xs, B, p.eps);
     if (!ds_grid_sync(p, epoch)) return;
 
     // ---- x += act . Wdown^T
-    L = DsLinear{W.down, H, p.inter, 1, 0, 0, 0, p.act, nullptr, 1, p.x, H, {nullptr, nullptr}, {0, 0}, {0, 0},
+    L = DsLinear{W.down, H, p.inter, 1, 0, 0, 0, p.xs_cols, p.act, nullptr, 1, p.x, H, {nullptr, nullptr}, {0, 0}, {0, 0},
                  nullptr, nullptr, 0};
     if (p.tp_world > 1) {
       L.epi = 0;
@@ -834,7 +905,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
   }
 
   // ---- logits = rmsNorm(x) . Wvocab^T
-  DsLinear L{p.lm_head, p.vocab_rows, H, 0, 0, 0, 0, p.x, p.final_norm, 0, p.logits, p.vocab_rows, {nullptr, nullptr},
+  DsLinear L{p.lm_head, p.vocab_rows, H, 0, 0, 0, 0, p.xs_cols, p.x, p.final_norm, 0, p.logits, p.vocab_rows, {nullptr, nullptr},
              {0, 0}, {0, 0}, nullptr, nullptr, 0};
   ds_linear_phase<MT>(L, xs, B, p.eps);
 }

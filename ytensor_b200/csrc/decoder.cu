@@ -653,11 +653,24 @@ static int ensure_activations(Qwen3Model* m, int64_t rows) {
 }
 
 constexpr int DS_MAX_CHUNKS = 64;
+constexpr int DS_AUTO_B = 8;
 
 
 // Whether the persistent step kernel covers this model (one new token per sequence is checked by the caller).
+// Activation rows the step kernel is instantiated for, and the columns of them that fit its shared memory at once.
+static int ds_rows(int batch) { return batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : batch <= 8 ? 8 : batch <= 16 ? 16 : 32; }
+static int ds_xs_cols(int mt) {
+  int cols = (160 * 1024 / (mt * 4)) / 256 * 256;
+  return cols > 3072 ? 3072 : cols;
+}
+
 static bool decode_step_supported(const Qwen3Model* m) {
   const int groups = m->heads / m->kv_heads;
+  const int xs_cols = ds_xs_cols(ds_rows(m->batch));
+  const int gw = sm_count() * DS_WARPS;
+  // whole activation rows must fit shared memory unless the phase has at most one weight row per warp
+  auto fits = [&](int n, int k) { return k <= xs_cols || n <= gw; };
+  if (m->hidden > xs_cols || !fits(m->hidden, m->l_heads * 128) || !fits(m->hidden, m->l_inter)) return false;
   return (m->tp_world == 1 || m->tp_ready) && m->batch <= DS_MAX_B && m->head_dim == 128 && (groups == 1 || groups == 2 || groups == 4) &&
          m->hidden % 8 == 0 && m->inter % 8 == 0;
 }
@@ -686,9 +699,10 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   }
   int kmax = m->hidden > m->l_inter ? m->hidden : m->l_inter;
   if (m->l_heads * D > kmax) kmax = m->l_heads * D;
-  // the kernel is instantiated for 1, 2, 4 or 8 activation rows and reads that many rows of shared memory
-  const int mt = B == 1 ? 1 : (B == 2 ? 2 : (B <= 4 ? 4 : 8));
-  int smem = mt * kmax * static_cast<int>(sizeof(float));
+  // the kernel is instantiated for 1 .. 32 activation rows and reads that many rows of shared memory
+  const int mt = ds_rows(B);
+  const int xs_cols = ds_xs_cols(mt);
+  int smem = mt * (kmax < xs_cols ? kmax : xs_cols) * static_cast<int>(sizeof(float));
   const int att = DS_ATT_FLOATS * static_cast<int>(sizeof(float));  // the attention phase's scratch
   if (smem < att) smem = att;
   DecodeStepParams p{};
@@ -721,6 +735,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   per = (per + 31) / 32 * 32;  // whole blocks of 32 keys
   p.keys_per_chunk = per;
   p.chunks = (keys + per - 1) / per;
+  p.xs_cols = xs_cols;
   YTC_CUDA(cudaMemsetAsync(m->ds_sync, 0, sync_words * sizeof(unsigned int), st));
   void* args[] = {&p};
   const void* fn = nullptr;
@@ -731,7 +746,9 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   if (mt == 1) DS_PICK(1);
   else if (mt == 2) DS_PICK(2);
   else if (mt == 4) DS_PICK(4);
-  else DS_PICK(8);
+  else if (mt == 8) DS_PICK(8);
+  else if (mt == 16) DS_PICK(16);
+  else DS_PICK(32);
 #undef DS_PICK
   if (m->ds_smem_set < smem) {
     YTC_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -758,7 +775,8 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   for (const LayerW& L : m->lw)
     YTC_REQUIRE(L.qkv && L.o && L.gate_up && L.down && L.q_norm && L.k_norm && L.norm1 && L.norm2,
                 "ytcuda_qwen3_forward: a layer weight is not set");
-  YTC_REQUIRE(m->tp_world == 1 || m->allreduce || (len == 1 && m->tp_ready && m->decode_path != 1),
+  YTC_REQUIRE(m->tp_world == 1 || m->allreduce ||
+                  (len == 1 && m->tp_ready && (m->decode_path == 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B))),
               "ytcuda_qwen3_forward: tensor parallel needs an all-reduce callback");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int B = m->batch, D = m->head_dim, Hd = m->hidden;
@@ -767,7 +785,9 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   if (s != YTC_OK) return s;
   const int pos0 = m->cur_len;
   const int kv_len = pos0 + len;
-  if (len == 1 && m->decode_path != 1 && decode_step_supported(m)) {
+  // Automatic choice: the step kernel up to DS_AUTO_B sequences. Beyond that its FFMA linears lose against the
+  // tensor-core linears of the operator path (measured at 16 and 32 sequences), so it runs only when asked for.
+  if (len == 1 && (m->decode_path == 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B)) && decode_step_supported(m)) {
     if ((s = decode_step_launch(m, ids, logits, st)) != YTC_OK) return s;
     m->cur_len = kv_len;
     return YTC_OK;
@@ -799,24 +819,34 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     if ((s = ytcuda_flash_attn_fwd(YTC_F32, m->q, kc, vc, m->attn, B, m->l_kv_heads, groups, len, kv_len, D, D, scale, qs,
                                    ks, ks, os, 1, kv_len - len, nullptr, 0, nullptr, 0, 0, st)) != YTC_OK)
       return s;
-    if ((s = linear_w16(m, m->attn, m->l_heads * D, W.o, m->proj, Hd, rows, Hd, m->l_heads * D, false, st)) != YTC_OK)
-      return s;
-    if (m->tp_world > 1 && (s = m->allreduce(m->proj, rows * Hd, m->allreduce_user)) != 0) {
-      set_last_error("ytcuda_qwen3_forward: all-reduce callback failed with %d", s);
-      return YTC_CUDA_ERROR;
+    if (m->tp_world == 1) {  // x2 = attn + x: the projection accumulates into the residual stream
+      if ((s = linear_w16(m, m->attn, m->l_heads * D, W.o, m->x, Hd, rows, Hd, m->l_heads * D, true, st)) != YTC_OK)
+        return s;
+    } else {
+      if ((s = linear_w16(m, m->attn, m->l_heads * D, W.o, m->proj, Hd, rows, Hd, m->l_heads * D, false, st)) != YTC_OK)
+        return s;
+      if ((s = m->allreduce(m->proj, rows * Hd, m->allreduce_user)) != 0) {
+        set_last_error("ytcuda_qwen3_forward: all-reduce callback failed with %d", s);
+        return YTC_CUDA_ERROR;
+      }
+      if ((s = add_inplace(m->x, m->proj, rows * Hd, st)) != YTC_OK) return s;
     }
-    if ((s = add_inplace(m->x, m->proj, rows * Hd, st)) != YTC_OK) return s;  // x2 = attn + x
     if ((s = rmsnorm_rows(m->x, W.norm2, m->h, rows, Hd, m->eps, st)) != YTC_OK) return s;
     if ((s = linear_w16(m, m->h, Hd, W.gate_up, m->gu, 2 * m->l_inter, rows, 2 * m->l_inter, Hd, false, st)) != YTC_OK)
       return s;
     if ((s = ytcuda_swiglu(YTC_F32, YTC_F32, m->gu, m->act, rows, m->l_inter, 2 * m->l_inter, m->l_inter, st)) != YTC_OK)
       return s;
-    if ((s = linear_w16(m, m->act, m->l_inter, W.down, m->proj, Hd, rows, Hd, m->l_inter, false, st)) != YTC_OK) return s;
-    if (m->tp_world > 1 && (s = m->allreduce(m->proj, rows * Hd, m->allreduce_user)) != 0) {
-      set_last_error("ytcuda_qwen3_forward: all-reduce callback failed with %d", s);
-      return YTC_CUDA_ERROR;
+    if (m->tp_world == 1) {  // x2 += mlp
+      if ((s = linear_w16(m, m->act, m->l_inter, W.down, m->x, Hd, rows, Hd, m->l_inter, true, st)) != YTC_OK) return s;
+    } else {
+      if ((s = linear_w16(m, m->act, m->l_inter, W.down, m->proj, Hd, rows, Hd, m->l_inter, false, st)) != YTC_OK)
+        return s;
+      if ((s = m->allreduce(m->proj, rows * Hd, m->allreduce_user)) != 0) {
+        set_last_error("ytcuda_qwen3_forward: all-reduce callback failed with %d", s);
+        return YTC_CUDA_ERROR;
+      }
+      if ((s = add_inplace(m->x, m->proj, rows * Hd, st)) != YTC_OK) return s;
     }
-    if ((s = add_inplace(m->x, m->proj, rows * Hd, st)) != YTC_OK) return s;  // x2 += mlp
   }
   // last position of every sequence -> final norm -> vocabulary projection
   float* last_in = m->last;

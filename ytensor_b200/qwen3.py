@@ -139,7 +139,7 @@ class Qwen3ForCausalLM:
 
             self._cb = _ALLREDUCE_T(allreduce)
             check(self.L.ytcuda_qwen3_set_allreduce(self.h, C.cast(self._cb, C.c_void_p), None))
-            if batch <= 8 and connect_peers:
+            if batch <= 32 and connect_peers:
                 self._connect_peers()
 
     def _connect_peers(self) -> None:
