@@ -1,5 +1,8 @@
 // Host-side plumbing of libytensor_cuda.so: error text, storage helpers, the device
 // status word, the tensor-map encoder and a small per-device workspace.
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -110,9 +113,45 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// A tensor map is a pure function of its arguments (address, extents, strides, box, type, swizzle) and encoding one
+// costs the host a microsecond or more; launch-bound loops (a decode step issues hundreds of GEMMs over the same
+// buffers) get them from this small cache instead.
+struct MapKey {
+  uint64_t v[16];
+  bool operator==(const MapKey& o) const { return std::memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t x : k.v) {
+      h ^= x;
+      h *= 1099511628211ull;
+    }
+    return static_cast<size_t>(h);
+  }
+};
+static std::mutex g_map_mutex;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base,
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                       CUtensorMapSwizzle swz) {
+  MapKey key{};
+  if (rank <= 4) {
+    key.v[0] = reinterpret_cast<uint64_t>(base);
+    key.v[1] = (static_cast<uint64_t>(dt) << 32) | (static_cast<uint64_t>(swz) << 8) | rank;
+    for (uint32_t i = 0; i < rank; ++i) {
+      key.v[2 + i] = dims[i];
+      key.v[6 + i] = i + 1 < rank ? strides_bytes[i] : 0;
+      key.v[10 + i] = box[i];
+    }
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) {
+      *map = it->second;
+      return YTC_OK;
+    }
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_last_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -137,6 +176,11 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, c
                    (unsigned long long)(rank > 2 ? strides_bytes[1] : 0), box[0], rank > 1 ? box[1] : 0,
                    rank > 2 ? box[2] : 0);
     return YTC_INVALID_ARG;
+  }
+  if (rank <= 4) {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_map_cache.size() >= 8192) g_map_cache.clear();
+    g_map_cache.emplace(key, *map);
   }
   return YTC_OK;
 }
