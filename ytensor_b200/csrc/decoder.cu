@@ -149,13 +149,14 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(const floa
   }
 }
 
-// y[r][c] (+)= sum over p of part[p][r][c] (partials of [rows][cols] floats, added in index order).
+// y[r][c] (+)= sum over p of (part[p][0][r][c] + part[p][1][r][c]): partials of two stacked [rows][cols] blocks
+// (the hi and lo planes of the activations) per k piece, added in index order.
 __global__ void __launch_bounds__(256) sum_partials_kernel(const float* part, int n_part, int64_t mn, float* y,
                                                            int64_t y_rs, int cols, int accumulate) {
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < mn;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     float s = 0.f;
-    for (int p = 0; p < n_part; ++p) s += part[p * mn + i];
+    for (int p = 0; p < n_part; ++p) s += part[2 * p * mn + i] + part[(2 * p + 1) * mn + i];
     const int64_t r = i / cols, c = i - r * cols;
     float* dst = y + r * y_rs + c;
     *dst = accumulate ? *dst + s : s;
@@ -277,7 +278,7 @@ struct Qwen3Model {
   // activations
   float *x = nullptr, *h = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr, *act = nullptr,
         *proj = nullptr, *last = nullptr;
-  uint16_t *hi = nullptr, *lo = nullptr;
+  uint16_t* hi = nullptr;  // bf16 planes of the activations: hi [rows][k], then lo [rows][k]
   int64_t act_rows = 0;
   AllReduceFn allreduce = nullptr;
   void* allreduce_user = nullptr;
@@ -350,7 +351,10 @@ static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_
   const int64_t total4 = M * (K / 4);
   const int64_t blocks = (total4 + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-  split_hi_lo_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, x_rs, m->hi, m->lo, M, K);
+  // the lo plane follows the hi plane: [2 M][K] is then one left operand whose rows M .. 2 M - 1 are the lo plane
+  uint16_t* hi = m->hi;
+  uint16_t* lo = m->hi + M * K;
+  split_hi_lo_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, x_rs, hi, lo, M, K);
   count_launch();
   YTC_CUDA(cudaGetLastError());
   // Few rows (decode with a larger batch): there are only N / 128 output tiles, too few to keep the SMs busy and the
@@ -362,30 +366,28 @@ static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_
     const int tiles = (N + 127) / 128;
     while (splits > 1 && (splits % 2 == 0) && tiles * (splits / 2) >= 2 * sm_count()) splits /= 2;
     const int kc = K / splits;
-    const size_t part_elems = static_cast<size_t>(2) * splits * M * N;
+    const size_t part_elems = static_cast<size_t>(2) * splits * M * N;  // [splits][2 M][N]
     float* part = static_cast<float*>(device_workspace(part_elems * sizeof(float)));
     if (!part) {
       set_last_error("linear: cannot allocate %zu bytes for split-k partial sums", part_elems * sizeof(float));
       return YTC_CUDA_ERROR;
     }
     const int64_t mn = M * N;
-    int s = ytcuda_gemm(YTC_BF16, YTC_F32, m->hi, W, part, static_cast<int>(M), N, kc, 1.f, 0.f, K, 1, 1, K, N, 1,
-                        splits, kc, kc, mn, st);
-    if (s != YTC_OK) return s;
-    s = ytcuda_gemm(YTC_BF16, YTC_F32, m->lo, W, part + static_cast<size_t>(splits) * mn, static_cast<int>(M), N, kc,
-                    1.f, 0.f, K, 1, 1, K, N, 1, splits, kc, kc, mn, st);
+    // one launch: both planes as 2 M rows of the left operand, the k pieces as batch items
+    int s = ytcuda_gemm(YTC_BF16, YTC_F32, hi, W, part, static_cast<int>(2 * M), N, kc, 1.f, 0.f, K, 1, 1, K, N, 1,
+                        splits, kc, kc, 2 * mn, st);
     if (s != YTC_OK) return s;
     const int64_t blocks = (mn / 4 + 255) / 256 + 1;
-    sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(part, 2 * splits, mn, y, y_rs,
-                                                                                             N, accumulate ? 1 : 0);
+    sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(part, splits, mn, y, y_rs, N,
+                                                                                             accumulate ? 1 : 0);
     count_launch();
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;
   }
-  int s = ytcuda_gemm(YTC_BF16, YTC_F32, m->hi, W, y, static_cast<int>(M), N, K, 1.f, accumulate ? 1.f : 0.f, K, 1, 1,
+  int s = ytcuda_gemm(YTC_BF16, YTC_F32, hi, W, y, static_cast<int>(M), N, K, 1.f, accumulate ? 1.f : 0.f, K, 1, 1,
                       K, y_rs, 1, 1, 0, 0, 0, st);
   if (s != YTC_OK) return s;
-  return ytcuda_gemm(YTC_BF16, YTC_F32, m->lo, W, y, static_cast<int>(M), N, K, 1.f, 1.f, K, 1, 1, K, y_rs, 1, 1, 0, 0,
+  return ytcuda_gemm(YTC_BF16, YTC_F32, lo, W, y, static_cast<int>(M), N, K, 1.f, 1.f, K, 1, 1, K, y_rs, 1, 1, 0, 0,
                      0, st);
 }
 
@@ -450,7 +452,6 @@ int ytcuda_linear_w16(const float* x, int64_t x_row_stride, const void* w_bf16, 
   if (m > SK_MAX_ROWS) {
     YTC_REQUIRE(hi_lo_scratch != nullptr, "ytcuda_linear_w16: more than %d rows need a scratch of 4*m*k bytes", SK_MAX_ROWS);
     tmp.hi = static_cast<uint16_t*>(hi_lo_scratch);
-    tmp.lo = tmp.hi + m * k;
   }
   return linear_w16(&tmp, x, x_row_stride, static_cast<const uint16_t*>(w_bf16), y, y_row_stride, m, n, k,
                     accumulate != 0, static_cast<cudaStream_t>(stream));
@@ -644,8 +645,7 @@ static int ensure_activations(Qwen3Model* m, int64_t rows) {
   if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->attn), rows * m->l_heads * D * 4)) != YTC_OK) return s;
   if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->gu), rows * 2 * m->l_inter * 4)) != YTC_OK) return s;
   if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->act), rows * m->l_inter * 4)) != YTC_OK) return s;
-  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->hi), rows * kmax2 * 2)) != YTC_OK) return s;
-  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->lo), rows * kmax2 * 2)) != YTC_OK) return s;
+  if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->hi), rows * kmax2 * 4)) != YTC_OK) return s;  // hi and lo planes
   if (!m->last && (s = dev_alloc(m, reinterpret_cast<void**>(&m->last), static_cast<size_t>(m->batch) * m->hidden * 8)) != YTC_OK)
     return s;
   m->act_rows = rows;
