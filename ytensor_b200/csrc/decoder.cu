@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float* part, in
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < mn;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     float s = 0.f;
+#pragma unroll 8
     for (int p = 0; p < n_part; ++p) s += part[2 * p * mn + i] + part[(2 * p + 1) * mn + i];
     const int64_t r = i / cols, c = i - r * cols;
     float* dst = y + r * y_rs + c;
@@ -377,7 +378,7 @@ static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_
     int s = ytcuda_gemm(YTC_BF16, YTC_F32, hi, W, part, static_cast<int>(2 * M), N, kc, 1.f, 0.f, K, 1, 1, K, N, 1,
                         splits, kc, kc, 2 * mn, st);
     if (s != YTC_OK) return s;
-    const int64_t blocks = (mn / 4 + 255) / 256 + 1;
+    const int64_t blocks = (mn + 255) / 256;
     sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(part, splits, mn, y, y_rs, N,
                                                                                              accumulate ? 1 : 0);
     count_launch();
