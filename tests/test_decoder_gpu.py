@@ -72,6 +72,12 @@ def test_single_kernel_decode_step_matches_operator_path(Q, B):
         m.load_weights(w)
         m.set_decode_path(path)
         ms.append(m)
+    # a single token into an empty cache (no prefill before it), then start over with the prompt
+    first = ids[:, :1].contiguous()
+    fa, fb = ms[0].forward(first), ms[1].forward(first)
+    assert normwise(fb.cpu().numpy(), fa.cpu().numpy()) < 2e-5
+    for m in ms:
+        m.reset_kv_cache()
     la, lb = ms[0].forward(ids), ms[1].forward(ids)  # prefill: the same kernels in both
     assert torch.equal(la, lb)
     launches = []
