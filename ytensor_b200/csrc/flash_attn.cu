@@ -1176,6 +1176,170 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(const AttnSimtParams p) 
 }
 
 // ------------------------------------------------------------------ host side
+
+// ------------------------------------------------------------------ fp32 attention with register tiles (prefill)
+// 64 query rows x 64 keys per step and CTA, 256 threads. S = Q K^T is formed in 4 x 4 register tiles (rows
+// 4 ry .. 4 ry + 3, keys kx, kx + 16, kx + 32, kx + 48: the strided keys keep the 128-bit shared-memory reads of K free
+// of bank conflicts), the row maximum and sum are taken over the 16 lanes that share a row group, P goes to shared
+// memory transposed ([key][row]) and O += P V runs in 4 x 8 register tiles (value columns 4 cx .. 4 cx + 3 and
+// 64 + 4 cx .. 64 + 4 cx + 3). 8 FMAs per 128-bit shared-memory read in the first product, about 11 in the second,
+// against 3.5 in attn_tile_kernel. fp32 operands with 16-byte aligned rows, head / value dim up to 128.
+constexpr int T64_BM = 64, T64_BN = 64, T64_LD = 128 + 4, T64_PLD = 64 + 4;
+constexpr int T64_SMEM = (3 * 64 * T64_LD + T64_BN * T64_PLD) * 4;
+
+__global__ void __launch_bounds__(256, 1) attn_tile64_kernel(const AttnSimtParams p) {
+  extern __shared__ __align__(16) float t64_smem[];
+  float(*Qs)[T64_LD] = reinterpret_cast<float(*)[T64_LD]>(t64_smem);
+  float(*Ks)[T64_LD] = Qs + T64_BM;
+  float(*Vs)[T64_LD] = Ks + T64_BN;
+  float(*PsT)[T64_PLD] = reinterpret_cast<float(*)[T64_PLD]>(Vs + T64_BN);  // [key][row]
+  const int tid = threadIdx.x;
+  const int ry = tid >> 4, kx = tid & 15, cx = kx;
+  const int row_blocks = (p.q_len + T64_BM - 1) / T64_BM;
+  const int rbk = row_blocks - 1 - static_cast<int>(blockIdx.x);  // long causal rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / p.groups;
+  const int row0 = rbk * T64_BM;
+  const float* Qf = static_cast<const float*>(p.Q) + b * p.q_sb + h * p.q_sh;
+  const float* Kf = static_cast<const float*>(p.K) + b * p.k_sb + kvh * p.k_sh;
+  const float* Vf = static_cast<const float*>(p.V) + b * p.v_sb + kvh * p.v_sh;
+  for (int i = tid; i < T64_BM * 32; i += 256) {
+    const int r = i >> 5, c = (i & 31) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row0 + r < p.q_len && c < p.d) v = *reinterpret_cast<const float4*>(Qf + static_cast<int64_t>(row0 + r) * p.q_sr + c);
+    *reinterpret_cast<float4*>(&Qs[r][c]) = v;
+  }
+  float acc[4][8];
+  float m_run[4], l_run[4];
+  int limit[4];  // last visible key of each of this thread's rows (-1: the row does not exist)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m_run[i] = -CUDART_INF_F;
+    l_run[i] = 0.f;
+    const int row = row0 + ry * 4 + i;
+    limit[i] = (row < p.q_len) ? ((p.causal && row + p.causal_off < p.kv_len - 1) ? row + p.causal_off : p.kv_len - 1) : -1;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[i][c] = 0.f;
+  }
+  int last = p.kv_len - 1;
+  if (p.causal) {
+    const int lim = row0 + T64_BM - 1 + p.causal_off;
+    if (lim < last) last = lim;
+  }
+  for (int k0 = 0; k0 <= last; k0 += T64_BN) {
+    __syncthreads();  // the previous step has finished with Ks, Vs and PsT
+    {
+      float4 kq[8], vq[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 256;
+        const int r = i >> 5, c = (i & 31) * 4;
+        const bool in = k0 + r < p.kv_len;
+        kq[u] = (in && c < p.d) ? *reinterpret_cast<const float4*>(Kf + static_cast<int64_t>(k0 + r) * p.k_sr + c)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+        vq[u] = (in && c < p.dv) ? *reinterpret_cast<const float4*>(Vf + static_cast<int64_t>(k0 + r) * p.v_sr + c)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 256;
+        const int r = i >> 5, c = (i & 31) * 4;
+        *reinterpret_cast<float4*>(&Ks[r][c]) = kq[u];
+        *reinterpret_cast<float4*>(&Vs[r][c]) = vq[u];
+      }
+    }
+    __syncthreads();
+    float sc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+#pragma unroll 2
+    for (int k4 = 0; k4 < 128; k4 += 4) {
+      float4 qv[4], kv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = *reinterpret_cast<const float4*>(&Qs[ry * 4 + i][k4]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kv[j] = *reinterpret_cast<const float4*>(&Ks[kx + 16 * j][k4]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sc[i][j] = fmaf(qv[i].x, kv[j].x, sc[i][j]);
+          sc[i][j] = fmaf(qv[i].y, kv[j].y, sc[i][j]);
+          sc[i][j] = fmaf(qv[i].z, kv[j].z, sc[i][j]);
+          sc[i][j] = fmaf(qv[i].w, kv[j].w, sc[i][j]);
+        }
+    }
+    float alpha[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row0 + ry * 4 + i;
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = k0 + kx + 16 * j;
+        bool vis = key <= limit[i];
+        if (vis && p.mask) vis = p.mask[static_cast<int64_t>(row) * p.mask_rs + key] != 0;
+        float v = sc[i][j] * p.scale;
+        if (vis && p.bias) v += p.bias[static_cast<int64_t>(row) * p.bias_rs + key * p.bias_cs];
+        sc[i][j] = vis ? v : -CUDART_INF_F;
+        mx = fmaxf(mx, sc[i][j]);
+      }
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_new = fmaxf(m_run[i], mx);
+      const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+      alpha[i] = (m_run[i] == -CUDART_INF_F) ? 0.f : __expf(m_run[i] - m_use);
+      float ps = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float pr = __expf(sc[i][j] - m_use);  // exp(-inf) = 0 for hidden keys
+        PsT[kx + 16 * j][ry * 4 + i] = pr;
+        ps += pr;
+      }
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      l_run[i] = l_run[i] * alpha[i] + ps;
+      m_run[i] = m_new;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[i][c] *= alpha[i];
+    }
+    __syncthreads();  // P of all 64 rows x 64 keys is in shared memory
+#pragma unroll 4
+    for (int j = 0; j < T64_BN; ++j) {
+      const float4 pr = *reinterpret_cast<const float4*>(&PsT[j][ry * 4]);
+      const float4 v0 = *reinterpret_cast<const float4*>(&Vs[j][cx * 4]);
+      const float4 v1 = *reinterpret_cast<const float4*>(&Vs[j][64 + cx * 4]);
+      const float pv[4] = {pr.x, pr.y, pr.z, pr.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i][0] = fmaf(pv[i], v0.x, acc[i][0]);
+        acc[i][1] = fmaf(pv[i], v0.y, acc[i][1]);
+        acc[i][2] = fmaf(pv[i], v0.z, acc[i][2]);
+        acc[i][3] = fmaf(pv[i], v0.w, acc[i][3]);
+        acc[i][4] = fmaf(pv[i], v1.x, acc[i][4]);
+        acc[i][5] = fmaf(pv[i], v1.y, acc[i][5]);
+        acc[i][6] = fmaf(pv[i], v1.z, acc[i][6]);
+        acc[i][7] = fmaf(pv[i], v1.w, acc[i][7]);
+      }
+    }
+  }
+  float* Of = static_cast<float*>(p.O) + b * p.o_sb + h * p.o_sh;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = row0 + ry * 4 + i;
+    if (row >= p.q_len) continue;
+    const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
+    float* orow = Of + static_cast<int64_t>(row) * p.o_sr;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (cx * 4 + c < p.dv) orow[cx * 4 + c] = acc[i][c] * inv;
+      if (64 + cx * 4 + c < p.dv) orow[64 + cx * 4 + c] = acc[i][4 + c] * inv;
+    }
+  }
+}
+
 static int g_attn_path = 0;  // 0 automatic, 1 always the one-warp-per-row kernel, 2 tensor-core kernel or fail
 
 static int make_qkv_map(CUtensorMap* map, const void* base, int d, int64_t len, int64_t heads, int64_t batch,
@@ -1358,6 +1522,20 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
     }
     attn_decode_merge_kernel<<<bk, 128, 0, st>>>(dp);
     count_launch(2);
+    YTC_CUDA(cudaGetLastError());
+    return YTC_OK;
+  }
+  if (dtype == YTC_F32 && q_len >= 64 && head_dim <= 128 && value_dim <= 128 && heads <= 65535 && batch <= 65535 &&
+      vec_ok && head_dim % 4 == 0 && value_dim % 4 == 0 && q_strides[0] % 4 == 0 && q_strides[1] % 4 == 0 &&
+      q_strides[2] % 4 == 0 && (reinterpret_cast<uint64_t>(Q) & 15) == 0) {
+    dim3 grid((q_len + T64_BM - 1) / T64_BM, heads, batch);
+    static bool attr64 = false;
+    if (!attr64) {
+      YTC_CUDA(cudaFuncSetAttribute(attn_tile64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T64_SMEM));
+      attr64 = true;
+    }
+    attn_tile64_kernel<<<grid, 256, T64_SMEM, st>>>(p);
+    count_launch();
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;
   }
