@@ -225,6 +225,14 @@ int ytcuda_embedding(const void* table_bf16, const int32_t* ids, float* out, int
 int ytcuda_linear_w16(const float* x, int64_t x_row_stride, const void* w_bf16, float* y, int64_t y_row_stride,
                       int64_t m, int n, int k, int accumulate, void* hi_lo_scratch, void* stream);
 
+/* Top-k sampling of qwen3::Qwen3ForCausalLM::generate (example/qwen3/src/qwen3.cpp:465-486): per row of fp32 logits
+ * [rows, vocab], probabilities = softmax, the k <= 64 most probable tokens in descending order go to top_probs /
+ * top_idx [rows, k] (the first index wins ties), and, when `sampled` is given, the token whose running sum of kept
+ * probabilities first reaches uniform[row] * (sum of the kept probabilities) goes to sampled[row]. The uniform numbers
+ * in [0, 1] come from the caller (the reference draws them on the host from std::mt19937); null means 0. */
+int ytcuda_topk_sample(const float* logits, int64_t row_stride, int rows, int vocab, int k, const float* uniform,
+                       float* top_probs, int32_t* top_idx, int32_t* sampled, void* stream);
+
 /* Fused per-head RMSNorm (q, k) + rotate-half RoPE + KV-cache append on the fused projection output
  * qkv [batch, len, (heads + 2 kv_heads) * 128] -> q_out [batch, heads, len, 128], k_cache / v_cache
  * [batch, kv_heads, max_len, 128] at slots slot0 .. slot0 + len - 1, RoPE positions pos0 .. (qwen3.cpp:237-247,

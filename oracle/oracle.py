@@ -89,6 +89,29 @@ class _Backend:
         assert rc == 0, rc
         return y
 
+    def topk_sample(self, logits, k=20, uniform=None):
+        """sample_token of Qwen3ForCausalLM::generate (reference example/qwen3/src/qwen3.cpp:465-486): softmax over
+        the row, the k largest probabilities in descending order (stable: the lower index first on ties), and the
+        token whose running sum first reaches uniform * sum(kept), the first kept token otherwise."""
+        probs = self.softmax(_f32(logits), [-1])
+        order = np.argsort(-probs, axis=1, kind="stable")[:, :k]
+        top = np.take_along_axis(probs, order, axis=1)
+        sampled = None
+        if uniform is not None:
+            sampled = np.empty(probs.shape[0], np.int32)
+            for r in range(probs.shape[0]):
+                kept = np.float32(0)
+                for j in range(k):
+                    kept = np.float32(kept + top[r, j])
+                target, cum, pick = np.float32(uniform[r]) * kept, np.float32(0), order[r, 0]
+                for j in range(k):
+                    cum = np.float32(cum + top[r, j])
+                    if target <= cum:
+                        pick = order[r, j]
+                        break
+                sampled[r] = pick
+        return top, order.astype(np.int32), sampled
+
     def rmsnorm(self, x, w, axes, eps):
         x, w = _f32(x), _f32(w)
         y = np.empty_like(x)

@@ -141,6 +141,12 @@ def main() -> None:
     g["mmask_c_batched"] = R.masked_matmul(a, b3, mk, 0.0)
     g["mmask_c_shared_naive"] = R.masked_matmul(a, b2, mk, -1.5, backend=0)
 
+    # ---- top-k sampling: probabilities from the reference's softmax, k = 20 as in its generate loop -----------
+    lg = (N(3, 5000) * 3.0).astype(np.float32)
+    un = np.array([0.0, 0.37, 0.999], np.float32)
+    tp, ti, ts = R.topk_sample(lg, 20, un)
+    g["topk_logits"], g["topk_uniform"], g["topk_probs"], g["topk_idx"], g["topk_sampled"] = lg, un, tp, ti, ts
+
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 

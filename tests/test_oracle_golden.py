@@ -50,6 +50,13 @@ def test_masked_matmul(golden, port):
     assert normwise(golden["mmask_c_shared_naive"], c) < 1e-6
 
 
+def test_topk_sampling(golden, port):
+    tp, ti, ts = port.topk_sample(golden["topk_logits"], 20, golden["topk_uniform"])
+    assert np.array_equal(ti, golden["topk_idx"]) and np.array_equal(tp, golden["topk_probs"])
+    assert np.array_equal(ts, golden["topk_sampled"])
+    assert np.all(np.diff(golden["topk_probs"], axis=1) <= 0)
+
+
 def test_matmul(golden, port):
     a = golden["mm_a"]
     assert np.array_equal(port.matmul(a, golden["mm_b2"]), golden["mm_c_shared"])

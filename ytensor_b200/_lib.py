@@ -50,6 +50,7 @@ SIGNATURES = {
     "ytcuda_embedding": (_i, [_vp, _vp, _vp, _i64, _i, _i, _vp]),
     "ytcuda_linear_w16": (_i, [_vp, _i64, _vp, _vp, _i64, _i64, _i, _i, _i, _vp, _vp]),
     "ytcuda_qwen3_qkv_post": (_i, [_vp] * 8 + [_i] * 8 + [_f, _vp]),
+    "ytcuda_topk_sample": (_i, [_vp, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "ytcuda_qwen3_create": (_vp, [_i] * 7 + [_f, _f, _i, _i, _i, _i]),
     "ytcuda_qwen3_destroy": (None, [_vp]),
     "ytcuda_qwen3_set_weight": (_i, [_vp, C.c_char_p, _i, _vp]),

@@ -345,6 +345,29 @@ def copy_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     return dst
 
 
+def topk_sample(logits: torch.Tensor, k: int = 20, uniform: torch.Tensor | None = None):
+    """Top-k sampling as qwen3::Qwen3ForCausalLM::generate does it (example/qwen3/src/qwen3.cpp:465-486).
+
+    logits fp32 [rows, vocab]. Returns (top_probs [rows, k], top_idx [rows, k] int32, sampled [rows] int32 or None):
+    the k most probable tokens of softmax(logits) in descending order and, when `uniform` (fp32 [rows], numbers in
+    [0, 1]) is given, the token whose running sum first reaches uniform * sum(top_probs)."""
+    _require_cuda(logits, uniform)
+    if logits.dim() != 2 or logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "topk_sample: logits must be fp32 [rows, vocab], unit stride")
+    rows, vocab = logits.shape
+    probs = torch.empty(rows, k, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(rows, k, dtype=torch.int32, device=logits.device)
+    sampled = None
+    if uniform is not None:
+        if uniform.dtype != torch.float32 or uniform.numel() != rows or not uniform.is_contiguous():
+            raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "topk_sample: uniform must be fp32 [rows]")
+        sampled = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    check(lib().ytcuda_topk_sample(logits.data_ptr(), logits.stride(0), rows, vocab, k,
+                                   uniform.data_ptr() if uniform is not None else None, probs.data_ptr(),
+                                   idx.data_ptr(), sampled.data_ptr() if sampled is not None else None, _stream()))
+    return probs, idx, sampled
+
+
 def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """swish(gate) * up for a fused [..., 2*I] projection (example/qwen3/src/qwen3.cpp:193-200)."""
     _require_cuda(gate_up)
