@@ -72,3 +72,21 @@ def test_ties_take_the_lower_index_and_bad_k_is_refused(api):
         api.topk_sample(x, 65)
     with pytest.raises(ValueError):
         api.topk_sample(x, 0)
+
+
+def test_sampled_generation_stays_inside_the_top_k(api):
+    from ytensor_b200 import qwen3 as Q
+    cfg = Q.Qwen3Config(hidden_size=64, num_hidden_layers=2, vocab_size=512, intermediate_size=96, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=128, max_position_embeddings=64)
+    m = Q.Qwen3ForCausalLM(cfg, batch=2)
+    m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
+    ids = dev(np.random.default_rng(0).integers(0, 512, (2, 7)).astype(np.int32))
+    a = m.generate_topk(ids, 12, k=5, seed=1).cpu().numpy()
+    m.reset_kv_cache()
+    b = m.generate_topk(ids, 12, k=5, seed=1).cpu().numpy()
+    assert np.array_equal(a, b)                      # the same seed gives the same tokens
+    m.reset_kv_cache()
+    g = m.generate_topk(ids, 12, k=1).cpu().numpy()  # k = 1 is greedy decoding
+    m.reset_kv_cache()
+    assert np.array_equal(g, m.generate_greedy(ids, 12).cpu().numpy())
+    m.close()

@@ -237,6 +237,25 @@ class Qwen3ForCausalLM:
                 logits = self.forward(tok.reshape(self.batch, 1).contiguous())
         return out
 
+    def generate_topk(self, prompt_ids, steps: int, k: int = 20, seed: int = 42):
+        """Sampled generation as Qwen3ForCausalLM::generate does it (reference qwen3.cpp:459-516): after every
+        forward the next token is drawn among the k most probable ones. The uniform numbers come from a host
+        generator (numpy's MT19937 seeded with `seed`; the reference's std::uniform_real_distribution consumes its
+        std::mt19937 differently, so the streams are not the same). Single GPU. Returns int32 [batch, steps]."""
+        from . import api
+        torch = self.torch
+        assert self.tp_world == 1, "sampling needs the whole vocabulary on one GPU"
+        rng = np.random.Generator(np.random.MT19937(seed))
+        out = torch.empty(self.batch, steps, dtype=torch.int32, device=prompt_ids.device)
+        logits = self.forward(prompt_ids)
+        for s in range(steps):
+            u = torch.from_numpy(rng.random(self.batch, dtype=np.float32)).to(prompt_ids.device)
+            _, _, tok = api.topk_sample(logits, k, u)
+            out[:, s] = tok
+            if s + 1 < steps:
+                logits = self.forward(tok.reshape(self.batch, 1).contiguous())
+        return out
+
     def close(self):
         if self.h:
             self.L.ytcuda_qwen3_destroy(self.h)
