@@ -273,7 +273,10 @@ int ytcuda_qwen3_set_decode_path(void* handle, int path);
 int ytcuda_qwen3_tp_export(void* handle, void* ipc_handle_64);
 int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64);
 /* ids [batch, len] int32 (device) -> logits of the last position [batch, rank's vocab rows] fp32 (device); appends
- * len tokens to the KV caches (Qwen3ForCausalLM::forward, qwen3.cpp:449-457). */
+ * len tokens to the KV caches (Qwen3ForCausalLM::forward, qwen3.cpp:449-457). The caches are ring buffers as in the
+ * reference (qwen3.cpp:70-126): once max_position_embeddings tokens are cached, a call with len == 1 overwrites the
+ * oldest slot, attends to every slot and uses rotary position 0 (the reference's position rule, :365-375); a call
+ * with len > 1 that would run past the end returns YTC_UNSUPPORTED. */
 int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream);
 
 #ifdef __cplusplus

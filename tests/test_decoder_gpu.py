@@ -127,6 +127,31 @@ def test_long_prefill_uses_tensor_cores_and_matches_oracle(Q, port):
     om.close()
 
 
+@pytest.mark.parametrize("path", [1, 2])
+def test_ring_buffer_cache_past_its_end_matches_reference(Q, path):
+    """The reference's KV cache is a ring buffer: past its end a token overwrites the oldest slot, sees every slot and
+    takes rotary position 0. Golden logits: 9-token prompt + 19 steps with max_position_embeddings = 16."""
+    from pathlib import Path
+    from ytensor_b200 import _lib
+    g = np.load(Path(__file__).resolve().parent / "golden" / "golden_qwen3_wrap.npz")
+    cfg = Q.Qwen3Config(**{**SMALL, "max_position_embeddings": 16})
+    m = Q.Qwen3ForCausalLM(cfg, batch=1)
+    m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
+    m.set_decode_path(path)
+    want = g["wrap_logits"]
+    logits = m.forward(dev_ids(g["wrap_ids"]))
+    for step in range(20):
+        got = logits.cpu().numpy()
+        assert normwise(got, want[step]) < 1e-4, step
+        assert np.array_equal(got.argmax(1), want[step].argmax(1))
+        assert m.get_kv_cache_len() == min(9 + step, 16)
+        if step < 19:
+            logits = m.forward(dev_ids(want[step].argmax(1).reshape(1, 1)))
+    with pytest.raises(_lib.YtCudaInvalidArgument):  # several tokens at once past the end: refused
+        m.forward(dev_ids(np.zeros((1, 3), np.int32)))
+    m.close()
+
+
 def test_cache_overflow_is_reported(Q):
     from ytensor_b200 import _lib
     cfg = Q.Qwen3Config(**SMALL)

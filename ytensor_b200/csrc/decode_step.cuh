@@ -54,7 +54,11 @@ struct DsLayer {
 };
 
 struct DecodeStepParams {
-  int B, hidden, layers, heads, kv_heads, inter, vocab_rows, vocab, max_pos, pos;
+  int B, hidden, layers, heads, kv_heads, inter, vocab_rows, vocab, max_pos;
+  // pos: cache slot the token of this step is written to; rope_pos: its rotary position; n_keys: keys it attends
+  // to, the new one included (pos + 1, or the whole cache once the ring buffer has wrapped: reference
+  // example/qwen3/src/qwen3.cpp:70-126, 365-375)
+  int pos, rope_pos, n_keys;
   float eps, scale;
   const int32_t* ids;
   const uint16_t* embed;
@@ -614,9 +618,9 @@ __device__ __noinline__ void ds_attention_phase(const DecodeStepParams& p, const
   const int B = p.B;
   const int qkv_w = (p.heads + 2 * p.kv_heads) * D;
   const int units = B * p.kv_heads * p.chunks;
-  const int n_keys = p.pos + 1;
-  const float* cr = p.cos_t + static_cast<int64_t>(p.pos) * D;
-  const float* sr = p.sin_t + static_cast<int64_t>(p.pos) * D;
+  const int n_keys = p.n_keys;
+  const float* cr = p.cos_t + static_cast<int64_t>(p.rope_pos) * D;
+  const float* sr = p.sin_t + static_cast<int64_t>(p.rope_pos) * D;
   float* qs = xs;                 // [G][128] query heads of the group, normalised and rotated
   float* pm = qs + G * D;         // [DS_WARPS][G] running maxima of the warps
   float* pl = pm + DS_WARPS * G;  // sums
@@ -829,7 +833,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
     const int chunk = blockIdx.x % p.chunks, bk = blockIdx.x / p.chunks;
     const int k_begin = chunk * p.keys_per_chunk;
     int k_end = k_begin + p.keys_per_chunk;
-    if (k_end > p.pos) k_end = p.pos;
+    if (k_end > p.n_keys) k_end = p.n_keys;
     kv_off = (static_cast<int64_t>(bk) * p.max_pos + k_begin) * D;
     kv_lines = k_end > k_begin ? (k_end - k_begin) * 4 : 0;
   }

@@ -275,7 +275,8 @@ struct Qwen3Model {
   // device state owned by the model
   float *cos_t = nullptr, *sin_t = nullptr;
   float *k_cache = nullptr, *v_cache = nullptr;  // [layers][batch, l_kv_heads, max_pos, head_dim]
-  int cur_len = 0;
+  int cur_len = 0;           // tokens in the cache (at most max_pos)
+  int64_t total_written = 0; // tokens ever appended: the ring buffer writes slot total_written % max_pos
   // activations
   float *x = nullptr, *h = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr, *act = nullptr,
         *proj = nullptr, *last = nullptr;
@@ -575,6 +576,7 @@ int ytcuda_qwen3_reset(void* handle) {
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m, "ytcuda_qwen3_reset: null handle");
   m->cur_len = 0;
+  m->total_written = 0;
   return YTC_OK;
 }
 // Allocates this rank's exchange buffer for the tensor-parallel step kernel and returns its CUDA IPC handle
@@ -708,7 +710,11 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   if (smem < att) smem = att;
   DecodeStepParams p{};
   p.B = B; p.hidden = m->hidden; p.layers = m->layers; p.heads = m->l_heads; p.kv_heads = m->l_kv_heads;
-  p.inter = m->l_inter; p.vocab_rows = m->l_vocab; p.vocab = m->vocab; p.max_pos = m->max_pos; p.pos = m->cur_len;
+  p.inter = m->l_inter; p.vocab_rows = m->l_vocab; p.vocab = m->vocab; p.max_pos = m->max_pos;
+  const bool wrapped = m->total_written >= m->max_pos;  // (the caller has checked that the cache is then full)
+  p.pos = static_cast<int>(m->total_written % m->max_pos);
+  p.rope_pos = wrapped ? 0 : p.pos;
+  p.n_keys = wrapped ? m->max_pos : p.pos + 1;
   p.eps = m->eps; p.scale = 1.0f / std::sqrt(static_cast<float>(D));
   p.ids = ids; p.embed = m->embed; p.lm_head = m->lm_head; p.final_norm = m->final_norm; p.lw = m->ds_lw;
   p.cos_t = m->cos_t; p.sin_t = m->sin_t; p.k_cache = m->k_cache; p.v_cache = m->v_cache;
@@ -725,7 +731,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   }
   p.x = m->x; p.qkv = m->qkv; p.attn = m->attn; p.act = m->act; p.logits = logits; p.part = m->ds_part;
   p.sync = m->ds_sync; p.status = device_status_word();
-  const int keys = m->cur_len + 1;
+  const int keys = p.n_keys;
   // Key chunks of 128 keys (8 per warp), fewer and longer ones when that would be more units than CTAs or more
   // than DS_MAX_CHUNKS chunks.
   int n_chunks = (keys + 127) / 128;
@@ -767,9 +773,15 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m && ids && logits, "ytcuda_qwen3_forward: null argument");
   YTC_REQUIRE(len > 0, "ytcuda_qwen3_forward: len must be positive");
-  if (m->cur_len + len > m->max_pos) {
-    set_last_error("ytcuda_qwen3_forward: %d cached + %d new tokens exceed max_position_embeddings %d "
-                   "(the reference's ring-buffer wrap is not implemented on the device)", m->cur_len, len, m->max_pos);
+  // The KV cache is a ring buffer (reference example/qwen3/src/qwen3.cpp:70-126): once it is full, a new token
+  // overwrites the oldest slot, sees every slot, and takes rotary position 0 (the position rule of
+  // Qwen3Model::forward, :365-375, falls back to 0 when the running position no longer fits the table). The device
+  // follows that for one new token per call; a longer input that would run over the end of the cache is refused.
+  const bool wrap_step = len == 1 && m->total_written >= m->max_pos;
+  if (!wrap_step && m->total_written + len > m->max_pos) {
+    set_last_error("ytcuda_qwen3_forward: %lld cached + %d new tokens exceed max_position_embeddings %d (past the end "
+                   "of the cache the device takes one token per call, as the ring buffer of the reference does)",
+                   static_cast<long long>(m->total_written), len, m->max_pos);
     return YTC_UNSUPPORTED;
   }
   YTC_REQUIRE(m->embed && m->lm_head && m->final_norm, "ytcuda_qwen3_forward: embed / lm_head / norm not set");
@@ -784,13 +796,19 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   const int64_t rows = static_cast<int64_t>(B) * len;
   int s = ensure_activations(m, rows);
   if (s != YTC_OK) return s;
-  const int pos0 = m->cur_len;
-  const int kv_len = pos0 + len;
+  // rotary position of the first new token, the slot it is written to, and the keys visible after the append
+  const int pos0 = wrap_step ? 0 : static_cast<int>(m->total_written);
+  const int slot0 = static_cast<int>(m->total_written % m->max_pos);
+  const int kv_len = wrap_step ? m->max_pos : pos0 + len;
+  auto advance = [&]() {
+    m->total_written += len;
+    m->cur_len = m->total_written < m->max_pos ? static_cast<int>(m->total_written) : m->max_pos;
+  };
   // Automatic choice: the step kernel up to DS_AUTO_B sequences. Beyond that its FFMA linears lose against the
   // tensor-core linears of the operator path (measured at 16 and 32 sequences), so it runs only when asked for.
   if (len == 1 && (m->decode_path == 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B)) && decode_step_supported(m)) {
     if ((s = decode_step_launch(m, ids, logits, st)) != YTC_OK) return s;
-    m->cur_len = kv_len;
+    advance();
     return YTC_OK;
   }
   if (len == 1 && m->decode_path == 2) {
@@ -811,14 +829,14 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     if ((s = rmsnorm_rows(m->x, W.norm1, m->h, rows, Hd, m->eps, st)) != YTC_OK) return s;
     if ((s = linear_w16(m, m->h, Hd, W.qkv, m->qkv, qkv_w, rows, qkv_w, Hd, false, st)) != YTC_OK) return s;
     if ((s = ytcuda_qwen3_qkv_post(m->qkv, m->q, kc, vc, W.q_norm, W.k_norm, m->cos_t, m->sin_t, B, len, m->l_heads,
-                                   m->l_kv_heads, D, m->max_pos, pos0, pos0, m->eps, st)) != YTC_OK)
+                                   m->l_kv_heads, D, m->max_pos, pos0, slot0, m->eps, st)) != YTC_OK)
       return s;
     // attention over the cache; the output lands as [B, len, heads, D] = rows x (heads * D)
     const int64_t qs[3] = {static_cast<int64_t>(m->l_heads) * len * D, static_cast<int64_t>(len) * D, D};
     const int64_t ks[3] = {static_cast<int64_t>(m->l_kv_heads) * m->max_pos * D, static_cast<int64_t>(m->max_pos) * D, D};
     const int64_t os[3] = {static_cast<int64_t>(len) * m->l_heads * D, D, static_cast<int64_t>(m->l_heads) * D};
     if ((s = ytcuda_flash_attn_fwd(YTC_F32, m->q, kc, vc, m->attn, B, m->l_kv_heads, groups, len, kv_len, D, D, scale, qs,
-                                   ks, ks, os, 1, kv_len - len, nullptr, 0, nullptr, 0, 0, st)) != YTC_OK)
+                                   ks, ks, os, wrap_step ? 0 : 1, kv_len - len, nullptr, 0, nullptr, 0, 0, st)) != YTC_OK)
       return s;
     if (m->tp_world == 1) {  // x2 = attn + x: the projection accumulates into the residual stream
       if ((s = linear_w16(m, m->attn, m->l_heads * D, W.o, m->x, Hd, rows, Hd, m->l_heads * D, true, st)) != YTC_OK)
@@ -857,7 +875,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
                              cudaMemcpyDeviceToDevice, st));
   if ((s = rmsnorm_rows(last_in, m->final_norm, last_out, B, Hd, m->eps, st)) != YTC_OK) return s;
   if ((s = linear_w16(m, last_out, Hd, m->lm_head, logits, m->l_vocab, B, m->l_vocab, Hd, false, st)) != YTC_OK) return s;
-  m->cur_len = kv_len;
+  advance();
   return YTC_OK;
 }
 
