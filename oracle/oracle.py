@@ -167,6 +167,19 @@ class _Backend:
         self._fn("swish_f32")(_opt(x), _opt(y), C.c_int64(x.size))
         return y
 
+    ACTIVATIONS = {"swish": 1, "relu": 4, "exp": 5, "sigmoid": 6, "leakyRelu": 7, "elu": 8, "selu": 9, "gelu": 10,
+                   "tanh": 11, "softplus": 12, "mish": 13, "hardSigmoid": 14, "hardSwish": 15}
+
+    def activation(self, name, x, alpha=None):
+        """yt::function::<name> (reference include/function/activation.hpp:9-109), forward form."""
+        x = _f32(x)
+        y = np.empty_like(x)
+        if alpha is None:
+            alpha = {"leakyRelu": 0.01, "elu": 1.0}.get(name, 0.0)
+        rc = self._fn("activation_f32")(self.ACTIVATIONS[name], _opt(x), _opt(y), C.c_int64(x.size), C.c_float(alpha))
+        assert rc == 0, rc
+        return y
+
     def chain(self, x, w, r, eps=1e-6):
         x, w, r = _f32(x), _f32(w), _f32(r)
         B, L, H = x.shape

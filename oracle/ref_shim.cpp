@@ -373,6 +373,37 @@ int ytref_swish_f32(const float* x, float* y, int64_t n) {
   }
 }
 
+// The activations of include/function/activation.hpp:9-109, forward form (order 0), in place on a copy of x.
+// op: 4 relu, 5 exp, 6 sigmoid, 7 leakyRelu(alpha), 8 elu(alpha), 9 selu, 10 gelu, 11 tanh, 12 softplus, 13 mish,
+// 14 hardSigmoid, 15 hardSwish (1 is swish).
+int ytref_activation_f32(int op, const float* x, float* y, int64_t n, float alpha) {
+  try {
+    const int s[2] = {1, static_cast<int>(n)};
+    auto t = make<2>(x, s);
+    namespace F = yt::function;
+    switch (op) {
+      case 1: F::swish_(t); break;
+      case 4: F::relu_(t); break;
+      case 5: F::exp_(t); break;
+      case 6: F::sigmoid_(t); break;
+      case 7: F::leakyRelu_(t, alpha); break;
+      case 8: F::elu_(t, alpha); break;
+      case 9: F::selu_(t); break;
+      case 10: F::gelu_(t); break;
+      case 11: F::tanh_(t); break;
+      case 12: F::softplus_(t); break;
+      case 13: F::mish_(t); break;
+      case 14: F::hardSigmoid_(t); break;
+      case 15: F::hardSwish_(t); break;
+      default: return 2;
+    }
+    dump(t, y);
+    return 0;
+  } catch (const std::exception&) {
+    return 1;
+  }
+}
+
 void ytref_f32_to_bf16(const float* x, uint16_t* y, int64_t n) {
   for (int64_t i = 0; i < n; ++i) {
     yt::bfloat16 v(x[i]);

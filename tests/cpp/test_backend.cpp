@@ -127,6 +127,14 @@ int main() {
     report("operator+ with broadcast", normwise(yt::cuda::add(x, r), x + r), 1e-30);
     report("operator* with broadcast", normwise(yt::cuda::mul(x, r), x * r), 1e-30);
     report("swish", normwise(yt::cuda::swish(x), yt::function::swish(x)), 1e-6);
+    {  // (the reference's out-of-place relu does not compile for float: its lambda returns two types)
+      auto xr = x.clone();
+      report("relu", normwise(yt::cuda::relu(x), yt::function::relu_(xr)), 1e-30);
+    }
+    report("gelu", normwise(yt::cuda::gelu(x), yt::function::gelu(x)), 1e-6);
+    report("elu(0.5)", normwise(yt::cuda::elu(x, 0.5f), yt::function::elu(x, 0.5f)), 1e-6);
+    report("mish", normwise(yt::cuda::mish(x), yt::function::mish(x)), 1e-6);
+    report("hardSwish", normwise(yt::cuda::hardSwish(x), yt::function::hardSwish(x)), 1e-30);
   }
   std::printf("%s (%d failures)\n", g_fail ? "SOME CASES FAILED" : "ALL CASES PASSED", g_fail);
   return g_fail ? 1 : 0;

@@ -147,6 +147,16 @@ def main() -> None:
     tp, ti, ts = R.topk_sample(lg, 20, un)
     g["topk_logits"], g["topk_uniform"], g["topk_probs"], g["topk_idx"], g["topk_sampled"] = lg, un, tp, ti, ts
 
+    # ---- the other activations, forward form; values around the branch points and in both tails -------------
+    ax = np.concatenate([N(4000) * 3.0, np.array([0.0, -0.0, 3.0, -3.0, 2.9999998, -2.9999998, 20.0, -20.0, 88.0,
+                                                  -88.0, -104.0, 1e-8, -1e-8], np.float32)]).astype(np.float32)
+    g["act_x"] = ax
+    for name in ("relu", "exp", "sigmoid", "leakyRelu", "elu", "selu", "gelu", "tanh", "softplus", "mish",
+                 "hardSigmoid", "hardSwish"):
+        g[f"act_{name}"] = R.activation(name, ax)
+    g["act_leakyRelu_0p2"] = R.activation("leakyRelu", ax, 0.2)
+    g["act_elu_0p5"] = R.activation("elu", ax, 0.5)
+
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 

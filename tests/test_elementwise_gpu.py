@@ -57,6 +57,43 @@ def test_swish_and_swiglu(api, port, golden):
     assert normwise(api.swiglu(dev(gu)).cpu().numpy(), want) < 1e-6
 
 
+@pytest.mark.parametrize("name,alpha,key", [
+    ("relu", None, "act_relu"), ("exp", None, "act_exp"), ("sigmoid", None, "act_sigmoid"),
+    ("leakyRelu", None, "act_leakyRelu"), ("leakyRelu", 0.2, "act_leakyRelu_0p2"), ("elu", None, "act_elu"),
+    ("elu", 0.5, "act_elu_0p5"), ("selu", None, "act_selu"), ("gelu", None, "act_gelu"), ("tanh", None, "act_tanh"),
+    ("softplus", None, "act_softplus"), ("mish", None, "act_mish"), ("hardSigmoid", None, "act_hardSigmoid"),
+    ("hardSwish", None, "act_hardSwish")])
+def test_activations_match_reference(api, golden, name, alpha, key):
+    x, want = golden["act_x"], golden[key]
+    args = () if alpha is None else (alpha,)
+    got = getattr(api, name)(dev(x), *args).cpu().numpy()
+    if name in ("relu", "leakyRelu", "hardSwish", "hardSigmoid"):
+        assert np.array_equal(got, want)  # comparisons and one or two IEEE operations: exact
+    else:
+        # device exp / erf / tanh / log1p differ from the host libm by a few ulp: 1e-5 relative per element, with an
+        # absolute floor for results that cancel towards zero (elu and selu near 0, gelu in its negative tail)
+        assert np.all(np.abs(got.astype(np.float64) - want) <= 1e-5 * np.abs(want) + 2e-7)
+    d = dev(x)
+    r = getattr(api, name + "_")(d, *args)
+    assert r.data_ptr() == d.data_ptr() and np.array_equal(d.cpu().numpy(), got)  # the in-place form
+
+
+def test_activation_dtypes_and_bad_op(api, port):
+    from ytensor_b200 import _lib
+    x = (np.random.default_rng(5).standard_normal(3000) * 2).astype(np.float32)
+    xb = dev(x).to(torch.bfloat16)
+    got = api.gelu(xb)
+    assert got.dtype == torch.bfloat16
+    want = port.activation("gelu", xb.float().cpu().numpy())
+    assert normwise(got.float().cpu().numpy(), want) < 2e-2
+    assert api.relu(dev(np.zeros((0, 4), np.float32))).shape == (0, 4)
+    t = dev(x)
+    with pytest.raises(RuntimeError):
+        api._unary(16, t, None, 0.0)
+    with pytest.raises(RuntimeError):
+        api._unary(-1, t, None, 0.0)
+
+
 def test_casts_bit_exact(api, port, golden):
     x = golden["cast_x"]
     assert np.array_equal(torch_to_bits(api.cast(dev(x), torch.bfloat16)), golden["cast_bf16"])

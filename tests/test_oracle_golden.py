@@ -103,6 +103,19 @@ def test_elementwise(golden, port):
     assert np.array_equal(port.swish(golden["swish_x"]), golden["swish_y"])
 
 
+ACT_CASES = [("relu", None, "act_relu"), ("exp", None, "act_exp"), ("sigmoid", None, "act_sigmoid"),
+             ("leakyRelu", None, "act_leakyRelu"), ("leakyRelu", 0.2, "act_leakyRelu_0p2"), ("elu", None, "act_elu"),
+             ("elu", 0.5, "act_elu_0p5"), ("selu", None, "act_selu"), ("gelu", None, "act_gelu"),
+             ("tanh", None, "act_tanh"), ("softplus", None, "act_softplus"), ("mish", None, "act_mish"),
+             ("hardSigmoid", None, "act_hardSigmoid"), ("hardSwish", None, "act_hardSwish")]
+
+
+@pytest.mark.parametrize("name,alpha,key", ACT_CASES)
+def test_activations(golden, port, name, alpha, key):
+    # the same libm calls in the same order as the reference: bit-exact on this host
+    assert np.array_equal(port.activation(name, golden["act_x"], alpha), golden[key], equal_nan=True)
+
+
 def test_chain(golden, port):
     for r in ("r1", "r2"):
         got = port.chain(golden["chain_x"], golden["chain_w"], golden[f"chain_{r}"])

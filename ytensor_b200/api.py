@@ -326,6 +326,29 @@ def swish_(x):
     """x * sigmoid(x) in place (reference yt::function::swish_, src/function/activation.inl:631-647)."""
     return _unary(1, x, x)
 
+# The other activations of yt::function (reference src/function/activation.inl), forward form; `name_` works in place.
+_ACTIVATIONS = {"relu": 4, "exp": 5, "sigmoid": 6, "leakyRelu": 7, "elu": 8, "selu": 9, "gelu": 10, "tanh": 11,
+                "softplus": 12, "mish": 13, "hardSigmoid": 14, "hardSwish": 15}
+_ACT_DEFAULT_PARAM = {"leakyRelu": 0.01, "elu": 1.0}
+
+
+def _make_activation(name: str, op: int):
+    default = _ACT_DEFAULT_PARAM.get(name)
+
+    def f(x, alpha=default):
+        return _unary(op, x, None, 0.0 if alpha is None else float(alpha))
+
+    def f_(x, alpha=default):
+        return _unary(op, x, x, 0.0 if alpha is None else float(alpha))
+
+    f.__name__, f_.__name__ = name, name + "_"
+    f.__doc__ = f_.__doc__ = f"yt::function::{name} (reference src/function/activation.inl), forward form."
+    return f, f_
+
+
+for _n, _op in _ACTIVATIONS.items():
+    globals()[_n], globals()[_n + "_"] = _make_activation(_n, _op)
+
 
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """dtype conversion with the reference's rounding (YTensorBase::cast, include/ytensor_base.hpp:399-404)."""

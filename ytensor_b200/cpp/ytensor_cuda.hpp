@@ -325,19 +325,35 @@ template <typename T, int dim> yt::YTensor<T, dim> sub(const yt::YTensor<T, dim>
 template <typename T, int dim> yt::YTensor<T, dim> mul(const yt::YTensor<T, dim>& a, const yt::YTensor<T, dim>& b) { return detail::binary(2, a, b); }
 template <typename T, int dim> yt::YTensor<T, dim> div(const yt::YTensor<T, dim>& a, const yt::YTensor<T, dim>& b) { return detail::binary(3, a, b); }
 
-// yt::function::swish (src/function/activation.inl:605-647, order 0)
+namespace detail {
 template <typename T, int dim>
-yt::YTensor<T, dim> swish(const yt::YTensor<T, dim>& x) {
-  DeviceBuffer dx = detail::to_device(x);
+yt::YTensor<T, dim> unary(int op, const yt::YTensor<T, dim>& x, float param = 0.f) {
+  DeviceBuffer dx = to_device(x);
   yt::YTensor<T, dim> y(x.shape());
   DeviceBuffer dy(y.size() * sizeof(T));
-  const auto shape = detail::widen(x.shape());
-  const auto st = detail::contiguous_strides(x.shape());
-  check(ytcuda_unary(1, dtype_of<T>(), dtype_of<T>(), dx.get(), dy.get(), dim, shape.data(), st.data(), st.data(), 0.f,
-                     nullptr));
+  const auto shape = widen(x.shape());
+  const auto st = contiguous_strides(x.shape());
+  check(ytcuda_unary(op, dtype_of<T>(), dtype_of<T>(), dx.get(), dy.get(), dim, shape.data(), st.data(), st.data(),
+                     param, nullptr));
   dy.download(y.data());
   return y;
 }
+}  // namespace detail
+
+// the activations of yt::function, forward form (include/function/activation.hpp:9-109; order 0)
+template <typename T, int dim> yt::YTensor<T, dim> swish(const yt::YTensor<T, dim>& x) { return detail::unary(1, x); }
+template <typename T, int dim> yt::YTensor<T, dim> relu(const yt::YTensor<T, dim>& x) { return detail::unary(4, x); }
+template <typename T, int dim> yt::YTensor<T, dim> exp(const yt::YTensor<T, dim>& x) { return detail::unary(5, x); }
+template <typename T, int dim> yt::YTensor<T, dim> sigmoid(const yt::YTensor<T, dim>& x) { return detail::unary(6, x); }
+template <typename T, int dim> yt::YTensor<T, dim> leakyRelu(const yt::YTensor<T, dim>& x, float alpha = 0.01f) { return detail::unary(7, x, alpha); }
+template <typename T, int dim> yt::YTensor<T, dim> elu(const yt::YTensor<T, dim>& x, float alpha = 1.0f) { return detail::unary(8, x, alpha); }
+template <typename T, int dim> yt::YTensor<T, dim> selu(const yt::YTensor<T, dim>& x) { return detail::unary(9, x); }
+template <typename T, int dim> yt::YTensor<T, dim> gelu(const yt::YTensor<T, dim>& x) { return detail::unary(10, x); }
+template <typename T, int dim> yt::YTensor<T, dim> tanh(const yt::YTensor<T, dim>& x) { return detail::unary(11, x); }
+template <typename T, int dim> yt::YTensor<T, dim> softplus(const yt::YTensor<T, dim>& x) { return detail::unary(12, x); }
+template <typename T, int dim> yt::YTensor<T, dim> mish(const yt::YTensor<T, dim>& x) { return detail::unary(13, x); }
+template <typename T, int dim> yt::YTensor<T, dim> hardSigmoid(const yt::YTensor<T, dim>& x) { return detail::unary(14, x); }
+template <typename T, int dim> yt::YTensor<T, dim> hardSwish(const yt::YTensor<T, dim>& x) { return detail::unary(15, x); }
 
 // YTensorBase::cast / copy_ between float, bfloat16 and float16 (src/ytensor_base.inl:257-430), bit-exact with the
 // reference's own constructors

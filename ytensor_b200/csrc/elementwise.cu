@@ -13,7 +13,13 @@ namespace ytk {
 
 constexpr int EW_MAXD = 8;
 enum BinOp { B_ADD = 0, B_SUB = 1, B_MUL = 2, B_DIV = 3 };
-enum UnOp { U_COPY = 0, U_SWISH = 1, U_SCALE = 2, U_ADD_SCALAR = 3 };
+enum UnOp {
+  U_COPY = 0, U_SWISH = 1, U_SCALE = 2, U_ADD_SCALAR = 3,
+  // the other activations of yt::function (src/function/activation.inl), forward form (order 0)
+  U_RELU = 4, U_EXP = 5, U_SIGMOID = 6, U_LEAKY_RELU = 7, U_ELU = 8, U_SELU = 9, U_GELU = 10, U_TANH = 11,
+  U_SOFTPLUS = 12, U_MISH = 13, U_HARD_SIGMOID = 14, U_HARD_SWISH = 15
+};
+constexpr int U_LAST = U_HARD_SWISH;
 
 __device__ __forceinline__ float bin_apply(int op, float a, float b) {
   switch (op) {
@@ -36,12 +42,38 @@ __device__ __forceinline__ float swish_ref(float v) {
   }
   return v * sig;
 }
+// sigmoid and softplus in the reference's stable forms (src/ytensor_function.inl:42-59)
+__device__ __forceinline__ float sigmoid_ref(float v) {
+  if (v >= 0.f) return 1.0f / (1.0f + expf(-v));
+  const float z = expf(v);
+  return z / (1.0f + z);
+}
+__device__ __forceinline__ float softplus_ref(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+
 __device__ __forceinline__ float un_apply(int op, float a, float param) {
   switch (op) {
     case U_COPY: return a;
     case U_SWISH: return swish_ref(a);
     case U_SCALE: return a * param;
-    default: return a + param;
+    case U_ADD_SCALAR: return a + param;
+    case U_RELU: return fmaxf(a, 0.f);                                              // activation.inl:3-10
+    case U_EXP: return expf(a);                                                     // :67-72
+    case U_SIGMOID: return sigmoid_ref(a);                                          // :87-93
+    case U_LEAKY_RELU: return a > 0.f ? a : param * a;                              // :413-420
+    case U_ELU: return a > 0.f ? a : param * (expf(a) - 1.0f);                      // :449-456
+    case U_SELU: {                                                                  // :485-494
+      const float l = 1.0507009873554804934193349852946f, al = 1.6732632423543772848170429916717f;
+      return a > 0.f ? l * a : l * al * (expf(a) - 1.0f);
+    }
+    case U_GELU: return 0.5f * a * (1.0f + erff(a / 1.4142135623730950488016887242097f));  // :529-537
+    case U_TANH: return tanhf(a);                                                   // :575-582
+    case U_SOFTPLUS: return softplus_ref(a);                                        // :651-657
+    case U_MISH: return a * tanhf(softplus_ref(a));                                 // :681-688
+    case U_HARD_SIGMOID: return fmaxf(0.f, fminf(1.f, a / 6.0f + 0.5f));            // :724-731
+    default:                                                                        // hardSwish, :760-775
+      if (a <= -3.f) return 0.f;
+      if (a >= 3.f) return a;
+      return a * (a + 3.f) / 6.0f;
   }
 }
 
@@ -228,7 +260,7 @@ int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const v
 
 int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
                  const int64_t* xstrides, const int64_t* ystrides, float param, void* stream) {
-  YTC_REQUIRE(op >= 0 && op <= 3, "ytcuda_unary: op must be 0..3 (copy, swish, scale, add scalar)");
+  YTC_REQUIRE(op >= 0 && op <= U_LAST, "ytcuda_unary: op %d outside 0..%d", op, U_LAST);
   YTC_REQUIRE(ndim >= 1 && ndim <= EW_MAXD, "ytcuda_unary: ndim %d outside [1, %d]", ndim, EW_MAXD);
   YTC_REQUIRE(shape && xstrides && ystrides, "ytcuda_unary: null shape/strides");
   YTC_REQUIRE(dt_in >= 0 && dt_in <= 2 && dt_out >= 0 && dt_out <= 2, "ytcuda_unary: bad dtype");
