@@ -195,6 +195,91 @@ __global__ void __launch_bounds__(256) split_hi_lo_kernel(const float* x, int64_
   }
 }
 
+__device__ __forceinline__ void split_store4(const float f[4], uint16_t* hi, uint16_t* lo) {
+  uint16_t h[4], l[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const __nv_bfloat16 hb = __float2bfloat16_rn(f[k]);
+    const __nv_bfloat16 lb = __float2bfloat16_rn(f[k] - __bfloat162float(hb));
+    h[k] = *reinterpret_cast<const uint16_t*>(&hb);
+    l[k] = *reinterpret_cast<const uint16_t*>(&lb);
+  }
+  uint2 ph, pl;
+  ph.x = h[0] | (static_cast<uint32_t>(h[1]) << 16);
+  ph.y = h[2] | (static_cast<uint32_t>(h[3]) << 16);
+  pl.x = l[0] | (static_cast<uint32_t>(l[1]) << 16);
+  pl.y = l[2] | (static_cast<uint32_t>(l[3]) << 16);
+  *reinterpret_cast<uint2*>(hi) = ph;
+  *reinterpret_cast<uint2*>(lo) = pl;
+}
+
+// sum over the k pieces p of both planes, in index order (the order of sum_partials_kernel), of 4 adjacent elements
+__device__ __forceinline__ float4 sum_pieces4(const float* part, int n_part, int64_t mn, int64_t off) {
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+  for (int p = 0; p < n_part; ++p) {
+    const float4 a = *reinterpret_cast<const float4*>(part + 2 * p * mn + off);
+    const float4 b = *reinterpret_cast<const float4*>(part + (2 * p + 1) * mn + off);
+    s.x += a.x + b.x; s.y += a.y + b.y; s.z += a.z + b.z; s.w += a.w + b.w;
+  }
+  return s;
+}
+
+// The glue between two projections of a decode step with 9 .. 128 rows, one CTA per row of the residual stream:
+//   x[r] += sum of the k-split partial products of the projection before (when there are any),
+//   y = rmsNorm(x[r]) * w   (reference src/function/normalization.inl:234-277),
+//   y -> hi + lo bf16 planes, the left operand of the projection that follows.
+// Three launches (sum_partials, the row kernel, split_hi_lo) as one.
+__global__ void __launch_bounds__(256) sum_norm_split_kernel(const float* part, int n_part, int64_t mn, float* x,
+                                                             const float* w, float eps, uint16_t* hi, uint16_t* lo,
+                                                             int hidden) {
+  extern __shared__ float row_s[];
+  __shared__ float red[8];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < hidden; c += 1024) {
+    float4 v = *reinterpret_cast<const float4*>(x + base + c);
+    if (n_part > 0) {
+      const float4 s = sum_pieces4(part, n_part, mn, base + c);
+      v.x += s.x; v.y += s.y; v.z += s.z; v.w += s.w;
+      *reinterpret_cast<float4*>(x + base + c) = v;
+    }
+    *reinterpret_cast<float4*>(row_s + c) = v;
+    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = 1.0f / sqrtf(tot * (1.0f / hidden) + eps);
+  for (int c = threadIdx.x * 4; c < hidden; c += 1024) {
+    const float4 v = *reinterpret_cast<const float4*>(row_s + c);
+    const float4 g = *reinterpret_cast<const float4*>(w + c);
+    const float f[4] = {v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w};
+    split_store4(f, hi + base + c, lo + base + c);
+  }
+}
+
+// gate_up partial products [pieces][2][rows][2 * inter] -> swish(gate) * up (reference qwen3.cpp:150-162) -> hi + lo
+// planes [rows][inter] for the down projection. Three launches (sum_partials, swiglu, split_hi_lo) as one.
+__global__ void __launch_bounds__(256) sum_swiglu_split_kernel(const float* part, int n_part, int64_t mn, uint16_t* hi,
+                                                               uint16_t* lo, int64_t rows, int inter) {
+  const int per_row = inter / 4;
+  const int64_t total = rows * per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / per_row;
+    const int c = static_cast<int>(i - r * per_row) * 4;
+    const float4 g = sum_pieces4(part, n_part, mn, r * 2 * inter + c);
+    const float4 u = sum_pieces4(part, n_part, mn, r * 2 * inter + inter + c);
+    const float f[4] = {ds_swish(g.x) * u.x, ds_swish(g.y) * u.y, ds_swish(g.z) * u.z, ds_swish(g.w) * u.w};
+    split_store4(f, hi + r * inter + c, lo + r * inter + c);
+  }
+}
+
 // ------------------------------------------------------------------ per-head RMSNorm + RoPE + KV append
 // qkv [B, L, (H + 2*KVH) * D] fp32 (the fused projection output). One warp per (b, t, head) vector, D == 128:
 //   q heads: rmsNorm over D with q_norm, rotate-half RoPE at position pos0 + t -> q_out [B, H, L, D]
@@ -204,7 +289,7 @@ __global__ void __launch_bounds__(256) split_hi_lo_kernel(const float* x, int64_
 __global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* q_out, float* k_cache, float* v_cache,
                                                        const float* q_norm, const float* k_norm, const float* cos_t,
                                                        const float* sin_t, int B, int L, int H, int KVH, int max_len,
-                                                       int pos0, int slot0, float eps) {
+                                                       int pos0, int slot0, float eps, int n_part, int64_t mn) {
   constexpr int D = 128;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_all = H + 2 * KVH;
@@ -215,8 +300,17 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* 
     const int b = static_cast<int>(v / (static_cast<int64_t>(heads_all) * L));
     const float* src = qkv + (static_cast<int64_t>(b) * L + t) * heads_all * D + static_cast<int64_t>(hh) * D;
     float x[4];
+    if (n_part > 0) {  // `qkv` holds the k-split partial products [pieces][2][B * L][heads_all * D]: add them here
 #pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = src[lane + 32 * i];
+      for (int i = 0; i < 4; ++i) x[i] = 0.f;
+      for (int p = 0; p < n_part; ++p) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] += src[2 * p * mn + lane + 32 * i] + src[(2 * p + 1) * mn + lane + 32 * i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = src[lane + 32 * i];
+    }
     if (hh >= H + KVH) {  // value head
       float* dst = v_cache + ((static_cast<int64_t>(b) * KVH + (hh - H - KVH)) * max_len + slot0 + t) * D;
 #pragma unroll
@@ -314,6 +408,53 @@ static int dev_alloc(Qwen3Model* m, void** p, size_t bytes) {
 }
 
 // y[M, N] (+)= x[M, K] . W[N, K]^T with fp32 x / y and bf16 W.
+// ---- the projections of a step with 9 .. 128 rows, taken apart so that the glue between them can be fused ----
+static bool split_k_ok(int64_t M, int K) { return M <= 128 && K % 128 == 0 && K >= 256; }
+
+static int split_planes(Qwen3Model* m, const float* x, int64_t x_rs, int64_t M, int K, cudaStream_t st) {
+  const int64_t blocks = (M * (K / 4) + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  split_hi_lo_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, x_rs, m->hi, m->hi + M * K,
+                                                                                         M, K);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+struct Pieces {  // k-split partial products [n][2][M][N] of one projection
+  const float* part = nullptr;
+  int n = 0;
+  int64_t mn = 0;
+};
+
+// planes [2 M][K] at m->hi times W^T as one GEMM launch with the k pieces as batch items (see linear_w16)
+static int gemm_pieces(Qwen3Model* m, const uint16_t* W, int64_t M, int N, int K, Pieces* out, cudaStream_t st) {
+  int splits = K / 128;
+  const int tiles = (N + 127) / 128;
+  while (splits > 1 && (splits % 2 == 0) && tiles * (splits / 2) >= 2 * sm_count()) splits /= 2;
+  const int kc = K / splits;
+  const size_t part_elems = static_cast<size_t>(2) * splits * M * N;
+  float* part = static_cast<float*>(device_workspace(part_elems * sizeof(float)));
+  if (!part) {
+    set_last_error("linear: cannot allocate %zu bytes for split-k partial sums", part_elems * sizeof(float));
+    return YTC_CUDA_ERROR;
+  }
+  out->part = part;
+  out->n = splits;
+  out->mn = M * N;
+  return ytcuda_gemm(YTC_BF16, YTC_F32, m->hi, W, part, static_cast<int>(2 * M), N, kc, 1.f, 0.f, K, 1, 1, K, N, 1, splits,
+                     kc, kc, 2 * out->mn, st);
+}
+
+static int sum_norm_split(Qwen3Model* m, const Pieces& pc, float* x, const float* w, int64_t rows, int hidden,
+                          cudaStream_t st) {
+  sum_norm_split_kernel<<<static_cast<unsigned>(rows), 256, hidden * sizeof(float), st>>>(
+      pc.part, pc.n, pc.mn, x, w, m->eps, m->hi, m->hi + rows * hidden, hidden);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
 static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_t* W, float* y, int64_t y_rs, int64_t M,
                       int N, int K, bool accumulate, cudaStream_t st) {
   if (M <= 0 || N <= 0) return YTC_OK;
@@ -349,44 +490,28 @@ static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;
   }
-  // many rows: split the activation into two bf16 planes and run the tensor-core GEMM on each
-  const int64_t total4 = M * (K / 4);
-  const int64_t blocks = (total4 + 255) / 256;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-  // the lo plane follows the hi plane: [2 M][K] is then one left operand whose rows M .. 2 M - 1 are the lo plane
+  // many rows: split the activation into two bf16 planes and run the tensor-core GEMM on each. The lo plane follows
+  // the hi plane: [2 M][K] is then one left operand whose rows M .. 2 M - 1 are the lo plane.
+  int s = split_planes(m, x, x_rs, M, K, st);
+  if (s != YTC_OK) return s;
   uint16_t* hi = m->hi;
   uint16_t* lo = m->hi + M * K;
-  split_hi_lo_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, x_rs, hi, lo, M, K);
-  count_launch();
-  YTC_CUDA(cudaGetLastError());
   // Few rows (decode with a larger batch): there are only N / 128 output tiles, too few to keep the SMs busy and the
   // weight stream at bandwidth. The k range is cut into pieces that run as "batch" items of one GEMM launch (a k
   // offset is a plain pointer offset for both K-major operands), each writing its own partial result, and a small
   // kernel adds the partials of both planes in a fixed order.
-  if (M <= 128 && K % 128 == 0 && K >= 256) {
-    int splits = K / 128;
-    const int tiles = (N + 127) / 128;
-    while (splits > 1 && (splits % 2 == 0) && tiles * (splits / 2) >= 2 * sm_count()) splits /= 2;
-    const int kc = K / splits;
-    const size_t part_elems = static_cast<size_t>(2) * splits * M * N;  // [splits][2 M][N]
-    float* part = static_cast<float*>(device_workspace(part_elems * sizeof(float)));
-    if (!part) {
-      set_last_error("linear: cannot allocate %zu bytes for split-k partial sums", part_elems * sizeof(float));
-      return YTC_CUDA_ERROR;
-    }
-    const int64_t mn = M * N;
-    // one launch: both planes as 2 M rows of the left operand, the k pieces as batch items
-    int s = ytcuda_gemm(YTC_BF16, YTC_F32, hi, W, part, static_cast<int>(2 * M), N, kc, 1.f, 0.f, K, 1, 1, K, N, 1,
-                        splits, kc, kc, 2 * mn, st);
-    if (s != YTC_OK) return s;
-    const int64_t blocks = (mn + 255) / 256;
-    sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(part, splits, mn, y, y_rs, N,
-                                                                                             accumulate ? 1 : 0);
+  if (split_k_ok(M, K)) {
+    Pieces pc;
+    if ((s = gemm_pieces(m, W, M, N, K, &pc, st)) != YTC_OK) return s;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    const int64_t blocks = (pc.mn + 255) / 256;
+    sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(pc.part, pc.n, pc.mn, y, y_rs,
+                                                                                             N, accumulate ? 1 : 0);
     count_launch();
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;
   }
-  int s = ytcuda_gemm(YTC_BF16, YTC_F32, hi, W, y, static_cast<int>(M), N, K, 1.f, accumulate ? 1.f : 0.f, K, 1, 1,
+  s = ytcuda_gemm(YTC_BF16, YTC_F32, hi, W, y, static_cast<int>(M), N, K, 1.f, accumulate ? 1.f : 0.f, K, 1, 1,
                       K, y_rs, 1, 1, 0, 0, 0, st);
   if (s != YTC_OK) return s;
   return ytcuda_gemm(YTC_BF16, YTC_F32, lo, W, y, static_cast<int>(M), N, K, 1.f, 1.f, K, 1, 1, K, y_rs, 1, 1, 0, 0,
@@ -459,10 +584,10 @@ int ytcuda_linear_w16(const float* x, int64_t x_row_stride, const void* w_bf16, 
                     accumulate != 0, static_cast<cudaStream_t>(stream));
 }
 
-int ytcuda_qwen3_qkv_post(const float* qkv, float* q_out, float* k_cache, float* v_cache, const float* q_norm,
-                          const float* k_norm, const float* cos_table, const float* sin_table, int batch, int len,
-                          int heads, int kv_heads, int head_dim, int max_len, int pos0, int slot0, float eps,
-                          void* stream) {
+static int qkv_post_launch(const float* qkv, int n_part, int64_t mn, float* q_out, float* k_cache, float* v_cache,
+                           const float* q_norm, const float* k_norm, const float* cos_table, const float* sin_table,
+                           int batch, int len, int heads, int kv_heads, int head_dim, int max_len, int pos0, int slot0,
+                           float eps, void* stream) {
   YTC_REQUIRE(batch >= 0 && len >= 0 && heads >= 0 && kv_heads >= 0, "ytcuda_qwen3_qkv_post: negative extent");
   if (batch == 0 || len == 0) return YTC_OK;
   if (head_dim != 128) {
@@ -478,10 +603,18 @@ int ytcuda_qwen3_qkv_post(const float* qkv, float* q_out, float* k_cache, float*
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   qkv_post_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       qkv, q_out, k_cache, v_cache, q_norm, k_norm, cos_table, sin_table, batch, len, heads, kv_heads, max_len, pos0,
-      slot0, eps);
+      slot0, eps, n_part, mn);
   count_launch();
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
+}
+
+int ytcuda_qwen3_qkv_post(const float* qkv, float* q_out, float* k_cache, float* v_cache, const float* q_norm,
+                          const float* k_norm, const float* cos_table, const float* sin_table, int batch, int len,
+                          int heads, int kv_heads, int head_dim, int max_len, int pos0, int slot0, float eps,
+                          void* stream) {
+  return qkv_post_launch(qkv, 0, 0, q_out, k_cache, v_cache, q_norm, k_norm, cos_table, sin_table, batch, len, heads,
+                         kv_heads, head_dim, max_len, pos0, slot0, eps, stream);
 }
 
 // ---------------------------------------------------------------- model handle
@@ -822,7 +955,50 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   const size_t cache_layer = static_cast<size_t>(B) * m->l_kv_heads * m->max_pos * D;
 
   if ((s = ytcuda_embedding(m->embed, ids, m->x, rows, Hd, m->vocab, st)) != YTC_OK) return s;
-  for (int l = 0; l < m->layers; ++l) {
+  // 9 .. 128 rows on one GPU: every projection runs as k pieces on the tensor cores, and the kernels between two
+  // projections (sum of the pieces, residual, rmsNorm or SwiGLU or the per-head norm + RoPE, the split into bf16
+  // planes) are one launch each: 11 launches per layer instead of 18.
+  const bool fused_glue = m->tp_world == 1 && rows > SK_MAX_ROWS && split_k_ok(rows, Hd) &&
+                          split_k_ok(rows, m->l_heads * D) && split_k_ok(rows, m->l_inter) && Hd <= 8192;
+  if (fused_glue) {
+    Pieces pc;  // the projection whose pieces still have to be added to the residual stream
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    for (int l = 0; l < m->layers; ++l) {
+      const LayerW& W = m->lw[l];
+      float* kc = m->k_cache + l * cache_layer;
+      float* vc = m->v_cache + l * cache_layer;
+      if ((s = sum_norm_split(m, pc, m->x, W.norm1, rows, Hd, st)) != YTC_OK) return s;
+      if ((s = gemm_pieces(m, W.qkv, rows, qkv_w, Hd, &pc, st)) != YTC_OK) return s;
+      if ((s = qkv_post_launch(pc.part, pc.n, pc.mn, m->q, kc, vc, W.q_norm, W.k_norm, m->cos_t, m->sin_t, B, len,
+                               m->l_heads, m->l_kv_heads, D, m->max_pos, pos0, slot0, m->eps, st)) != YTC_OK)
+        return s;
+      const int64_t qs[3] = {static_cast<int64_t>(m->l_heads) * len * D, static_cast<int64_t>(len) * D, D};
+      const int64_t ks[3] = {static_cast<int64_t>(m->l_kv_heads) * m->max_pos * D, static_cast<int64_t>(m->max_pos) * D, D};
+      const int64_t os[3] = {static_cast<int64_t>(len) * m->l_heads * D, D, static_cast<int64_t>(m->l_heads) * D};
+      if ((s = ytcuda_flash_attn_fwd(YTC_F32, m->q, kc, vc, m->attn, B, m->l_kv_heads, groups, len, kv_len, D, D, scale,
+                                     qs, ks, ks, os, wrap_step ? 0 : 1, kv_len - len, nullptr, 0, nullptr, 0, 0, st)) !=
+          YTC_OK)
+        return s;
+      if ((s = split_planes(m, m->attn, m->l_heads * D, rows, m->l_heads * D, st)) != YTC_OK) return s;
+      if ((s = gemm_pieces(m, W.o, rows, Hd, m->l_heads * D, &pc, st)) != YTC_OK) return s;
+      if ((s = sum_norm_split(m, pc, m->x, W.norm2, rows, Hd, st)) != YTC_OK) return s;
+      if ((s = gemm_pieces(m, W.gate_up, rows, 2 * m->l_inter, Hd, &pc, st)) != YTC_OK) return s;
+      {
+        const int64_t blocks = (rows * (m->l_inter / 4) + 255) / 256;
+        sum_swiglu_split_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(
+            pc.part, pc.n, pc.mn, m->hi, m->hi + rows * m->l_inter, rows, m->l_inter);
+        count_launch();
+        YTC_CUDA(cudaGetLastError());
+      }
+      if ((s = gemm_pieces(m, W.down, rows, Hd, m->l_inter, &pc, st)) != YTC_OK) return s;
+    }
+    const int64_t blocks = (pc.mn + 255) / 256;  // the last down projection joins the residual stream
+    sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(pc.part, pc.n, pc.mn, m->x,
+                                                                                             Hd, Hd, 1);
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+  }
+  for (int l = fused_glue ? m->layers : 0; l < m->layers; ++l) {
     const LayerW& W = m->lw[l];
     float* kc = m->k_cache + l * cache_layer;
     float* vc = m->v_cache + l * cache_layer;
