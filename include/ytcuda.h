@@ -263,6 +263,8 @@ int ytcuda_qwen3_cache_len(void* handle);
 /* How a forward of ONE new token per sequence runs: 0 = automatic (one persistent cooperative kernel for the whole
  * step for batch <= 8; under tensor parallelism it needs connected exchange buffers, see ytcuda_qwen3_tp_export),
  * 1 = one launch per operator as for longer inputs, 2 = the persistent kernel (batch <= 32) or YTC_UNSUPPORTED.
+ * 3 = as 2, with the FFMA form of the kernel's linear phases even where the tensor-core form (five or more
+ * sequences, hidden <= 1024) applies.
  * Both forms compute the operator sequence of Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has
  * no counterpart in the reference. */
 int ytcuda_qwen3_set_decode_path(void* handle, int path);

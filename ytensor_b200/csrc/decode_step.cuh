@@ -72,6 +72,7 @@ struct DecodeStepParams {
   unsigned int* sync;  // grid barrier counter
   int chunks, keys_per_chunk;
   int xs_cols;  // activation columns that fit shared memory at once (a multiple of 256, at most 3072)
+  int mma;      // 1: the linear phases run on the tensor cores (ds_linear_mma), 0: FFMA (ds_linear_phase)
   int* status;
   // Tensor parallelism (tp_world > 1): heads, kv_heads, inter and vocab_rows above are this rank's share. The partial
   // sums of the o and down projections are exchanged through "mailboxes" in peer-visible device memory:
@@ -218,8 +219,10 @@ __device__ __forceinline__ float ds_dot8(const uint4& w, const float4& xa, const
 // xs[b][:] = rmsNorm(src[b][:]) * w for b < B (src in global memory, read around L1). One warp per row takes the
 // sum of squares with all its loads in flight at once; meanwhile every thread has requested its piece of w, so the
 // whole staging costs about one trip to the L2.
-__device__ __forceinline__ void ds_stage_rmsnorm(float* xs, const float* src, const float* w, int B, int H, float eps,
-                                                 int warp, int lane) {
+// TWO: a warp takes two rows at a time (worth it with more than 8 sequences, at the cost of 32 more registers).
+template <bool TWO = false>
+__device__ __forceinline__ void ds_stage_rmsnorm(float* xs, int xs_ld, const float* src, const float* w, int B, int H,
+                                                 float eps, int warp, int lane) {
   __shared__ float row_inv[DS_MAX_B];
   const int n4 = H / 4;
   float4 wreg[2];  // this thread's columns of w: float4 index threadIdx.x and threadIdx.x + DS_THREADS (H <= 4096)
@@ -229,29 +232,43 @@ __device__ __forceinline__ void ds_stage_rmsnorm(float* xs, const float* src, co
     wreg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c4 < n4) wreg[i] = __ldg(reinterpret_cast<const float4*>(w) + c4);
   }
-  for (int b = warp; b < B; b += DS_WARPS) {
-    float ss = 0.f;
+  for (int b0 = warp; b0 < B; b0 += (TWO ? 2 : 1) * DS_WARPS) {
+    const int b1 = b0 + DS_WARPS;
+    const bool two = TWO && b1 < B;
+    float ss0 = 0.f, ss1 = 0.f;
     for (int c0 = 0; c0 < H; c0 += 1024) {
-      float4 v[8];
+      float4 v0[8], v1[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int c = c0 + i * 128 + lane * 4;
-        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < H) v[i] = ds_ldcg4(src + static_cast<int64_t>(b) * H + c);
+        v0[i] = v1[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < H) v0[i] = ds_ldcg4(src + static_cast<int64_t>(b0) * H + c);
+        if (two && c < H) v1[i] = ds_ldcg4(src + static_cast<int64_t>(b1) * H + c);
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int c = c0 + i * 128 + lane * 4;
-        if (c < H) *reinterpret_cast<float4*>(&xs[b * H + c]) = v[i];
-        ss = fmaf(v[i].x, v[i].x, ss);
-        ss = fmaf(v[i].y, v[i].y, ss);
-        ss = fmaf(v[i].z, v[i].z, ss);
-        ss = fmaf(v[i].w, v[i].w, ss);
+        if (c < H) *reinterpret_cast<float4*>(&xs[b0 * xs_ld + c]) = v0[i];
+        if (two && c < H) *reinterpret_cast<float4*>(&xs[b1 * xs_ld + c]) = v1[i];
+        ss0 = fmaf(v0[i].x, v0[i].x, ss0);
+        ss0 = fmaf(v0[i].y, v0[i].y, ss0);
+        ss0 = fmaf(v0[i].z, v0[i].z, ss0);
+        ss0 = fmaf(v0[i].w, v0[i].w, ss0);
+        ss1 = fmaf(v1[i].x, v1[i].x, ss1);
+        ss1 = fmaf(v1[i].y, v1[i].y, ss1);
+        ss1 = fmaf(v1[i].z, v1[i].z, ss1);
+        ss1 = fmaf(v1[i].w, v1[i].w, ss1);
       }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (lane == 0) row_inv[b] = 1.0f / sqrtf(ss * (1.0f / static_cast<float>(H)) + eps);
+    for (int o = 16; o > 0; o >>= 1) {
+      ss0 += __shfl_xor_sync(0xffffffffu, ss0, o);
+      ss1 += __shfl_xor_sync(0xffffffffu, ss1, o);
+    }
+    if (lane == 0) {
+      row_inv[b0] = 1.0f / sqrtf(ss0 * (1.0f / static_cast<float>(H)) + eps);
+      if (two) row_inv[b1] = 1.0f / sqrtf(ss1 * (1.0f / static_cast<float>(H)) + eps);
+    }
   }
   __syncthreads();
   for (int b = 0; b < B; ++b) {
@@ -260,35 +277,36 @@ __device__ __forceinline__ void ds_stage_rmsnorm(float* xs, const float* src, co
     for (int i = 0; i < 2; ++i) {
       const int c4 = threadIdx.x + i * DS_THREADS;
       if (c4 < n4) {
-        float4 v = *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]);
+        float4 v = *reinterpret_cast<float4*>(&xs[b * xs_ld + c4 * 4]);
         v.x = v.x * inv * wreg[i].x;
         v.y = v.y * inv * wreg[i].y;
         v.z = v.z * inv * wreg[i].z;
         v.w = v.w * inv * wreg[i].w;
-        *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]) = v;
+        *reinterpret_cast<float4*>(&xs[b * xs_ld + c4 * 4]) = v;
       }
     }
     for (int c4 = threadIdx.x + 2 * DS_THREADS; c4 < n4; c4 += DS_THREADS) {  // hidden sizes above 4096
-      float4 v = *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]);
+      float4 v = *reinterpret_cast<float4*>(&xs[b * xs_ld + c4 * 4]);
       const float4 g = __ldg(reinterpret_cast<const float4*>(w) + c4);
       v.x = v.x * inv * g.x;
       v.y = v.y * inv * g.y;
       v.z = v.z * inv * g.z;
       v.w = v.w * inv * g.w;
-      *reinterpret_cast<float4*>(&xs[b * H + c4 * 4]) = v;
+      *reinterpret_cast<float4*>(&xs[b * xs_ld + c4 * 4]) = v;
     }
   }
   __syncthreads();
 }
 
-// xs[b][0 .. kc) = src[b][c0 .. c0 + kc) for b < B (src rows of K floats)
+// xs[b][0 .. kc) = src[b][c0 .. c0 + kc) for b < B (src rows of K floats); U 128-bit loads per thread in flight
+template <int U = 4>
 __device__ __forceinline__ void ds_stage_copy(float* xs, int xs_ld, const float* src, int B, int K, int c0, int kc) {
   const int per_row = kc / 4;
   const int n4 = B * per_row;
-  for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * DS_THREADS) {
-    float4 v[4];
+  for (int i0 = threadIdx.x; i0 < n4; i0 += U * DS_THREADS) {
+    float4 v[U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int i = i0 + u * DS_THREADS;
       if (i < n4) {
         const int b = i / per_row, c = (i - b * per_row) * 4;
@@ -296,7 +314,7 @@ __device__ __forceinline__ void ds_stage_copy(float* xs, int xs_ld, const float*
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int i = i0 + u * DS_THREADS;
       if (i < n4) {
         const int b = i / per_row, c = (i - b * per_row) * 4;
@@ -311,62 +329,133 @@ __device__ __forceinline__ void ds_stage_copy(float* xs, int xs_ld, const float*
 // left in global memory: o = sum_c e^(m_c - m) o_c / sum_c e^(m_c - m) l_c. Every CTA combines for itself while it
 // stages, so the chunks need no finishing step of their own.
 // Columns c0 .. c0 + kc (whole heads) of the rows go to xs[b][0 .. kc).
-__device__ __forceinline__ void ds_stage_attention(float* xs, int xs_ld, const float* part, int B, int heads,
-                                                   int kv_heads, int chunks, int c0, int kc) {
+// U outputs (128-bit pieces of a head's output row) per thread at a time, CS chunks of each requested together.
+template <int U, int CS>
+__device__ __forceinline__ void ds_stage_attention_t(float* xs, int xs_ld, const float* part, int B, int heads,
+                                                     int kv_heads, int chunks, int c0, int kc) {
   constexpr int D = 128;
   const int G = heads / kv_heads;
   const int per_row = kc / 4;
-  for (int i = threadIdx.x; i < B * per_row; i += DS_THREADS) {
-    const int b = i / per_row, r = i - b * per_row;
-    const int head = c0 / D + r / (D / 4), d4 = r % (D / 4);
-    const int kvh = head / G, g = head - kvh * G;
-    const float* base = part + ((static_cast<int64_t>(b) * kv_heads + kvh) * chunks * G + g) * (4 + D);
-    const int64_t cs = static_cast<int64_t>(G) * (4 + D);  // chunk stride
-    // eight chunks at a time with all their loads in flight; the running combination is an online softmax over chunks
-    float m = -CUDART_INF_F, lsum = 0.f;
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c0 = 0; c0 < chunks; c0 += 8) {
-      float mc[8], lc[8];
-      float4 oc[8];
+  const int total = B * per_row;
+  const int64_t cs = static_cast<int64_t>(G) * (4 + D);  // chunk stride
+  for (int i0 = threadIdx.x; i0 < total; i0 += U * DS_THREADS) {
+    const float* base[U];
+    int d4[U];
+    float m[U], lsum[U];
+    float4 o[U];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        mc[u] = -CUDART_INF_F;
-        lc[u] = 0.f;
-        oc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c0 + u < chunks) {
-          mc[u] = ds_ldcg(base + (c0 + u) * cs);
-          lc[u] = ds_ldcg(base + (c0 + u) * cs + 1);
-          oc[u] = ds_ldcg4(base + (c0 + u) * cs + 4 + d4 * 4);
-        }
-      }
-      float m_new = m;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) m_new = fmaxf(m_new, mc[u]);
-      const float alpha = (m == -CUDART_INF_F) ? 0.f : __expf(m - m_new);
-      lsum *= alpha;
-      o.x *= alpha;
-      o.y *= alpha;
-      o.z *= alpha;
-      o.w *= alpha;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float f = (mc[u] == -CUDART_INF_F) ? 0.f : __expf(mc[u] - m_new);
-        lsum = fmaf(lc[u], f, lsum);
-        o.x = fmaf(oc[u].x, f, o.x);
-        o.y = fmaf(oc[u].y, f, o.y);
-        o.z = fmaf(oc[u].z, f, o.z);
-        o.w = fmaf(oc[u].w, f, o.w);
-      }
-      m = m_new;
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * DS_THREADS;
+      const int ii = i < total ? i : 0;
+      const int b = ii / per_row, r = ii - b * per_row;
+      const int head = c0 / D + r / (D / 4);
+      d4[u] = r % (D / 4);
+      const int kvh = head / G, g = head - kvh * G;
+      base[u] = part + ((static_cast<int64_t>(b) * kv_heads + kvh) * chunks * G + g) * (4 + D);
+      m[u] = -CUDART_INF_F;
+      lsum[u] = 0.f;
+      o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-    o.x *= inv;
-    o.y *= inv;
-    o.z *= inv;
-    o.w *= inv;
-    *reinterpret_cast<float4*>(&xs[b * xs_ld + r * 4]) = o;
+    // the running combination is an online softmax over the chunks
+    for (int cb = 0; cb < chunks; cb += CS) {
+      float mc[U][CS], lc[U][CS];
+      float4 oc[U][CS];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int c = 0; c < CS; ++c) {
+          mc[u][c] = -CUDART_INF_F;
+          lc[u][c] = 0.f;
+          oc[u][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (cb + c < chunks && i0 + u * DS_THREADS < total) {
+            mc[u][c] = ds_ldcg(base[u] + (cb + c) * cs);
+            lc[u][c] = ds_ldcg(base[u] + (cb + c) * cs + 1);
+            oc[u][c] = ds_ldcg4(base[u] + (cb + c) * cs + 4 + d4[u] * 4);
+          }
+        }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float m_new = m[u];
+#pragma unroll
+        for (int c = 0; c < CS; ++c) m_new = fmaxf(m_new, mc[u][c]);
+        const float alpha = (m[u] == -CUDART_INF_F) ? 0.f : __expf(m[u] - m_new);
+        lsum[u] *= alpha;
+        o[u].x *= alpha;
+        o[u].y *= alpha;
+        o[u].z *= alpha;
+        o[u].w *= alpha;
+#pragma unroll
+        for (int c = 0; c < CS; ++c) {
+          const float f = (mc[u][c] == -CUDART_INF_F) ? 0.f : __expf(mc[u][c] - m_new);
+          lsum[u] = fmaf(lc[u][c], f, lsum[u]);
+          o[u].x = fmaf(oc[u][c].x, f, o[u].x);
+          o[u].y = fmaf(oc[u][c].y, f, o[u].y);
+          o[u].z = fmaf(oc[u][c].z, f, o[u].z);
+          o[u].w = fmaf(oc[u][c].w, f, o[u].w);
+        }
+        m[u] = m_new;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * DS_THREADS;
+      if (i >= total) continue;
+      const int b = i / per_row, r = i - b * per_row;
+      const float inv = lsum[u] > 0.f ? 1.0f / lsum[u] : 0.f;
+      float4 v = o[u];
+      v.x *= inv;
+      v.y *= inv;
+      v.z *= inv;
+      v.w *= inv;
+      *reinterpret_cast<float4*>(&xs[b * xs_ld + r * 4]) = v;
+    }
   }
   __syncthreads();
+}
+
+// One chunk per sequence and head (many sequences): the output is o / l of that chunk; U outputs per thread in flight.
+template <int U>
+__device__ __forceinline__ void ds_stage_attention_one(float* xs, int xs_ld, const float* part, int B, int heads, int c0,
+                                                       int kc) {
+  constexpr int D = 128;
+  const int per_row = kc / 4;
+  const int total = B * per_row;
+  for (int i0 = threadIdx.x; i0 < total; i0 += U * DS_THREADS) {
+    float l[U];
+    float4 o[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * DS_THREADS;
+      if (i < total) {
+        const int b = i / per_row, r = i - b * per_row;
+        const float* base = part + (static_cast<int64_t>(b) * heads + c0 / D + r / (D / 4)) * (4 + D);
+        l[u] = ds_ldcg(base + 1);
+        o[u] = ds_ldcg4(base + 4 + (r % (D / 4)) * 4);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * DS_THREADS;
+      if (i < total) {
+        const int b = i / per_row, r = i - b * per_row;
+        const float inv = l[u] > 0.f ? 1.0f / l[u] : 0.f;
+        *reinterpret_cast<float4*>(&xs[b * xs_ld + r * 4]) = make_float4(o[u].x * inv, o[u].y * inv, o[u].z * inv, o[u].w * inv);
+      }
+    }
+  }
+  __syncthreads();
+}
+
+template <bool WIDE = false>
+__device__ __forceinline__ void ds_stage_attention(float* xs, int xs_ld, const float* part, int B, int heads,
+                                                   int kv_heads, int chunks, int c0, int kc) {
+  if constexpr (WIDE) {
+    if (chunks == 1) {
+      ds_stage_attention_one<4>(xs, xs_ld, part, B, heads, c0, kc);
+      return;
+    }
+  }
+  ds_stage_attention_t<1, 8>(xs, xs_ld, part, B, heads, kv_heads, chunks, c0, kc);
 }
 
 __device__ __forceinline__ float ds_swish(float v) {  // x * sigmoid(x), two-branch stable sigmoid
@@ -447,6 +536,16 @@ struct DsLinear {
   int pf_lines;
 };
 
+__device__ __forceinline__ void ds_prefetch_later(const DsLinear& L, int gw, int GW, int lane) {
+  for (int i = 0; i < 2; ++i)
+    if (L.pf_w[i]) ds_prefetch_rows(L.pf_w[i], L.pf_n[i], L.pf_k[i], gw, GW, lane);
+  if (L.pf_k_rows)
+    for (int i = threadIdx.x; i < L.pf_lines; i += DS_THREADS) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_k_rows + i * 128));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_v_rows + i * 128));
+    }
+}
+
 // y[b][n] = sum_k xs[b][k] * W[n][k] for the rows this warp owns (n = gw, gw + GW, ...).
 // Two "slots" of DS_UN 128-bit loads per lane are in flight at once: two rows when the warp owns several, the two
 // halves of a piece of one row when it owns at most one, rows n and N + n of a fused gate / up weight when
@@ -459,15 +558,7 @@ __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B
   const int K = L.K, N = L.N;
   const bool pair = L.epi == 2;
   const bool split_k = !pair && N <= GW;  // at most one row per warp: the slots take the two halves of the row
-  auto prefetch_later_phases = [&]() {
-    for (int i = 0; i < 2; ++i)
-      if (L.pf_w[i]) ds_prefetch_rows(L.pf_w[i], L.pf_n[i], L.pf_k[i], gw, GW, lane);
-    if (L.pf_k_rows)
-      for (int i = threadIdx.x; i < L.pf_lines; i += DS_THREADS) {
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_k_rows + i * 128));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(L.pf_v_rows + i * 128));
-      }
-  };
+  auto prefetch_later_phases = [&]() { ds_prefetch_later(L, gw, GW, lane); };
   if (split_k) {
     // One row per warp at most. The activations are staged in pieces of xs_cols columns (all of them at once when
     // they fit); within a piece slot 0 takes the first half of the columns and slot 1 the second.
@@ -491,7 +582,7 @@ __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B
       }
       if (c0 == 0) prefetch_later_phases();
       else __syncthreads();  // every warp has finished with the previous piece
-      if (L.stage == 0) ds_stage_rmsnorm(xs, L.src, L.norm_w, B, K, eps, warp, lane);  // (K <= xs_cols: one piece)
+      if (L.stage == 0) ds_stage_rmsnorm(xs, K, L.src, L.norm_w, B, K, eps, warp, lane);  // (K <= xs_cols: one piece)
       else if (L.stage == 1) ds_stage_copy(xs, XC, L.src, B, K, c0, kc);
       else ds_stage_attention(xs, XC, L.src, B, L.heads, L.kv_heads, L.chunks, c0, kc);
       if (!have) continue;
@@ -556,7 +647,7 @@ __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B
       }
       if (!staged) {
         prefetch_later_phases();
-        if (L.stage == 0) ds_stage_rmsnorm(xs, L.src, L.norm_w, B, K, eps, warp, lane);
+        if (L.stage == 0) ds_stage_rmsnorm(xs, K, L.src, L.norm_w, B, K, eps, warp, lane);
         else if (L.stage == 1) ds_stage_copy(xs, K, L.src, B, K, 0, K);
         else ds_stage_attention(xs, K, L.src, B, L.heads, L.kv_heads, L.chunks, 0, K);
         staged = true;
@@ -607,6 +698,217 @@ __device__ __noinline__ void ds_linear_phase(const DsLinear& L, float* xs, int B
       }
     }
   }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// The linear phases on the tensor cores (two or more sequences). The FFMA form above spends one FMA per weight and
+// sequence and is bound by that and by shared-memory reads from 2 sequences on; here a warp multiplies 8 x 32 pieces
+// of W with 16 x 32 pieces of the activations by mma.sync (m16n8k16, bf16 operands, fp32 accumulators):
+//   * the activations are the row operand: fp32 in shared memory, split into hi = bf16(x) and lo = bf16(x - hi) in
+//     registers, both multiplied and added into the same accumulator (16 mantissa bits of x take part, as in the
+//     operator path's tensor-core linears);
+//   * 8 weight rows are the column operand, loaded straight from global memory with one 128-bit load per lane: lane
+//     (g, t) holds W[n0 + g][k0 + 8 t .. k0 + 8 t + 7]. The k order inside a block of 32 is permuted the same way for
+//     both operands (a sum over k does not care), so that no lane needs less than 16 contiguous bytes;
+//   * a CTA owns 8 R weight rows (R = 1, 2, 4, chosen per phase so that the units fill the grid), its 8 warps split
+//     the k range, their accumulators are added in warp order through shared memory (a fixed order: results do not
+//     depend on timing), and the epilogue of ds_linear_phase is applied;
+//   * k ranges longer than DS_MMA_XC are staged piece by piece.
+constexpr int DS_MMA_XC = 1024;                       // activation columns staged at once
+constexpr int DS_MMA_LD = DS_MMA_XC + 4;              // their row stride in shared memory (rows 4 banks apart)
+constexpr int DS_MMA_NB = DS_MMA_XC / DS_WARPS / 32;  // blocks of 32 columns per warp and piece
+constexpr int DS_MMA_RTS = 40;                        // row stride of the per-warp accumulator tiles (8 R <= 32, + 8)
+
+// floats of dynamic shared memory the tensor-core phases need for `rows` (16 or 32) activation rows
+constexpr int ds_mma_smem_floats(int rows) { return rows * DS_MMA_LD + DS_WARPS * rows * DS_MMA_RTS; }
+
+__device__ __forceinline__ void ds_mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// (x0, x1) -> packed bf16 pairs hi and lo with x = hi + lo up to 16 mantissa bits; x0 in the low half
+__device__ __forceinline__ void ds_split2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(x0 - __low2float(h), x1 - __high2float(h));
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// R: tiles of 8 weight rows per unit of work (a CTA takes units blockIdx.x, + gridDim.x, ...);
+// MTILES: tiles of 16 activation rows (1: up to 16 sequences, 2: up to 32). Rows of `xs` beyond B hold anything:
+// they only reach accumulator rows that are never stored.
+template <int R, int MTILES>
+__device__ __noinline__ void ds_linear_mma(const DsLinear& L, float* xs, int B, float eps) {
+  constexpr int ROWS = 16 * MTILES;
+  constexpr int NB = DS_MMA_NB;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int gw = blockIdx.x * DS_WARPS + warp, GW = gridDim.x * DS_WARPS;
+  const int K = L.K, N = L.N;
+  const bool pair = L.epi == 2;         // rows n and N + n of a fused gate / up weight: half of the tiles each
+  const int out = pair ? 4 * R : 8 * R;  // output columns of a unit
+  const int units = (N + out - 1) / out;
+  const int pieces = (K + DS_MMA_XC - 1) / DS_MMA_XC;
+  float* red = xs + ROWS * DS_MMA_LD;
+  if (static_cast<int>(blockIdx.x) >= units) {  // nothing to multiply here: only the requests for later phases
+    ds_prefetch_later(L, gw, GW, lane);
+    return;
+  }
+  bool first = true;
+  for (int u = blockIdx.x; u < units; u += gridDim.x) {
+    const uint16_t* wrow[R];  // the row of W this lane loads for tile r
+    bool wok[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      int local = r * 8 + g, base = 0;
+      if constexpr (R >= 2) {
+        if (pair) {
+          local = (r % (R / 2)) * 8 + g;
+          base = r >= R / 2 ? N : 0;
+        }
+      }
+      const int n = u * out + local;
+      wok[r] = n < N;
+      wrow[r] = L.W + static_cast<int64_t>(base + (wok[r] ? n : 0)) * K;
+    }
+    float acc[R][MTILES][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int mt = 0; mt < MTILES; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][mt][i] = 0.f;
+    uint4 wc[R][NB];
+    auto load = [&](uint4(&w)[R][NB], int piece) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          const int k = piece * DS_MMA_XC + (warp * NB + j) * 32 + 8 * t;
+          w[r][j] = make_uint4(0u, 0u, 0u, 0u);
+          if (wok[r] && k < K) w[r][j] = __ldg(reinterpret_cast<const uint4*>(wrow[r] + k));
+        }
+    };
+    load(wc, 0);
+    for (int pc = 0; pc < pieces; ++pc) {
+      const int c0 = pc * DS_MMA_XC;
+      const int kc = K - c0 < DS_MMA_XC ? K - c0 : DS_MMA_XC;
+      if (first || pieces > 1) {
+        if (first) ds_prefetch_later(L, gw, GW, lane);
+        else __syncthreads();  // every warp has finished with what `xs` held
+        if (L.stage == 0) ds_stage_rmsnorm(xs, DS_MMA_LD, L.src, L.norm_w, B, K, eps, warp, lane);  // (K <= DS_MMA_XC)
+        else if (L.stage == 1) ds_stage_copy(xs, DS_MMA_LD, L.src, B, K, c0, kc);
+        else ds_stage_attention<true>(xs, DS_MMA_LD, L.src, B, L.heads, L.kv_heads, L.chunks, c0, kc);
+        first = false;
+      }
+      const bool more = pc + 1 < pieces;
+      uint4 wn[1][NB];  // with one tile per unit the next piece's weights are requested ahead
+      if constexpr (R == 1) {
+        if (more) load(wn, pc + 1);
+      }
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        const int kl = (warp * NB + j) * 32;  // first column of the block within the piece (the same for the warp)
+        if (kl >= kc) continue;
+#pragma unroll
+        for (int mt = 0; mt < MTILES; ++mt) {
+          const float* r0 = xs + (16 * mt + g) * DS_MMA_LD + kl + 8 * t;
+          const float4 x00 = *reinterpret_cast<const float4*>(r0);
+          const float4 x01 = *reinterpret_cast<const float4*>(r0 + 4);
+          const float4 x10 = *reinterpret_cast<const float4*>(r0 + 8 * DS_MMA_LD);
+          const float4 x11 = *reinterpret_cast<const float4*>(r0 + 8 * DS_MMA_LD + 4);
+          uint32_t h[8], l[8];
+          ds_split2(x00.x, x00.y, h[0], l[0]);  // rows g / g + 8, columns 8 t + {0, 1} and + {2, 3}
+          ds_split2(x10.x, x10.y, h[1], l[1]);
+          ds_split2(x00.z, x00.w, h[2], l[2]);
+          ds_split2(x10.z, x10.w, h[3], l[3]);
+          ds_split2(x01.x, x01.y, h[4], l[4]);  // columns 8 t + {4, 5} and + {6, 7}
+          ds_split2(x11.x, x11.y, h[5], l[5]);
+          ds_split2(x01.z, x01.w, h[6], l[6]);
+          ds_split2(x11.z, x11.w, h[7], l[7]);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const uint4 w = wc[r][j];
+            ds_mma_bf16(acc[r][mt], h[0], h[1], h[2], h[3], w.x, w.y);
+            ds_mma_bf16(acc[r][mt], l[0], l[1], l[2], l[3], w.x, w.y);
+            ds_mma_bf16(acc[r][mt], h[4], h[5], h[6], h[7], w.z, w.w);
+            ds_mma_bf16(acc[r][mt], l[4], l[5], l[6], l[7], w.z, w.w);
+          }
+        }
+      }
+      if (more) {
+        if constexpr (R == 1) {
+#pragma unroll
+          for (int j = 0; j < NB; ++j) wc[0][j] = wn[0][j];
+        } else {
+          load(wc, pc + 1);
+        }
+      }
+    }
+    // the warps' accumulators, added in warp order
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int mt = 0; mt < MTILES; ++mt) {
+        float* d = red + (warp * ROWS + 16 * mt + g) * DS_MMA_RTS + 8 * r + 2 * t;
+        *reinterpret_cast<float2*>(d) = make_float2(acc[r][mt][0], acc[r][mt][1]);
+        *reinterpret_cast<float2*>(d + 8 * DS_MMA_RTS) = make_float2(acc[r][mt][2], acc[r][mt][3]);
+      }
+    __syncthreads();
+    for (int e = threadIdx.x; e < B * out; e += DS_THREADS) {
+      const int b = e / out, c = e - b * out;
+      const int n = u * out + c;
+      if (n >= N) continue;
+      float y = 0.f;
+#pragma unroll
+      for (int w = 0; w < DS_WARPS; ++w) y += red[(w * ROWS + b) * DS_MMA_RTS + c];
+      float* d0 = L.dst + static_cast<int64_t>(b) * L.ld + n;
+      if (pair) {
+        float up = 0.f;
+#pragma unroll
+        for (int w = 0; w < DS_WARPS; ++w) up += red[(w * ROWS + b) * DS_MMA_RTS + 4 * R + c];
+        *d0 = ds_swish(y) * up;
+      } else if (L.epi == 1) {
+        *d0 = y + ds_ldcg(d0);  // this thread is the only writer of the element
+      } else {
+        *d0 = y;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Chooses the tiles per unit so that the busiest CTA streams the fewest weight rows (more tiles per unit when that
+// costs at most a few per cent: the activations are then read from shared memory once for more rows).
+template <int MTILES>
+__device__ __forceinline__ void ds_linear_mma_any(const DsLinear& L, float* xs, int B, float eps) {
+  const bool pair = L.epi == 2;
+  int best = 0;
+  float best_cost = 1e30f;
+  for (int R = 4; R >= (pair ? 2 : 1); R >>= 1) {
+    const int out = pair ? 4 * R : 8 * R;
+    const int units = (L.N + out - 1) / out;
+    const int rounds = (units + gridDim.x - 1) / gridDim.x;
+    const float cost = static_cast<float>(rounds * R);
+    if (cost < 0.94f * best_cost) {
+      best = R;
+      best_cost = cost;
+    }
+  }
+  if (best == 4) ds_linear_mma<4, MTILES>(L, xs, B, eps);
+  else if (best == 2) ds_linear_mma<2, MTILES>(L, xs, B, eps);
+  else ds_linear_mma<1, MTILES>(L, xs, B, eps);
+}
+
+// (A kernel holds one form only: with both in one kernel the register allocation of every phase function suffered.)
+template <int MT, bool MMA>
+__device__ __forceinline__ void ds_linear(const DecodeStepParams& p, const DsLinear& L, float* xs, int B) {
+  if constexpr (MMA) ds_linear_mma_any<(MT > 16 ? 2 : 1)>(L, xs, B, p.eps);
+  else ds_linear_phase<MT>(L, xs, B, p.eps);
 }
 
 // The attention phase of one layer (see the file header). G = query heads per kv head.
@@ -796,7 +1098,7 @@ __device__ __noinline__ void ds_attention_phase(const DecodeStepParams& p, const
   }
 }
 
-template <int MT, int G>
+template <int MT, int G, bool MMA>
 __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const DecodeStepParams p) {
   extern __shared__ __align__(16) float xs[];  // [MT][max K]; the attention phase uses it as scratch
   constexpr int D = 128;
@@ -851,7 +1153,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
     // ---- qkv = rmsNorm(x) . Wqkv^T
     L = DsLinear{W.qkv, qkv_w, H, 0, 0, 0, 0, p.xs_cols, p.x, W.norm1, 0, p.qkv, qkv_w, {W.o, nullptr}, {H, 0}, {attn_w, 0},
                  kv_k, kv_v, kv_lines};
-    ds_linear_phase<MT>(L, xs, B, p.eps);
+    ds_linear<MT, MMA>(p, L, xs, B);
     if (!ds_grid_sync(p, epoch)) return;
 
     // ---- attention over the cache (+ per-head rmsNorm, RoPE, KV append); the gate / up rows are requested here
@@ -871,7 +1173,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
       L.epi = 0;
       L.dst = p.mail[p.tp_rank] + static_cast<int64_t>((p.ar_base + ar) & 1) * DS_MAX_B * H;
     }
-    ds_linear_phase<MT>(L, xs, B, p.eps);
+    ds_linear<MT, MMA>(p, L, xs, B);
     if (p.tp_world > 1) {
       if (!ds_cross_sync(p, epoch, p.ar_base + ar + 1)) return;
       ds_reduce_mailboxes(p, (p.ar_base + ar) & 1);
@@ -889,7 +1191,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
       L = DsLinear{W.gate_up, p.inter, H, 0, 0, 0, 0, p.xs_cols, p.x, W.norm2, 2, p.act, p.inter,
                    {last ? p.lm_head : p.lw[l + 1].qkv, nullptr}, {nxt.x, 0}, {nxt.y, 0}, nullptr, nullptr, 0};
     }
-    ds_linear_phase<MT>(L, xs, B, p.eps);
+    ds_linear<MT, MMA>(p, L, xs, B);
     if (!ds_grid_sync(p, epoch)) return;
 
     // ---- x += act . Wdown^T
@@ -899,7 +1201,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
       L.epi = 0;
       L.dst = p.mail[p.tp_rank] + static_cast<int64_t>((p.ar_base + ar) & 1) * DS_MAX_B * H;
     }
-    ds_linear_phase<MT>(L, xs, B, p.eps);
+    ds_linear<MT, MMA>(p, L, xs, B);
     if (p.tp_world > 1) {
       if (!ds_cross_sync(p, epoch, p.ar_base + ar + 1)) return;
       ds_reduce_mailboxes(p, (p.ar_base + ar) & 1);
@@ -911,7 +1213,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const Decode
   // ---- logits = rmsNorm(x) . Wvocab^T
   DsLinear L{p.lm_head, p.vocab_rows, H, 0, 0, 0, 0, p.xs_cols, p.x, p.final_norm, 0, p.logits, p.vocab_rows, {nullptr, nullptr},
              {0, 0}, {0, 0}, nullptr, nullptr, 0};
-  ds_linear_phase<MT>(L, xs, B, p.eps);
+  ds_linear<MT, MMA>(p, L, xs, B);
 }
 
 }  // namespace ytk

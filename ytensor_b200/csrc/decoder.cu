@@ -17,7 +17,9 @@
 
 #include <cmath>
 #include <cstring>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "decode_step.cuh"
@@ -58,6 +60,11 @@ constexpr int SK_KC = 1024;
 constexpr int SK_UNROLL = 4;  // 256-column trips fetched together per lane
 // Rows up to which the FFMA kernel is used; above, the activations are split into two bf16 planes and the tensor
 // cores do the product (the FFMA kernel's time grows with the rows, the tensor-core GEMM's hardly does).
+// Sequences from which the step kernel's linear phases run on the tensor cores. Measured per step on the 0.6B shape
+// (FFMA form / tensor-core form): 2 sequences 1.30 / 1.71 ms, 4: 1.83 / 2.08, 8: 3.01 / 2.69, 16: 6.6 / 3.5, 32: 13.4 / 6.1.
+#ifndef DS_MMA_MIN_B
+#define DS_MMA_MIN_B 5
+#endif
 #ifndef SK_MAX_ROWS
 #define SK_MAX_ROWS 8
 #endif
@@ -384,7 +391,6 @@ struct Qwen3Model {
   bool ds_lw_stale = true;
   float* ds_part = nullptr;         // attention partials
   unsigned int* ds_sync = nullptr;  // barrier counter + per (sequence, kv head) chunk counters
-  int ds_smem_set = 0;
   // exchange buffers of the tensor-parallel step kernel: this rank's (mailbox, flag words, release word) and the
   // peers' buffers opened through CUDA IPC
   char* tp_comm = nullptr;
@@ -752,11 +758,11 @@ int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64) {
 }
 
 // 0: automatic (the persistent step kernel where it applies), 1: always one launch per operator, 2: the persistent
-// step kernel or YTC_UNSUPPORTED.
+// step kernel or YTC_UNSUPPORTED, 3: as 2 with the FFMA form of its linear phases at every batch size.
 int ytcuda_qwen3_set_decode_path(void* handle, int path) {
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m, "ytcuda_qwen3_set_decode_path: null handle");
-  YTC_REQUIRE(path >= 0 && path <= 2, "ytcuda_qwen3_set_decode_path: path must be 0, 1 or 2");
+  YTC_REQUIRE(path >= 0 && path <= 3, "ytcuda_qwen3_set_decode_path: path must be 0, 1, 2 or 3");
   m->decode_path = path;
   return YTC_OK;
 }
@@ -800,6 +806,13 @@ static int ds_xs_cols(int mt) {
   return cols > 3072 ? 3072 : cols;
 }
 
+// Whether the step kernel's linear phases run on the tensor cores: enough sequences for that to pay, activation rows
+// that fit the staging area in one piece, whole blocks of 32 columns. decode_path 3 keeps the FFMA form.
+static bool decode_step_mma(const Qwen3Model* m) {
+  return m->decode_path != 3 && m->batch >= DS_MMA_MIN_B && m->hidden <= DS_MMA_XC && m->hidden % 32 == 0 &&
+         (m->l_heads * 128) % 32 == 0 && m->l_inter % 32 == 0;
+}
+
 static bool decode_step_supported(const Qwen3Model* m) {
   const int groups = m->heads / m->kv_heads;
   const int xs_cols = ds_xs_cols(ds_rows(m->batch));
@@ -841,7 +854,13 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   int smem = mt * (kmax < xs_cols ? kmax : xs_cols) * static_cast<int>(sizeof(float));
   const int att = DS_ATT_FLOATS * static_cast<int>(sizeof(float));  // the attention phase's scratch
   if (smem < att) smem = att;
+  const bool mma = decode_step_mma(m);
+  if (mma) {
+    const int need = ds_mma_smem_floats(mt > 16 ? 32 : 16) * static_cast<int>(sizeof(float));
+    if (smem < need) smem = need;
+  }
   DecodeStepParams p{};
+  p.mma = mma ? 1 : 0;
   p.B = B; p.hidden = m->hidden; p.layers = m->layers; p.heads = m->l_heads; p.kv_heads = m->l_kv_heads;
   p.inter = m->l_inter; p.vocab_rows = m->l_vocab; p.vocab = m->vocab; p.max_pos = m->max_pos;
   const bool wrapped = m->total_written >= m->max_pos;  // (the caller has checked that the cache is then full)
@@ -879,20 +898,34 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   YTC_CUDA(cudaMemsetAsync(m->ds_sync, 0, sync_words * sizeof(unsigned int), st));
   void* args[] = {&p};
   const void* fn = nullptr;
-#define DS_PICK(MT)                                                                       \
-  fn = groups == 1   ? reinterpret_cast<const void*>(decode_step_kernel<MT, 1>)           \
-       : groups == 2 ? reinterpret_cast<const void*>(decode_step_kernel<MT, 2>)           \
-                     : reinterpret_cast<const void*>(decode_step_kernel<MT, 4>)
-  if (mt == 1) DS_PICK(1);
+#define DS_PICK_G(MT, MMA)                                                                    \
+  fn = groups == 1   ? reinterpret_cast<const void*>(decode_step_kernel<MT, 1, MMA>)          \
+       : groups == 2 ? reinterpret_cast<const void*>(decode_step_kernel<MT, 2, MMA>)          \
+                     : reinterpret_cast<const void*>(decode_step_kernel<MT, 4, MMA>)
+#define DS_PICK(MT)              \
+  do {                           \
+    if (mma) DS_PICK_G(MT, true); \
+    else DS_PICK_G(MT, false);   \
+  } while (0)
+  if (mt == 1) DS_PICK_G(1, false);
   else if (mt == 2) DS_PICK(2);
   else if (mt == 4) DS_PICK(4);
   else if (mt == 8) DS_PICK(8);
   else if (mt == 16) DS_PICK(16);
   else DS_PICK(32);
+#undef DS_PICK_G
 #undef DS_PICK
-  if (m->ds_smem_set < smem) {
-    YTC_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    m->ds_smem_set = smem;
+  {
+    // the limit belongs to the kernel, not to the model: several models (other paths, other sizes) share a kernel,
+    // and a smaller request must not lower what another model's launches need
+    static std::mutex mu;
+    static std::unordered_map<const void*, int> limit;
+    std::lock_guard<std::mutex> lock(mu);
+    int& cur = limit[fn];
+    if (cur < smem) {
+      YTC_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      cur = smem;
+    }
   }
   YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(DS_THREADS), args, smem, st));
   count_launch();
@@ -922,7 +955,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     YTC_REQUIRE(L.qkv && L.o && L.gate_up && L.down && L.q_norm && L.k_norm && L.norm1 && L.norm2,
                 "ytcuda_qwen3_forward: a layer weight is not set");
   YTC_REQUIRE(m->tp_world == 1 || m->allreduce ||
-                  (len == 1 && m->tp_ready && (m->decode_path == 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B))),
+                  (len == 1 && m->tp_ready && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B))),
               "ytcuda_qwen3_forward: tensor parallel needs an all-reduce callback");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int B = m->batch, D = m->head_dim, Hd = m->hidden;
@@ -939,12 +972,12 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   };
   // Automatic choice: the step kernel up to DS_AUTO_B sequences. Beyond that its FFMA linears lose against the
   // tensor-core linears of the operator path (measured at 16 and 32 sequences), so it runs only when asked for.
-  if (len == 1 && (m->decode_path == 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B)) && decode_step_supported(m)) {
+  if (len == 1 && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B)) && decode_step_supported(m)) {
     if ((s = decode_step_launch(m, ids, logits, st)) != YTC_OK) return s;
     advance();
     return YTC_OK;
   }
-  if (len == 1 && m->decode_path == 2) {
+  if (len == 1 && m->decode_path >= 2) {
     set_last_error("ytcuda_qwen3_forward: the single-kernel decode step needs batch <= %d, 1, 2 or %d query heads "
                    "per kv head and, under tensor parallelism, connected exchange buffers", DS_MAX_B, DS_MAX_G);
     return YTC_UNSUPPORTED;

@@ -191,7 +191,8 @@ class Qwen3ForCausalLM:
         check(self.L.ytcuda_qwen3_reset(self.h))
 
     def set_decode_path(self, path: int) -> None:
-        """0: automatic, 1: one launch per operator, 2: the single persistent kernel per decode step (or an error)."""
+        """0: automatic, 1: one launch per operator, 2: the single persistent kernel per decode step (or an error),
+        3: as 2 with FFMA linear phases at every batch size."""
         check(self.L.ytcuda_qwen3_set_decode_path(self.h, int(path)))
 
     def get_kv_cache_len(self) -> int:
