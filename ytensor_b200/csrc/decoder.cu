@@ -223,7 +223,7 @@ __device__ __forceinline__ void split_store4(const float f[4], uint16_t* hi, uin
 // sum over the k pieces p of both planes, in index order (the order of sum_partials_kernel), of 4 adjacent elements
 __device__ __forceinline__ float4 sum_pieces4(const float* part, int n_part, int64_t mn, int64_t off) {
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
+#pragma unroll 8
   for (int p = 0; p < n_part; ++p) {
     const float4 a = *reinterpret_cast<const float4*>(part + 2 * p * mn + off);
     const float4 b = *reinterpret_cast<const float4*>(part + (2 * p + 1) * mn + off);
@@ -237,21 +237,42 @@ __device__ __forceinline__ float4 sum_pieces4(const float* part, int n_part, int
 //   y = rmsNorm(x[r]) * w   (reference src/function/normalization.inl:234-277),
 //   y -> hi + lo bf16 planes, the left operand of the projection that follows.
 // Three launches (sum_partials, the row kernel, split_hi_lo) as one.
-__global__ void __launch_bounds__(256) sum_norm_split_kernel(const float* part, int n_part, int64_t mn, float* x,
-                                                             const float* w, float eps, uint16_t* hi, uint16_t* lo,
-                                                             int hidden) {
-  extern __shared__ float row_s[];
-  __shared__ float red[8];
+__global__ void __launch_bounds__(1024) sum_norm_split_kernel(const float* part, int n_part, int64_t mn, float* x,
+                                                              const float* w, float eps, uint16_t* hi, uint16_t* lo,
+                                                              int hidden) {
+  extern __shared__ float row_s[];  // [4][hidden]: the sums of the four thread groups, then (in [0]) the row
+  __shared__ float red[32];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
+  if (n_part > 0) {
+    // group q of 256 threads adds the pieces q, q + 4, ... (both planes) with all its loads in flight at once
+    const int q = threadIdx.x >> 8, t = threadIdx.x & 255;
+    for (int c = t * 4; c < hidden; c += 1024) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 6
+      for (int p = q; p < n_part; p += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(part + 2 * p * mn + base + c);
+        const float4 b = *reinterpret_cast<const float4*>(part + (2 * p + 1) * mn + base + c);
+        s.x += a.x + b.x; s.y += a.y + b.y; s.z += a.z + b.z; s.w += a.w + b.w;
+      }
+      *reinterpret_cast<float4*>(row_s + q * hidden + c) = s;
+    }
+    __syncthreads();
+  }
   float ss = 0.f;
-  for (int c = threadIdx.x * 4; c < hidden; c += 1024) {
+  for (int c = threadIdx.x * 4; c < hidden; c += 4096) {
     float4 v = *reinterpret_cast<const float4*>(x + base + c);
     if (n_part > 0) {
-      const float4 s = sum_pieces4(part, n_part, mn, base + c);
-      v.x += s.x; v.y += s.y; v.z += s.z; v.w += s.w;
+      const float4 s0 = *reinterpret_cast<const float4*>(row_s + c);
+      const float4 s1 = *reinterpret_cast<const float4*>(row_s + hidden + c);
+      const float4 s2 = *reinterpret_cast<const float4*>(row_s + 2 * hidden + c);
+      const float4 s3 = *reinterpret_cast<const float4*>(row_s + 3 * hidden + c);
+      v.x += (s0.x + s1.x) + (s2.x + s3.x);  // a fixed order: the result does not depend on timing
+      v.y += (s0.y + s1.y) + (s2.y + s3.y);
+      v.z += (s0.z + s1.z) + (s2.z + s3.z);
+      v.w += (s0.w + s1.w) + (s2.w + s3.w);
       *reinterpret_cast<float4*>(x + base + c) = v;
     }
-    *reinterpret_cast<float4*>(row_s + c) = v;
+    *reinterpret_cast<float4*>(row_s + c) = v;  // (read back by this thread only)
     ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
   }
 #pragma unroll
@@ -260,9 +281,9 @@ __global__ void __launch_bounds__(256) sum_norm_split_kernel(const float* part, 
   __syncthreads();
   float tot = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) tot += red[i];
+  for (int i = 0; i < 32; ++i) tot += red[i];
   const float inv = 1.0f / sqrtf(tot * (1.0f / hidden) + eps);
-  for (int c = threadIdx.x * 4; c < hidden; c += 1024) {
+  for (int c = threadIdx.x * 4; c < hidden; c += 4096) {
     const float4 v = *reinterpret_cast<const float4*>(row_s + c);
     const float4 g = *reinterpret_cast<const float4*>(w + c);
     const float f[4] = {v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w};
@@ -310,6 +331,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* 
     if (n_part > 0) {  // `qkv` holds the k-split partial products [pieces][2][B * L][heads_all * D]: add them here
 #pragma unroll
       for (int i = 0; i < 4; ++i) x[i] = 0.f;
+#pragma unroll 8
       for (int p = 0; p < n_part; ++p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) x[i] += src[2 * p * mn + lane + 32 * i] + src[(2 * p + 1) * mn + lane + 32 * i];
@@ -454,7 +476,7 @@ static int gemm_pieces(Qwen3Model* m, const uint16_t* W, int64_t M, int N, int K
 
 static int sum_norm_split(Qwen3Model* m, const Pieces& pc, float* x, const float* w, int64_t rows, int hidden,
                           cudaStream_t st) {
-  sum_norm_split_kernel<<<static_cast<unsigned>(rows), 256, hidden * sizeof(float), st>>>(
+  sum_norm_split_kernel<<<static_cast<unsigned>(rows), 1024, 4 * hidden * sizeof(float), st>>>(
       pc.part, pc.n, pc.mn, x, w, m->eps, m->hi, m->hi + rows * hidden, hidden);
   count_launch();
   YTC_CUDA(cudaGetLastError());
@@ -992,7 +1014,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   // projections (sum of the pieces, residual, rmsNorm or SwiGLU or the per-head norm + RoPE, the split into bf16
   // planes) are one launch each: 11 launches per layer instead of 18.
   const bool fused_glue = m->tp_world == 1 && rows > SK_MAX_ROWS && split_k_ok(rows, Hd) &&
-                          split_k_ok(rows, m->l_heads * D) && split_k_ok(rows, m->l_inter) && Hd <= 8192;
+                          split_k_ok(rows, m->l_heads * D) && split_k_ok(rows, m->l_inter) && Hd <= 3072;
   if (fused_glue) {
     Pieces pc;  // the projection whose pieces still have to be added to the residual stream
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
@@ -1017,8 +1039,8 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
       if ((s = sum_norm_split(m, pc, m->x, W.norm2, rows, Hd, st)) != YTC_OK) return s;
       if ((s = gemm_pieces(m, W.gate_up, rows, 2 * m->l_inter, Hd, &pc, st)) != YTC_OK) return s;
       {
-        const int64_t blocks = (rows * (m->l_inter / 4) + 255) / 256;
-        sum_swiglu_split_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(
+        const int64_t blocks = (rows * (m->l_inter / 4) + 127) / 128;
+        sum_swiglu_split_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 128, 0, st>>>(
             pc.part, pc.n, pc.mn, m->hi, m->hi + rows * m->l_inter, rows, m->l_inter);
         count_launch();
         YTC_CUDA(cudaGetLastError());
