@@ -526,7 +526,9 @@ def decode_arm(args) -> None:
             "prefill_tokens_per_s": B * prompt_len / (prefill_ms * 1e-3), "prefill_ms": prefill_ms,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "kernel": "decode_step_kernel" if B <= 8 else "gemm_tc_kernel<128> (hi + lo planes, split-k pieces)",
+                         "kernel": ("decode_step_kernel (FFMA linear phases)" if B <= 4 else
+                                    "decode_step_kernel (mma.sync linear phases)" if B <= 8 else
+                                    "gemm_tc_kernel (hi + lo planes, split-k pieces) + fused glue kernels"),
                          "peak_source": f"{peaks['source']} (copy bandwidth)",
                          "algorithmic_bytes_per_launch": bytes_per_step,
                          "note": "bytes of this rank's bf16 weights streamed once per decode step / step time"},
