@@ -53,6 +53,32 @@ def _worker(rank, world, port, ret):
                     assert (launched == 1) if path == 2 else (launched > 10), (path, launched)
             assert Q._lib.lib().ytcuda_device_status(None) == 0
             m.close()
+        # six sequences: the step kernel's linear phases run on the tensor cores (mma.sync form), the sums over ranks
+        # still inside the kernel; against the operator path with the NCCL callback, both fed the same tokens
+        cfg = Q.Qwen3Config(hidden_size=256, num_hidden_layers=3, vocab_size=1000, intermediate_size=2816,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=128)
+        w = Q.random_weights(cfg, seed=11, std=0.05)
+        ids = torch.from_numpy(np.random.default_rng(6).integers(0, cfg.vocab_size, (6, 20)).astype(np.int32)).cuda()
+        ms = []
+        for path in (1, 2):
+            m = Q.Qwen3ForCausalLM(cfg, batch=6, tp_rank=rank, tp_world=world)
+            m.load_weights(w)
+            m.set_decode_path(path)
+            ms.append(m)
+        la, lb = ms[0].forward(ids), ms[1].forward(ids)
+        assert torch.equal(la, lb)
+        for step in range(12):
+            tok, _ = ms[0].argmax(la)
+            tok = tok.reshape(6, 1).contiguous()
+            la = ms[0].forward(tok)
+            n0 = Q._lib.lib().ytcuda_launch_count()
+            lb = ms[1].forward(tok)
+            assert Q._lib.lib().ytcuda_launch_count() - n0 == 1
+            a, b = la.cpu().numpy(), lb.cpu().numpy()
+            assert np.linalg.norm(b - a) / np.linalg.norm(a) < 2e-5, (step, np.linalg.norm(b - a) / np.linalg.norm(a))
+        assert Q._lib.lib().ytcuda_device_status(None) == 0
+        for m in ms:
+            m.close()
         # Qwen3-0.6B shape: the first 16 greedy tokens of the reference
         cfg = Q.Qwen3Config(max_position_embeddings=768)
         m = Q.Qwen3ForCausalLM(cfg, batch=1, tp_rank=rank, tp_world=world)
