@@ -457,9 +457,14 @@ struct Pieces {  // k-split partial products [n][2][M][N] of one projection
 
 // planes [2 M][K] at m->hi times W^T as one GEMM launch with the k pieces as batch items (see linear_w16)
 static int gemm_pieces(Qwen3Model* m, const uint16_t* W, int64_t M, int N, int K, Pieces* out, cudaStream_t st) {
-  int splits = K / 128;
-  const int tiles = (N + 127) / 128;
-  while (splits > 1 && (splits % 2 == 0) && tiles * (splits / 2) >= 2 * sm_count()) splits /= 2;
+  // As many k pieces as keep the work items (128 x 128 output tiles x pieces) within one wave of the SMs: more
+  // pieces than that only add partial sums to write and read back (measured at 32 rows: 4 pieces for the qkv
+  // projection of the 0.6B shape, 2 for gate / up, 16 or 12 for the o and down projections).
+  const int blocks = K / 128;
+  const int tiles = ((N + 127) / 128) * static_cast<int>((2 * M + 127) / 128);
+  int splits = 1;
+  for (int d = 1; d <= blocks; ++d)
+    if (blocks % d == 0 && tiles * d <= sm_count()) splits = d;
   const int kc = K / splits;
   const size_t part_elems = static_cast<size_t>(2) * splits * M * N;
   float* part = static_cast<float*>(device_workspace(part_elems * sizeof(float)));
