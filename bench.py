@@ -527,7 +527,7 @@ def decode_arm(args) -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": None,
                          "kernel": ("decode_step_kernel (FFMA linear phases)" if B <= 4 else
-                                    "decode_step_kernel (mma.sync linear phases)" if B <= 8 else
+                                    "decode_step_kernel (mma.sync linear phases)" if B <= (6 if world == 1 else 8) else
                                     "gemm_tc_kernel (hi + lo planes, split-k pieces) + fused glue kernels"),
                          "peak_source": f"{peaks['source']} (copy bandwidth)",
                          "algorithmic_bytes_per_launch": bytes_per_step,

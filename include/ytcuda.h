@@ -220,7 +220,7 @@ int ytcuda_embedding(const void* table_bf16, const int32_t* ids, float* out, int
                      void* stream);
 
 /* y[m, n] (+)= x[m, k] . W[n, k]^T with fp32 x, y and bf16 W [n, k] row-major: yt::function::linear
- * (src/function/ops.inl:84-91) with the weight left in its storage type. Up to 8 rows: one pass over W with FFMA
+ * (src/function/ops.inl:84-91) with the weight left in its storage type. Up to 4 rows: one pass over W with FFMA
  * (decode). More rows: x is split into two bf16 planes (hi + lo) and multiplied on tcgen05 (up to 128 rows with the
  * k range cut into pieces that run side by side, partial sums added in a fixed order); `hi_lo_scratch` must then
  * hold 4*m*k bytes of device memory. */
@@ -261,7 +261,8 @@ int ytcuda_qwen3_set_allreduce(void* handle, int (*fn)(void* buf, int64_t count,
 int ytcuda_qwen3_reset(void* handle);
 int ytcuda_qwen3_cache_len(void* handle);
 /* How a forward of ONE new token per sequence runs: 0 = automatic (one persistent cooperative kernel for the whole
- * step for batch <= 8; under tensor parallelism it needs connected exchange buffers, see ytcuda_qwen3_tp_export),
+ * step for batch <= 6, or <= 8 under tensor parallelism, where it needs connected exchange buffers, see
+ * ytcuda_qwen3_tp_export),
  * 1 = one launch per operator as for longer inputs, 2 = the persistent kernel (batch <= 32) or YTC_UNSUPPORTED.
  * 3 = as 2, with the FFMA form of the kernel's linear phases even where the tensor-core form (five or more
  * sequences, hidden <= 1024) applies.

@@ -66,7 +66,7 @@ constexpr int SK_UNROLL = 4;  // 256-column trips fetched together per lane
 #define DS_MMA_MIN_B 5
 #endif
 #ifndef SK_MAX_ROWS
-#define SK_MAX_ROWS 8
+#define SK_MAX_ROWS 4
 #endif
 
 template <int MT>
@@ -232,7 +232,7 @@ __device__ __forceinline__ float4 sum_pieces4(const float* part, int n_part, int
   return s;
 }
 
-// The glue between two projections of a decode step with 9 .. 128 rows, one CTA per row of the residual stream:
+// The glue between two projections of a decode step with 5 .. 128 rows, one CTA per row of the residual stream:
 //   x[r] += sum of the k-split partial products of the projection before (when there are any),
 //   y = rmsNorm(x[r]) * w   (reference src/function/normalization.inl:234-277),
 //   y -> hi + lo bf16 planes, the left operand of the projection that follows.
@@ -436,7 +436,7 @@ static int dev_alloc(Qwen3Model* m, void** p, size_t bytes) {
 }
 
 // y[M, N] (+)= x[M, K] . W[N, K]^T with fp32 x / y and bf16 W.
-// ---- the projections of a step with 9 .. 128 rows, taken apart so that the glue between them can be fused ----
+// ---- the projections of a step with 5 .. 128 rows, taken apart so that the glue between them can be fused ----
 static bool split_k_ok(int64_t M, int K) { return M <= 128 && K % 128 == 0 && K >= 256; }
 
 static int split_planes(Qwen3Model* m, const float* x, int64_t x_rs, int64_t M, int K, cudaStream_t st) {
@@ -822,7 +822,12 @@ static int ensure_activations(Qwen3Model* m, int64_t rows) {
 }
 
 constexpr int DS_MAX_CHUNKS = 64;
-constexpr int DS_AUTO_B = 8;
+// Sequences up to which the step kernel is the automatic choice. On one GPU the operator path with tensor-core
+// linears wins from 7 on (per step at 6 / 8 sequences: 2.37 / 2.70 ms against 2.51 / 2.54); under tensor parallelism
+// the step kernel keeps the sums over ranks inside the kernel, which the operator path pays a collective call for.
+constexpr int DS_AUTO_B = 6;
+constexpr int DS_AUTO_B_TP = 8;
+static int ds_auto_b(const Qwen3Model* m) { return m->tp_world > 1 ? DS_AUTO_B_TP : DS_AUTO_B; }
 
 
 // Whether the persistent step kernel covers this model (one new token per sequence is checked by the caller).
@@ -982,7 +987,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     YTC_REQUIRE(L.qkv && L.o && L.gate_up && L.down && L.q_norm && L.k_norm && L.norm1 && L.norm2,
                 "ytcuda_qwen3_forward: a layer weight is not set");
   YTC_REQUIRE(m->tp_world == 1 || m->allreduce ||
-                  (len == 1 && m->tp_ready && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B))),
+                  (len == 1 && m->tp_ready && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= ds_auto_b(m)))),
               "ytcuda_qwen3_forward: tensor parallel needs an all-reduce callback");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int B = m->batch, D = m->head_dim, Hd = m->hidden;
@@ -997,9 +1002,9 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     m->total_written += len;
     m->cur_len = m->total_written < m->max_pos ? static_cast<int>(m->total_written) : m->max_pos;
   };
-  // Automatic choice: the step kernel up to DS_AUTO_B sequences. Beyond that its FFMA linears lose against the
+  // Automatic choice: the step kernel up to ds_auto_b() sequences. Beyond that its linear phases lose against the
   // tensor-core linears of the operator path (measured at 16 and 32 sequences), so it runs only when asked for.
-  if (len == 1 && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= DS_AUTO_B)) && decode_step_supported(m)) {
+  if (len == 1 && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= ds_auto_b(m))) && decode_step_supported(m)) {
     if ((s = decode_step_launch(m, ids, logits, st)) != YTC_OK) return s;
     advance();
     return YTC_OK;
@@ -1015,7 +1020,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   const size_t cache_layer = static_cast<size_t>(B) * m->l_kv_heads * m->max_pos * D;
 
   if ((s = ytcuda_embedding(m->embed, ids, m->x, rows, Hd, m->vocab, st)) != YTC_OK) return s;
-  // 9 .. 128 rows on one GPU: every projection runs as k pieces on the tensor cores, and the kernels between two
+  // 5 .. 128 rows on one GPU: every projection runs as k pieces on the tensor cores, and the kernels between two
   // projections (sum of the pieces, residual, rmsNorm or SwiGLU or the per-head norm + RoPE, the split into bf16
   // planes) are one launch each: 11 launches per layer instead of 18.
   const bool fused_glue = m->tp_world == 1 && rows > SK_MAX_ROWS && split_k_ok(rows, Hd) &&
