@@ -167,6 +167,7 @@ int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const v
 /* y = f(x): op 0 copy, 1 swish (x * stable sigmoid(x)), 2 x * param, 3 x + param, and the forward forms of the other
  * activations of yt::function (src/function/activation.inl): 4 relu, 5 exp, 6 sigmoid, 7 leakyRelu (param = alpha),
  * 8 elu (param = alpha), 9 selu, 10 gelu (erf form), 11 tanh, 12 softplus, 13 mish, 14 hardSigmoid, 15 hardSwish.
+ * op + 32 for an activation (33, 36 .. 47) is its first derivative, the `order = 1` form of the same functions.
  * Replaces yt::function::swish_ (:631-647) and its siblings, and scalar broadcastInplace calls. */
 int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
                  const int64_t* xstrides, const int64_t* ystrides, float param, void* stream);

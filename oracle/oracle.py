@@ -170,13 +170,19 @@ class _Backend:
     ACTIVATIONS = {"swish": 1, "relu": 4, "exp": 5, "sigmoid": 6, "leakyRelu": 7, "elu": 8, "selu": 9, "gelu": 10,
                    "tanh": 11, "softplus": 12, "mish": 13, "hardSigmoid": 14, "hardSwish": 15}
 
-    def activation(self, name, x, alpha=None):
-        """yt::function::<name> (reference include/function/activation.hpp:9-109), forward form."""
+    def activation(self, name, x, alpha=None, order=0):
+        """yt::function::<name> (reference include/function/activation.hpp:9-109): order 0 the function, order 1 its
+        first derivative."""
         x = _f32(x)
         y = np.empty_like(x)
         if alpha is None:
             alpha = {"leakyRelu": 0.01, "elu": 1.0}.get(name, 0.0)
-        rc = self._fn("activation_f32")(self.ACTIVATIONS[name], _opt(x), _opt(y), C.c_int64(x.size), C.c_float(alpha))
+        if order == 0:
+            rc = self._fn("activation_f32")(self.ACTIVATIONS[name], _opt(x), _opt(y), C.c_int64(x.size),
+                                            C.c_float(alpha))
+        else:
+            rc = self._fn("activation_order_f32")(self.ACTIVATIONS[name], int(order), _opt(x), _opt(y),
+                                                  C.c_int64(x.size), C.c_float(alpha))
         assert rc == 0, rc
         return y
 

@@ -404,6 +404,35 @@ int ytref_activation_f32(int op, const float* x, float* y, int64_t n, float alph
   }
 }
 
+// The same activations with their `order` argument (1: first derivative), include/function/activation.hpp:9-109.
+int ytref_activation_order_f32(int op, int order, const float* x, float* y, int64_t n, float alpha) {
+  try {
+    const int s[2] = {1, static_cast<int>(n)};
+    auto t = make<2>(x, s);
+    namespace F = yt::function;
+    switch (op) {
+      case 1: F::swish_(t, order); break;
+      case 4: F::relu_(t, order); break;
+      case 5: F::exp_(t, order); break;
+      case 6: F::sigmoid_(t, order); break;
+      case 7: F::leakyRelu_(t, alpha, order); break;
+      case 8: F::elu_(t, alpha, order); break;
+      case 9: F::selu_(t, order); break;
+      case 10: F::gelu_(t, order); break;
+      case 11: F::tanh_(t, order); break;
+      case 12: F::softplus_(t, order); break;
+      case 13: F::mish_(t, order); break;
+      case 14: F::hardSigmoid_(t, order); break;
+      case 15: F::hardSwish_(t, order); break;
+      default: return 2;
+    }
+    dump(t, y);
+    return 0;
+  } catch (const std::exception&) {
+    return 1;
+  }
+}
+
 void ytref_f32_to_bf16(const float* x, uint16_t* y, int64_t n) {
   for (int64_t i = 0; i < n; ++i) {
     yt::bfloat16 v(x[i]);

@@ -157,6 +157,13 @@ def main() -> None:
     g["act_leakyRelu_0p2"] = R.activation("leakyRelu", ax, 0.2)
     g["act_elu_0p5"] = R.activation("elu", ax, 0.5)
 
+    # ---- first derivatives (order = 1) of the activations on the same inputs -------------
+    for name in ("swish", "relu", "exp", "sigmoid", "leakyRelu", "elu", "selu", "gelu", "tanh", "softplus", "mish",
+                 "hardSigmoid", "hardSwish"):
+        g[f"actd_{name}"] = R.activation(name, ax, order=1)
+    g["actd_leakyRelu_0p2"] = R.activation("leakyRelu", ax, 0.2, order=1)
+    g["actd_elu_0p5"] = R.activation("elu", ax, 0.5, order=1)
+
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB, {len(g)} arrays)")
 

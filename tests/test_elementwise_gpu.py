@@ -78,6 +78,26 @@ def test_activations_match_reference(api, golden, name, alpha, key):
     assert r.data_ptr() == d.data_ptr() and np.array_equal(d.cpu().numpy(), got)  # the in-place form
 
 
+@pytest.mark.parametrize("name,alpha", [
+    ("swish", None), ("relu", None), ("exp", None), ("sigmoid", None), ("leakyRelu", None), ("leakyRelu", 0.2),
+    ("elu", None), ("elu", 0.5), ("selu", None), ("gelu", None), ("tanh", None), ("softplus", None), ("mish", None),
+    ("hardSigmoid", None), ("hardSwish", None)])
+def test_activation_first_derivatives_match_reference(api, golden, name, alpha):
+    key = f"actd_{name}" + ("" if alpha is None else "_0p2" if name == "leakyRelu" else "_0p5")
+    x, want = golden["act_x"], golden[key]
+    kw = {} if alpha is None else {"alpha": alpha}
+    got = getattr(api, name)(dev(x), order=1, **kw).cpu().numpy()
+    if name in ("relu", "leakyRelu", "hardSigmoid", "hardSwish"):
+        assert np.array_equal(got, want)
+    else:
+        assert np.all(np.abs(got.astype(np.float64) - want) <= 1e-5 * np.abs(want) + 2e-7)
+    d = dev(x)
+    getattr(api, name + "_")(d, order=1, **kw)
+    assert np.array_equal(d.cpu().numpy(), got)
+    with pytest.raises(ValueError):  # the reference's other orders (integrals, higher derivatives) stay on the host
+        getattr(api, name)(dev(x), order=2, **kw)
+
+
 def test_activation_dtypes_and_bad_op(api, port):
     from ytensor_b200 import _lib
     x = (np.random.default_rng(5).standard_normal(3000) * 2).astype(np.float32)
@@ -90,6 +110,8 @@ def test_activation_dtypes_and_bad_op(api, port):
     t = dev(x)
     with pytest.raises(RuntimeError):
         api._unary(16, t, None, 0.0)
+    with pytest.raises(RuntimeError):
+        api._unary(34, t, None, 0.0)  # 32 + scale: not an activation
     with pytest.raises(RuntimeError):
         api._unary(-1, t, None, 0.0)
 

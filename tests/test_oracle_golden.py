@@ -116,6 +116,21 @@ def test_activations(golden, port, name, alpha, key):
     assert np.array_equal(port.activation(name, golden["act_x"], alpha), golden[key], equal_nan=True)
 
 
+DERIV_CASES = [(n, None, f"actd_{n}") for n in ("swish", "relu", "exp", "sigmoid", "leakyRelu", "elu", "selu", "gelu",
+                                                 "tanh", "softplus", "mish", "hardSigmoid", "hardSwish")]
+DERIV_CASES += [("leakyRelu", 0.2, "actd_leakyRelu_0p2"), ("elu", 0.5, "actd_elu_0p5")]
+
+
+@pytest.mark.parametrize("name,alpha,key", DERIV_CASES)
+def test_activation_derivatives(golden, port, name, alpha, key):
+    got, want = port.activation(name, golden["act_x"], alpha, order=1), golden[key]
+    if name in ("swish", "tanh", "mish"):
+        # the reference was compiled with FMA contraction (1 - t * t as one fused operation), the port without
+        assert np.all(np.abs(got.astype(np.float64) - want) <= 2.5e-7 * np.abs(want) + 1.5e-7)  # (one ulp at 1)
+    else:
+        assert np.array_equal(got, want, equal_nan=True)
+
+
 def test_chain(golden, port):
     for r in ("r1", "r2"):
         got = port.chain(golden["chain_x"], golden["chain_w"], golden[f"chain_{r}"])

@@ -319,30 +319,46 @@ def _unary(op: int, x: torch.Tensor, out: torch.Tensor | None, param: float = 0.
     return out
 
 
-def swish(x): return _unary(1, x, None)
+def swish(x, order=0): return _unary(_act_op("swish", 1, order), x, None)
 
 
-def swish_(x):
-    """x * sigmoid(x) in place (reference yt::function::swish_, src/function/activation.inl:631-647)."""
-    return _unary(1, x, x)
+def swish_(x, order=0):
+    """x * sigmoid(x) in place (reference yt::function::swish_, src/function/activation.inl:631-647); order 1: its
+    first derivative."""
+    return _unary(_act_op("swish", 1, order), x, x)
 
-# The other activations of yt::function (reference src/function/activation.inl), forward form; `name_` works in place.
+# The other activations of yt::function (reference src/function/activation.inl); `name_` works in place.
 _ACTIVATIONS = {"relu": 4, "exp": 5, "sigmoid": 6, "leakyRelu": 7, "elu": 8, "selu": 9, "gelu": 10, "tanh": 11,
                 "softplus": 12, "mish": 13, "hardSigmoid": 14, "hardSwish": 15}
 _ACT_DEFAULT_PARAM = {"leakyRelu": 0.01, "elu": 1.0}
 
 
+def _act_op(name: str, op: int, order: int) -> int:
+    if order == 0:
+        return op
+    if order == 1:
+        return 32 + op
+    raise _lib.YtCudaInvalidArgument(_lib.UNSUPPORTED, f"{name}: order {order} is not on the device (0 and 1 are)")
+
+
 def _make_activation(name: str, op: int):
     default = _ACT_DEFAULT_PARAM.get(name)
+    if default is None:
+        def f(x, order=0):
+            return _unary(_act_op(name, op, order), x, None, 0.0)
 
-    def f(x, alpha=default):
-        return _unary(op, x, None, 0.0 if alpha is None else float(alpha))
+        def f_(x, order=0):
+            return _unary(_act_op(name, op, order), x, x, 0.0)
+    else:
+        def f(x, alpha=default, order=0):
+            return _unary(_act_op(name, op, order), x, None, float(alpha))
 
-    def f_(x, alpha=default):
-        return _unary(op, x, x, 0.0 if alpha is None else float(alpha))
+        def f_(x, alpha=default, order=0):
+            return _unary(_act_op(name, op, order), x, x, float(alpha))
 
     f.__name__, f_.__name__ = name, name + "_"
-    f.__doc__ = f_.__doc__ = f"yt::function::{name} (reference src/function/activation.inl), forward form."
+    f.__doc__ = f_.__doc__ = (f"yt::function::{name} (reference src/function/activation.inl): order 0 the function, "
+                              "order 1 its first derivative.")
     return f, f_
 
 

@@ -20,6 +20,7 @@ enum UnOp {
   U_SOFTPLUS = 12, U_MISH = 13, U_HARD_SIGMOID = 14, U_HARD_SWISH = 15
 };
 constexpr int U_LAST = U_HARD_SWISH;
+constexpr int U_DERIV = 32;  // op + 32: the first derivative (order 1) of activation `op`
 
 __device__ __forceinline__ float bin_apply(int op, float a, float b) {
   switch (op) {
@@ -50,7 +51,49 @@ __device__ __forceinline__ float sigmoid_ref(float v) {
 }
 __device__ __forceinline__ float softplus_ref(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 
+// First derivatives (the order == 1 branches of src/function/activation.inl)
+__device__ __forceinline__ float un_deriv(int op, float a, float param) {
+  switch (op) {
+    case U_SWISH: {                                                                 // :621-629
+      const float sig = sigmoid_ref(a);
+      return sig * (1.0f + a * (1.0f - sig));
+    }
+    case U_RELU: return a > 0.f ? 1.f : 0.f;                                        // :11-14
+    case U_EXP: return expf(a);                                                     // :67-84
+    case U_SIGMOID: {                                                               // :94-99
+      const float sig = sigmoid_ref(a);
+      return sig * (1.0f - sig);
+    }
+    case U_LEAKY_RELU: return a > 0.f ? 1.f : param;                                // :421-425
+    case U_ELU: return a > 0.f ? 1.f : param * expf(a);                             // :457-461
+    case U_SELU: {                                                                  // :495-503
+      const float l = 1.0507009873554804934193349852946f, al = 1.6732632423543772848170429916717f;
+      return a > 0.f ? l : l * al * expf(a);
+    }
+    case U_GELU: {                                                                  // :538-547
+      const float cdf = 0.5f * (1.0f + erff(a / 1.4142135623730950488016887242097f));
+      const float pdf = 0.3989422804014326779399460599343f * expf(-0.5f * a * a);
+      return cdf + a * pdf;
+    }
+    case U_TANH: {                                                                  // :583-588
+      const float t = tanhf(a);
+      return 1.0f - t * t;
+    }
+    case U_SOFTPLUS: return sigmoid_ref(a);                                         // :658-660
+    case U_MISH: {                                                                  // :689-697
+      const float tsp = tanhf(softplus_ref(a));
+      return tsp + a * (1.0f - tsp * tsp) * sigmoid_ref(a);
+    }
+    case U_HARD_SIGMOID: return (a > -3.f && a < 3.f) ? 1.0f / 6.0f : 0.f;          // :733-739
+    default:                                                                        // hardSwish, :776-783
+      if (a <= -3.f) return 0.f;
+      if (a >= 3.f) return 1.f;
+      return (2.f * a + 3.f) / 6.0f;
+  }
+}
+
 __device__ __forceinline__ float un_apply(int op, float a, float param) {
+  if (op >= U_DERIV) return un_deriv(op - U_DERIV, a, param);
   switch (op) {
     case U_COPY: return a;
     case U_SWISH: return swish_ref(a);
@@ -260,7 +303,11 @@ int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const v
 
 int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
                  const int64_t* xstrides, const int64_t* ystrides, float param, void* stream) {
-  YTC_REQUIRE(op >= 0 && op <= U_LAST, "ytcuda_unary: op %d outside 0..%d", op, U_LAST);
+  {
+    const int base = op >= U_DERIV ? op - U_DERIV : op;
+    YTC_REQUIRE(op >= 0 && base <= U_LAST && (op < U_DERIV || base == U_SWISH || base >= U_RELU),
+                "ytcuda_unary: op %d is neither 0..%d nor %d + an activation (1, 4..%d)", op, U_LAST, U_DERIV, U_LAST);
+  }
   YTC_REQUIRE(ndim >= 1 && ndim <= EW_MAXD, "ytcuda_unary: ndim %d outside [1, %d]", ndim, EW_MAXD);
   YTC_REQUIRE(shape && xstrides && ystrides, "ytcuda_unary: null shape/strides");
   YTC_REQUIRE(dt_in >= 0 && dt_in <= 2 && dt_out >= 0 && dt_out <= 2, "ytcuda_unary: bad dtype");
