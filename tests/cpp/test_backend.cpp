@@ -135,6 +135,9 @@ int main() {
     report("elu(0.5)", normwise(yt::cuda::elu(x, 0.5f), yt::function::elu(x, 0.5f)), 1e-6);
     report("mish", normwise(yt::cuda::mish(x), yt::function::mish(x)), 1e-6);
     report("hardSwish", normwise(yt::cuda::hardSwish(x), yt::function::hardSwish(x)), 1e-30);
+    report("gelu'", normwise(yt::cuda::gelu(x, 1), yt::function::gelu(x, 1)), 1e-6);
+    report("mish'", normwise(yt::cuda::mish(x, 1), yt::function::mish(x, 1)), 1e-6);
+    report("elu'(0.5)", normwise(yt::cuda::elu(x, 0.5f, 1), yt::function::elu(x, 0.5f, 1)), 1e-6);
   }
   std::printf("%s (%d failures)\n", g_fail ? "SOME CASES FAILED" : "ALL CASES PASSED", g_fail);
   return g_fail ? 1 : 0;

@@ -340,20 +340,28 @@ yt::YTensor<T, dim> unary(int op, const yt::YTensor<T, dim>& x, float param = 0.
 }
 }  // namespace detail
 
-// the activations of yt::function, forward form (include/function/activation.hpp:9-109; order 0)
-template <typename T, int dim> yt::YTensor<T, dim> swish(const yt::YTensor<T, dim>& x) { return detail::unary(1, x); }
-template <typename T, int dim> yt::YTensor<T, dim> relu(const yt::YTensor<T, dim>& x) { return detail::unary(4, x); }
-template <typename T, int dim> yt::YTensor<T, dim> exp(const yt::YTensor<T, dim>& x) { return detail::unary(5, x); }
-template <typename T, int dim> yt::YTensor<T, dim> sigmoid(const yt::YTensor<T, dim>& x) { return detail::unary(6, x); }
-template <typename T, int dim> yt::YTensor<T, dim> leakyRelu(const yt::YTensor<T, dim>& x, float alpha = 0.01f) { return detail::unary(7, x, alpha); }
-template <typename T, int dim> yt::YTensor<T, dim> elu(const yt::YTensor<T, dim>& x, float alpha = 1.0f) { return detail::unary(8, x, alpha); }
-template <typename T, int dim> yt::YTensor<T, dim> selu(const yt::YTensor<T, dim>& x) { return detail::unary(9, x); }
-template <typename T, int dim> yt::YTensor<T, dim> gelu(const yt::YTensor<T, dim>& x) { return detail::unary(10, x); }
-template <typename T, int dim> yt::YTensor<T, dim> tanh(const yt::YTensor<T, dim>& x) { return detail::unary(11, x); }
-template <typename T, int dim> yt::YTensor<T, dim> softplus(const yt::YTensor<T, dim>& x) { return detail::unary(12, x); }
-template <typename T, int dim> yt::YTensor<T, dim> mish(const yt::YTensor<T, dim>& x) { return detail::unary(13, x); }
-template <typename T, int dim> yt::YTensor<T, dim> hardSigmoid(const yt::YTensor<T, dim>& x) { return detail::unary(14, x); }
-template <typename T, int dim> yt::YTensor<T, dim> hardSwish(const yt::YTensor<T, dim>& x) { return detail::unary(15, x); }
+namespace detail {
+inline int act_op(int op, int order) {
+  if (order == 0) return op;
+  if (order == 1) return op + 32;
+  throw std::invalid_argument("yt::cuda activation: only order 0 and 1 run on the device");
+}
+}  // namespace detail
+
+// the activations of yt::function (include/function/activation.hpp:9-109): order 0 the function, 1 its first derivative
+template <typename T, int dim> yt::YTensor<T, dim> swish(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(1, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> relu(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(4, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> exp(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(5, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> sigmoid(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(6, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> leakyRelu(const yt::YTensor<T, dim>& x, float alpha = 0.01f, int order = 0) { return detail::unary(detail::act_op(7, order), x, alpha); }
+template <typename T, int dim> yt::YTensor<T, dim> elu(const yt::YTensor<T, dim>& x, float alpha = 1.0f, int order = 0) { return detail::unary(detail::act_op(8, order), x, alpha); }
+template <typename T, int dim> yt::YTensor<T, dim> selu(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(9, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> gelu(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(10, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> tanh(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(11, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> softplus(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(12, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> mish(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(13, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> hardSigmoid(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(14, order), x); }
+template <typename T, int dim> yt::YTensor<T, dim> hardSwish(const yt::YTensor<T, dim>& x, int order = 0) { return detail::unary(detail::act_op(15, order), x); }
 
 // YTensorBase::cast / copy_ between float, bfloat16 and float16 (src/ytensor_base.inl:257-430), bit-exact with the
 // reference's own constructors
