@@ -41,12 +41,38 @@ int ytcuda_host_alloc(void** hptr, uint64_t bytes);
 int ytcuda_host_free(void* hptr);
 int ytcuda_memcpy_h2d(void* dst, const void* src, uint64_t bytes, void* stream);
 int ytcuda_memcpy_d2h(void* dst, const void* src, uint64_t bytes, void* stream);
+int ytcuda_memcpy_d2d(void* dst, const void* src, uint64_t bytes, void* stream);
 int ytcuda_stream_sync(void* stream);
+/* 1 when `p` points into device memory (storage from ytcuda_malloc), 0 for host memory, pinned or pageable. The C++
+ * layer asks this to tell a device-resident YTensor from a host-resident one: the reference's tensor carries no
+ * residency tag (include/ytensor_base.hpp:388-393), only its storage pointer. */
+int ytcuda_pointer_is_device(const void* p);
 /* Reads and clears the device status word that kernels with bounded waits write
  * (YTC_OK or YTC_TIMEOUT). Synchronises `stream`. */
 int ytcuda_device_status(void* stream);
 /* Number of kernels this library has launched in the calling process. */
 uint64_t ytcuda_launch_count(void);
+/* Number of ytcuda_memcpy_h2d / ytcuda_memcpy_d2h calls made by the calling process: lets a caller check that a chain
+ * of operators on device-resident tensors crossed PCIe only where it meant to. */
+void ytcuda_copy_counts(uint64_t* h2d, uint64_t* d2h);
+/* Cycle budget of the bounded device-side waits of the decode step kernel (grid barriers, barriers across
+ * tensor-parallel ranks) and of ytcuda_wait_probe; the default, 2e9 cycles, is about a second. A wait that runs out
+ * makes its kernel return and ytcuda_device_status report YTC_TIMEOUT. Process-wide. The TMA / MMA pipelines of the
+ * GEMM and attention kernels keep their compiled-in budget. No counterpart in the reference (its kernels have no
+ * waits). */
+int ytcuda_set_wait_limit(int64_t cycles);
+int64_t ytcuda_get_wait_limit(void);
+/* Launches one small kernel that waits on an mbarrier nothing arrives on, with the current cycle budget: the wait gives
+ * up, the kernel returns, ytcuda_device_status reports YTC_TIMEOUT once and the device stays usable. The give-up path
+ * of the library's bounded waits in isolation, for tests and health checks. waited_cycles_dev (device pointer, may be
+ * NULL) receives the cycles spent. No counterpart in the reference. */
+int ytcuda_wait_probe(int64_t* waited_cycles_dev, void* stream);
+
+/* Scratch memory. The entry points that need scratch beyond their inputs and outputs (fp32 GEMM on the tensor cores,
+ * long reductions, attention over a KV cache split over keys, the decoder's split-k linears) take it from a buffer the
+ * library keeps per (device, stream), grown with stream-ordered allocation on the caller's stream: calls on different
+ * streams never share scratch, and growing does not synchronise the device. Such a call may therefore allocate; make
+ * the first call of each kind outside any stream capture. ytcuda_reduce_noalloc is the form that never allocates. */
 
 /* ---------------------------------------------------------------- GEMM
  * C[b] = alpha * A[b] . B[b] + beta * C[b],  A [m,k], B [k,n], C [m,n], b in [0,batch).
@@ -146,6 +172,10 @@ int ytcuda_reduce(int op, int dt_in, int dt_out, const void* x, void* y, int32_t
  * from different threads, race on it - serialise them. */
 int ytcuda_reduce_noalloc(int op, int dt_in, int dt_out, const void* x, void* y, int32_t* index, const int64_t* shape,
                           const int64_t* xstrides, int ndim, const int* axes, int naxes, void* stream);
+/* Bytes of the fixed array a ytcuda_reduce_noalloc call may use (0 = all 65536). With the library's own chunking a
+ * call needs at most 8 bytes x 6 x the SM count (about 7 KiB on a 148-SM part), so the refusal cannot occur at the
+ * default; an embedder that wants the guarantee checked, or a test, lowers the limit. No counterpart in the reference. */
+int ytcuda_reduce_noalloc_set_limit(uint64_t bytes);
 
 /* Fused memory-bound chain: out = cast(softmax(rmsNorm(x, weight, -1, eps) + residual, -1)).
  * x [batch, rows, hidden] fp32 contiguous; residual [batch, rows, hidden] (residual_batched != 0) or
@@ -278,6 +308,14 @@ int ytcuda_qwen3_set_decode_path(void* handle, int path);
  * the reference (single process). */
 int ytcuda_qwen3_tp_export(void* handle, void* ipc_handle_64);
 int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64);
+/* Tear-down order of a tensor-parallel group: every rank calls ytcuda_qwen3_tp_disconnect (waits for its own kernels,
+ * closes the peers' buffers), the caller runs a barrier over the group, then every rank calls ytcuda_qwen3_destroy
+ * (which frees the buffer it exported). Freeing an exported buffer that a peer still has open is undefined. */
+int ytcuda_qwen3_tp_disconnect(void* handle);
+/* Recovery after ytcuda_device_status reported YTC_TIMEOUT under tensor parallelism (a peer never arrived): every rank
+ * waits for its own stream, the caller runs a barrier, every rank calls this (exchange counters and arrival words
+ * start again from zero, KV caches reset), a second barrier, then forward may be called again. */
+int ytcuda_qwen3_tp_resync(void* handle);
 /* ids [batch, len] int32 (device) -> logits of the last position [batch, rank's vocab rows] fp32 (device); appends
  * len tokens to the KV caches (Qwen3ForCausalLM::forward, qwen3.cpp:449-457). The caches are ring buffers as in the
  * reference (qwen3.cpp:70-126): once max_position_embeddings tokens are cached, a call with len == 1 overwrites the

@@ -1,7 +1,8 @@
-"""GPU (2 devices): the tensor-parallel decoder gives the reference's logits and greedy tokens.
-Two child processes, one per GPU; the partial sums after the attention output and down projections are reduced by NCCL
+"""GPU (2, 4 or 8 devices): the tensor-parallel decoder gives the reference's logits and greedy tokens.
+One child process per GPU; the partial sums after the attention output and down projections are reduced by NCCL
 (prefill, and decode with one launch per operator) or inside the persistent decode-step kernel over peer memory.
-Skipped when fewer than two devices are visible."""
+A second test lets one rank skip a decode step: the other rank's step kernel waits for it with a short cycle budget,
+gives up, reports YTC_TIMEOUT, and the group recovers. Each case is skipped when too few devices are visible."""
 import os
 import sys
 from pathlib import Path
@@ -34,7 +35,7 @@ def _worker(rank, world, port, ret):
         cfg = Q.Qwen3Config(**SMALL)
         want = g["small_logits_b2"]
         ids = torch.from_numpy(g["small_ids_b2"]).cuda()
-        for path in (2, 1):
+        for path in ((2, 1) if world == 2 else ()):  # (the small reference model has two kv heads)
             m = Q.Qwen3ForCausalLM(cfg, batch=2, tp_rank=rank, tp_world=world)
             m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
             m.set_decode_path(path)
@@ -56,7 +57,8 @@ def _worker(rank, world, port, ret):
         # six sequences: the step kernel's linear phases run on the tensor cores (mma.sync form), the sums over ranks
         # still inside the kernel; against the operator path with the NCCL callback, both fed the same tokens
         cfg = Q.Qwen3Config(hidden_size=256, num_hidden_layers=3, vocab_size=1000, intermediate_size=2816,
-                            num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=128)
+                            num_attention_heads=4 if world == 2 else 16, num_key_value_heads=2 if world == 2 else 8,
+                            head_dim=128, max_position_embeddings=128)
         w = Q.random_weights(cfg, seed=11, std=0.05)
         ids = torch.from_numpy(np.random.default_rng(6).integers(0, cfg.vocab_size, (6, 20)).astype(np.int32)).cuda()
         ms = []
@@ -93,21 +95,88 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_two_gpu_tensor_parallel_matches_reference():
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs two CUDA devices")
+def _run_ranks(target, world):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        port = 29600 + (os.getpid() % 2000)
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
+        port = 29600 + (os.getpid() % 2000) + world
+        procs = [ctx.Process(target=target, args=(r, world, port, ret)) for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:
-            p.join(600)
+            p.join(900)
         for p in procs:
             if p.is_alive():
                 p.kill()
                 pytest.fail("a rank did not finish")
-        assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)
+        assert dict(ret) == {r: "ok" for r in range(world)}, dict(ret)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_matches_reference(world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
+    _run_ranks(_worker, world)
+
+
+def _timeout_worker(rank, world, port, ret):
+    """Rank 1 leaves out one decode step (between steps, nothing of its own in flight); rank 0's step kernel waits for
+    rank 1's arrival word with a 20 ms budget, gives up and returns; the status word says so; the group recovers and
+    reproduces the reference's logits."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    from ytensor_b200 import _lib
+    from ytensor_b200 import qwen3 as Q
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    L = _lib.lib()
+    try:
+        g = np.load(ROOT / "tests" / "golden" / "golden_qwen3.npz")
+        cfg = Q.Qwen3Config(**SMALL)
+        want = g["small_logits_b2"]
+        ids = torch.from_numpy(g["small_ids_b2"]).cuda()
+        m = Q.Qwen3ForCausalLM(cfg, batch=2, tp_rank=rank, tp_world=world)
+        m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
+        m.set_decode_path(2)
+        logits = m.forward(ids)
+        tok, _ = m.argmax(logits)
+        tok = tok.reshape(2, 1).contiguous()
+        logits = m.forward(tok)       # one good step on both ranks
+        m.check_status()
+        dist.barrier()
+        old = L.ytcuda_get_wait_limit()
+        _lib.check(L.ytcuda_set_wait_limit(40_000_000))   # about 20 ms
+        if rank == 0:
+            t0 = __import__("time").perf_counter()
+            m.forward(tok)            # rank 1 never launches this step
+            try:
+                m.check_status()
+                raise AssertionError("the step kernel should have given up on its peer")
+            except _lib.YtCudaError as e:
+                assert e.status == _lib.TIMEOUT, e
+            assert __import__("time").perf_counter() - t0 < 5.0
+        _lib.check(L.ytcuda_set_wait_limit(old))
+        m.recover()                   # every rank: barrier, counters and arrival words to zero, barrier
+        logits = m.forward(ids)
+        for step in range(4):
+            got = logits.cpu().numpy()
+            err = np.abs(got - want[step][:, m.v0:m.v1]).max() / np.abs(want[step]).max()
+            assert err < 1e-4, (step, err)
+            tok, _ = m.argmax(logits)
+            logits = m.forward(tok.reshape(2, 1).contiguous())
+        m.check_status()
+        m.close()
+        ret[rank] = "ok"
+    except Exception as e:  # noqa: BLE001 - reported to the parent
+        ret[rank] = f"{type(e).__name__}: {e}"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_step_kernel_gives_up_on_a_missing_peer_and_the_group_recovers():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    _run_ranks(_timeout_worker, 2)

@@ -23,9 +23,15 @@ SIGNATURES = {
     "ytcuda_host_free": (_i, [_vp]),
     "ytcuda_memcpy_h2d": (_i, [_vp, _vp, _u64, _vp]),
     "ytcuda_memcpy_d2h": (_i, [_vp, _vp, _u64, _vp]),
+    "ytcuda_memcpy_d2d": (_i, [_vp, _vp, _u64, _vp]),
+    "ytcuda_pointer_is_device": (_i, [_vp]),
     "ytcuda_stream_sync": (_i, [_vp]),
     "ytcuda_device_status": (_i, [_vp]),
     "ytcuda_launch_count": (_u64, []),
+    "ytcuda_copy_counts": (None, [_vp, _vp]),
+    "ytcuda_set_wait_limit": (_i, [_i64]),
+    "ytcuda_get_wait_limit": (_i64, []),
+    "ytcuda_wait_probe": (_i, [_vp, _vp]),
     "ytcuda_gemm": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4 + [_vp]),
     "ytcuda_gemm_masked": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i] + [_i64] * 6 + [_i64] * 4 + [_vp, _i64, _f, _vp]),
     "ytcuda_gemm_set_path": (_i, [_i]),
@@ -38,6 +44,7 @@ SIGNATURES = {
     "ytcuda_layernorm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp]),
     "ytcuda_reduce": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "ytcuda_reduce_noalloc": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "ytcuda_reduce_noalloc_set_limit": (_i, [_u64]),
     "ytcuda_rmsnorm_add_softmax_cast": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _i64, _i, _i, _f, _vp]),
     "ytcuda_binary": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "ytcuda_unary": (_i, [_i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp]),
@@ -60,6 +67,8 @@ SIGNATURES = {
     "ytcuda_qwen3_set_decode_path": (_i, [_vp, _i]),
     "ytcuda_qwen3_tp_export": (_i, [_vp, _vp]),
     "ytcuda_qwen3_tp_import": (_i, [_vp, _i, _vp]),
+    "ytcuda_qwen3_tp_disconnect": (_i, [_vp]),
+    "ytcuda_qwen3_tp_resync": (_i, [_vp]),
     "ytcuda_qwen3_forward": (_i, [_vp, _vp, _i, _vp, _vp]),
 }
 

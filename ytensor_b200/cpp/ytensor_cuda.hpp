@@ -9,6 +9,8 @@
 //   auto o = yt::cuda::scaledDotProductAttention(q, k, v, 0.f, yt::cuda::Causal{kv_len - q_len});
 #pragma once
 #include <cstdint>
+#include <cstring>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <type_traits>
@@ -137,6 +139,11 @@ yt::YTensor<T, dim> linear(const yt::YTensor<T, dim>& x, const yt::YTensor<T, 2>
 // ------------------------------------------------------------------ attention
 struct Causal {
   int offset;  // key c is visible to query r iff c <= r + offset (the reference's masks use kv_len - q_len)
+  // the callable and tile-pruning forms the reference's predicate overloads expect (src/ytensor_math.inl:386,
+  // src/kernel/avx2/sgemm.inl:449-475), so that the same object also works with its CPU back-ends
+  bool operator()(int r, int c) const { return c <= r + offset; }
+  bool tileAllTrue(int r0, int c0, int, int nr) const { return c0 + nr - 1 <= r0 + offset; }
+  bool tileAllFalse(int r0, int c0, int mr, int) const { return c0 > r0 + mr - 1 + offset; }
 };
 
 namespace detail {
@@ -376,5 +383,393 @@ yt::YTensor<U, dim> cast(const yt::YTensor<T, dim>& x) {
   dy.download(y.data());
   return y;
 }
+
+
+// ------------------------------------------------------------------ device-resident tensors
+// A device-resident tensor IS a yt::YTensor<T, dim>: its storage comes from ytcuda_malloc and is released by
+// ytcuda_free through the deleter of the tensor's std::shared_ptr<char[]> (the hook the reference already uses for
+// its own storage, include/ytensor_base.hpp:388-393, src/ytensor_base.inl:51-58). Shape, strides, offset, views
+// (slice / transpose / reshape) and shallow copies work as on any YTensor; element access (at(), printing, host
+// loops) must not be used on it. The functions of yt::cuda::dev below take and return such tensors and copy nothing
+// between host and device, so that a chain of operators pays PCIe once on the way in and once on the way out.
+namespace detail {
+template <typename T, int dim>
+class DeviceBacked : public yt::YTensor<T, dim> {
+ public:
+  explicit DeviceBacked(const std::vector<int>& shape) {
+    if (static_cast<int>(shape.size()) != dim) throw std::invalid_argument("device tensor: wrong number of dims");
+    size_t n = 1;
+    for (int v : shape) {
+      if (v < 0) throw std::invalid_argument("device tensor: negative extent");
+      n *= static_cast<size_t>(v);
+    }
+    void* p = nullptr;
+    check(ytcuda_malloc(&p, n * sizeof(T) > 0 ? n * sizeof(T) : 1));
+    this->_data = std::shared_ptr<char[]>(static_cast<char*>(p), [](char* q) { ytcuda_free(q); });
+    this->_shape = shape;
+    this->_stride.assign(dim, 1);
+    for (int d = dim - 2; d >= 0; --d) this->_stride[d] = this->_stride[d + 1] * shape[d + 1];
+    this->_offset = 0;
+    this->_element_size = sizeof(T);
+    this->_dtype = yt::types::getTypeName<T>();
+  }
+};
+template <typename T, int dim>
+std::vector<int64_t> strides_of(const yt::YTensor<T, dim>& t) {
+  std::vector<int64_t> s(dim);
+  for (int d = 0; d < dim; ++d) s[d] = t.stride_(d);
+  return s;
+}
+}  // namespace detail
+
+// True when the tensor's storage is device memory.
+template <typename T, int dim>
+bool on_device(const yt::YTensor<T, dim>& t) {
+  return t.size() > 0 && ytcuda_pointer_is_device(t.data()) != 0;
+}
+
+// A new device-resident tensor (contents undefined).
+template <typename T, int dim>
+yt::YTensor<T, dim> empty_device(const std::vector<int>& shape) {
+  const detail::DeviceBacked<T, dim> backed(shape);
+  const yt::YTensor<T, dim>& as_tensor = backed;  // (the copy constructor: shares the storage)
+  return yt::YTensor<T, dim>(as_tensor);
+}
+// One upload: a contiguous device-resident copy of a host tensor.
+template <typename T, int dim>
+yt::YTensor<T, dim> to_device(const yt::YTensor<T, dim>& host) {
+  auto c = host.isContiguous() ? host : host.contiguous();
+  auto d = empty_device<T, dim>(c.shape());
+  check(ytcuda_memcpy_h2d(d.data(), c.data(), c.size() * sizeof(T), nullptr));
+  check(ytcuda_stream_sync(nullptr));
+  return d;
+}
+// One download: a host tensor with the contents of a device-resident one (any strides).
+template <typename T, int dim>
+yt::YTensor<T, dim> to_host(const yt::YTensor<T, dim>& dev_t);
+
+namespace dev {
+// contiguous device copy of a device tensor with any strides (ytcuda_cast with equal types is a strided copy)
+template <typename T, int dim>
+yt::YTensor<T, dim> contiguous(const yt::YTensor<T, dim>& x) {
+  if (x.isContiguous()) return x;
+  auto y = empty_device<T, dim>(x.shape());
+  const auto shape = detail::widen(x.shape());
+  const auto xs = detail::strides_of(x), ys = detail::strides_of(y);
+  check(ytcuda_cast(dtype_of<T>(), dtype_of<T>(), x.data(), y.data(), dim, shape.data(), xs.data(), ys.data(), nullptr));
+  return y;
+}
+
+// YTensor::matmul on device-resident operands (same operand forms as yt::cuda::matmul); the result stays on the device.
+template <typename T, int dim0, int dim1>
+auto matmul(const yt::YTensor<T, dim0>& a, const yt::YTensor<T, dim1>& b) {
+  static_assert(dim0 >= 2 && dim1 >= 2, "matmul needs rank >= 2 operands");
+  static_assert(dim1 == 2 || dim0 == dim1, "matmul: the right operand is 2-D or has the rank of the left operand");
+  if (a.shape(-1) != b.shape(-2)) throw std::invalid_argument("matmul: inner dimensions do not match");
+  if constexpr (dim1 != 2)
+    for (int d = 0; d < dim0 - 2; ++d)
+      if (a.shape(d) != b.shape(d)) throw std::invalid_argument("matmul: batch dimensions do not match");
+  const int m = a.shape(-2), k = a.shape(-1), n = b.shape(-1);
+  auto ac = dim0 == 2 ? a : contiguous(a);  // leading dims must collapse into one batch stride
+  auto bc = dim1 == 2 ? b : contiguous(b);
+  std::vector<int> oshape = ac.shape();
+  oshape[dim0 - 1] = n;
+  auto out = empty_device<T, dim0>(oshape);
+  int64_t batch = 1;
+  for (int d = 0; d < dim0 - 2; ++d) batch *= ac.shape(d);
+  check(ytcuda_gemm(dtype_of<T>(), dtype_of<T>(), ac.data(), bc.data(), out.data(), m, n, k, 1.0f, 0.0f, ac.stride_(-2),
+                    ac.stride_(-1), bc.stride_(-2), bc.stride_(-1), n, 1, batch, static_cast<int64_t>(m) * k,
+                    dim1 == 2 ? 0 : static_cast<int64_t>(k) * n, static_cast<int64_t>(m) * n, nullptr));
+  return out;
+}
+
+// yt::function::softmax_ (src/function/activation.inl:376-409) in place on a device tensor, any strides.
+template <typename T, int dim>
+yt::YTensor<T, dim>& softmax_(yt::YTensor<T, dim>& x, const std::vector<int>& axes) {
+  const auto shape = detail::widen(x.shape());
+  const auto st = detail::strides_of(x);
+  check(ytcuda_softmax(dtype_of<T>(), dtype_of<T>(), x.data(), x.data(), shape.data(), st.data(), st.data(), dim,
+                       axes.data(), static_cast<int>(axes.size()), nullptr));
+  return x;
+}
+template <typename T, int dim>
+yt::YTensor<T, dim> softmax(const yt::YTensor<T, dim>& x, const std::vector<int>& axes) {
+  auto y = empty_device<T, dim>(x.shape());
+  const auto shape = detail::widen(x.shape());
+  const auto xs = detail::strides_of(x), ys = detail::strides_of(y);
+  check(ytcuda_softmax(dtype_of<T>(), dtype_of<T>(), x.data(), y.data(), shape.data(), xs.data(), ys.data(), dim,
+                       axes.data(), static_cast<int>(axes.size()), nullptr));
+  return y;
+}
+
+// yt::function::rmsNorm_ / rmsNorm (src/function/normalization.inl:234-277) on device tensors; the weight (device
+// resident, one dim per axis, contiguous) multiplies after the division.
+template <typename T, int dim, int wdim>
+void rmsNorm_into(const yt::YTensor<T, dim>& x, const yt::YTensor<T, wdim>& weight, const std::vector<int>& axes, T eps,
+                  yt::YTensor<T, dim>& y) {
+  if (static_cast<int>(axes.size()) != wdim) throw std::invalid_argument("rmsNorm: weight dim must match axes size");
+  for (int i = 0; i < wdim; ++i)
+    if (weight.shape(i) != x.shape(axes[i])) throw std::invalid_argument("rmsNorm: weight shape must match affine axes");
+  auto w = contiguous(weight);
+  const auto shape = detail::widen(x.shape());
+  const auto xs = detail::strides_of(x), ys = detail::strides_of(y);
+  check(ytcuda_rmsnorm(dtype_of<T>(), dtype_of<T>(), dtype_of<T>(), x.data(), w.data(), y.data(), shape.data(),
+                       xs.data(), ys.data(), dim, axes.data(), wdim, static_cast<float>(eps), nullptr));
+}
+template <typename T, int dim, int wdim>
+yt::YTensor<T, dim>& rmsNorm_(yt::YTensor<T, dim>& x, const yt::YTensor<T, wdim>& weight, const std::vector<int>& axes,
+                              T eps) {
+  rmsNorm_into(x, weight, axes, eps, x);
+  return x;
+}
+template <typename T, int dim, int wdim>
+yt::YTensor<T, dim> rmsNorm(const yt::YTensor<T, dim>& x, const yt::YTensor<T, wdim>& weight,
+                            const std::vector<int>& axes, T eps) {
+  auto y = empty_device<T, dim>(x.shape());
+  rmsNorm_into(x, weight, axes, eps, y);
+  return y;
+}
+
+// The in-place operators += -= *= /= (src/ytensor_math.inl:35-49) with the right operand broadcast over `a` by the
+// reference's rule: shapes are aligned at the last dim and a size-1 (or missing) dim of b repeats.
+template <typename T, int dim, int dim1>
+yt::YTensor<T, dim>& binary_(int op, yt::YTensor<T, dim>& a, const yt::YTensor<T, dim1>& b) {
+  static_assert(dim1 <= dim, "in-place operator: the right operand may not have more dims than the left");
+  std::vector<int64_t> bs(dim, 0);
+  for (int d = 0; d < dim1; ++d) {
+    const int ad = dim - dim1 + d;
+    if (b.shape(d) != a.shape(ad) && b.shape(d) != 1)
+      throw std::runtime_error("broadcast: shapes do not match");  // std::runtime_error, src/kernel/broadcast.inl:133
+    bs[ad] = b.shape(d) == 1 ? 0 : b.stride_(d);
+  }
+  const auto shape = detail::widen(a.shape());
+  const auto as = detail::strides_of(a);
+  check(ytcuda_binary(op, dtype_of<T>(), dtype_of<T>(), dtype_of<T>(), a.data(), b.data(), a.data(), dim, shape.data(),
+                      as.data(), bs.data(), as.data(), nullptr));
+  return a;
+}
+
+// YTensorBase::copy_ / cast between device tensors (src/ytensor_base.inl:257-430): strided, with the reference's
+// own float -> bfloat16 / float16 rounding.
+template <typename U, typename T, int dim>
+yt::YTensor<U, dim>& copy_(yt::YTensor<U, dim>& dst, const yt::YTensor<T, dim>& src) {
+  if (dst.shape() != src.shape()) throw std::invalid_argument("copy_: shapes do not match");
+  const auto shape = detail::widen(src.shape());
+  const auto xs = detail::strides_of(src), ys = detail::strides_of(dst);
+  check(ytcuda_cast(dtype_of<T>(), dtype_of<U>(), src.data(), dst.data(), dim, shape.data(), xs.data(), ys.data(),
+                    nullptr));
+  return dst;
+}
+template <typename U, typename T, int dim>
+yt::YTensor<U, dim> cast(const yt::YTensor<T, dim>& x) {
+  auto y = empty_device<U, dim>(x.shape());
+  return copy_(y, x);
+}
+
+// scaledDotProductAttention on device tensors: query [b, kv_heads, groups, lq, d] with key / value either
+// [b, kv_heads, groups (stride 0), lk, d] as example/qwen3/src/qwen3.cpp:252-264 builds them, or any equal-rank form
+// whose leading dims are then all "heads". mask_kind as in ytcuda_flash_attn_fwd; mask / bias device pointers.
+template <typename T, int dim>
+yt::YTensor<T, dim> sdpa(const yt::YTensor<T, dim>& q, const yt::YTensor<T, dim>& k, const yt::YTensor<T, dim>& v,
+                         T scale, int mask_kind, int causal_offset, const uint8_t* mask_dev, const float* bias_dev) {
+  static_assert(dim >= 2, "attention needs [..., len, dim] operands");
+  const int lq = q.shape(-2), d = q.shape(-1), lk = k.shape(-2), dv = v.shape(-1);
+  std::vector<int> oshape = q.shape();
+  oshape[dim - 1] = dv;
+  auto out = empty_device<T, dim>(oshape);
+  int b = 1, kvh = 1, g = 1;
+  int64_t qs[3], ks[3], vs[3], os[3];
+  bool gqa = false;
+  if constexpr (dim == 5) gqa = k.stride_(2) == 0 && v.stride_(2) == 0 && q.isContiguous() && k.stride_(4) == 1 && v.stride_(4) == 1;
+  if (gqa) {
+    if constexpr (dim == 5) {
+      b = q.shape(0); kvh = q.shape(1); g = q.shape(2);
+      qs[0] = q.stride_(0); qs[1] = q.stride_(2); qs[2] = q.stride_(3);
+      ks[0] = k.stride_(0); ks[1] = k.stride_(1); ks[2] = k.stride_(3);
+      vs[0] = v.stride_(0); vs[1] = v.stride_(1); vs[2] = v.stride_(3);
+      os[0] = out.stride_(0); os[1] = out.stride_(2); os[2] = out.stride_(3);
+      check(ytcuda_flash_attn_fwd(dtype_of<T>(), q.data(), k.data(), v.data(), out.data(), b, kvh, g, lq, lk, d, dv,
+                                  static_cast<float>(scale), qs, ks, vs, os, mask_kind, causal_offset, mask_dev, lk,
+                                  bias_dev, lk, 1, nullptr));
+    }
+    return out;
+  }
+  auto qc = contiguous(q), kc = contiguous(k), vc = contiguous(v);
+  for (int i = 0; i < dim - 2; ++i) kvh *= q.shape(i);
+  qs[0] = 0; qs[1] = static_cast<int64_t>(lq) * d; qs[2] = d;
+  ks[0] = 0; ks[1] = static_cast<int64_t>(lk) * d; ks[2] = d;
+  vs[0] = 0; vs[1] = static_cast<int64_t>(lk) * dv; vs[2] = dv;
+  os[0] = 0; os[1] = static_cast<int64_t>(lq) * dv; os[2] = dv;
+  check(ytcuda_flash_attn_fwd(dtype_of<T>(), qc.data(), kc.data(), vc.data(), out.data(), b, kvh, g, lq, lk, d, dv,
+                              static_cast<float>(scale), qs, ks, vs, os, mask_kind, causal_offset, mask_dev, lk,
+                              bias_dev, lk, 1, nullptr));
+  return out;
+}
+}  // namespace dev
+
+template <typename T, int dim>
+yt::YTensor<T, dim> to_host(const yt::YTensor<T, dim>& dev_t) {
+  auto c = dev::contiguous(dev_t);
+  yt::YTensor<T, dim> h(c.shape());
+  check(ytcuda_memcpy_d2h(h.data(), c.data(), c.size() * sizeof(T), nullptr));
+  check(ytcuda_stream_sync(nullptr));
+  return h;
+}
+
+// ------------------------------------------------------------------ the seam: what YTensor's own entry points call
+// With -DYT_USE_CUDA=1 the reference's dispatch sites gain one branch each (matmul's switch on MatmulBackend, the
+// sdpaBackend tests of scaledDotProductAttention, the first lines of softmax / softmax_ / rmsNorm / rmsNorm_ /
+// copy_ and of the in-place operators); those branches are one-line calls into this namespace. Operators asked for
+// explicitly by a backend argument (MatmulBackend::CUDA, sdpaBackend::FLASH_CUDA) take host tensors through the device
+// and return host tensors, or stay on the device when the operands live there; the named functions and operators go
+// to the device exactly when their tensor is device-resident. Nothing here computes on the CPU.
+namespace seam {
+template <typename T>
+inline constexpr bool device_type_v =
+    std::is_same_v<T, float> || std::is_same_v<T, yt::bfloat16> || std::is_same_v<T, yt::float16>;
+
+template <typename T, int dim0, int dim1>
+auto matmul(const yt::YTensor<T, dim0>& a, const yt::YTensor<T, dim1>& b) {
+  constexpr int odim = dim0 > dim1 ? (dim0 > 2 ? dim0 : 2) : (dim1 > 2 ? dim1 : 2);
+  if constexpr (device_type_v<T> && dim0 >= 2 && dim1 >= 2 && (dim1 == 2 || dim0 == dim1)) {
+    const bool da = on_device(a), db = on_device(b);
+    if (da != db) throw std::invalid_argument("matmul: one operand is device-resident and the other is not");
+    if (da) return yt::YTensor<T, odim>(dev::matmul(a, b));
+    return yt::YTensor<T, odim>(yt::cuda::matmul(a, b));
+  } else {
+    throw std::invalid_argument("MatmulBackend::CUDA: float / bfloat16 / float16 operands of rank >= 2, the right one "
+                                "2-D or of the left one's rank (no CPU fallback)");
+    return yt::YTensor<T, odim>();
+  }
+}
+
+// bool mask (or none) and optional bias; any rank >= 2
+template <typename T, int dim>
+yt::YTensor<T, dim> sdpa(yt::YTensor<T, dim>& q, yt::YTensor<T, dim>& k, yt::YTensor<T, dim>& v, T scale, int mask_kind,
+                         int causal_offset, const yt::YTensor<bool, 2>* mask, const yt::YTensor<T, 2>* bias) {
+  if constexpr (!device_type_v<T> || dim < 2) {
+    throw std::invalid_argument("sdpaBackend::FLASH_CUDA: float / bfloat16 / float16 tensors of rank >= 2");
+    return yt::YTensor<T, dim>();
+  } else {
+    const int lq = q.shape(-2), lk = k.shape(-2);
+    if (mask && (mask->shape(0) != lq || mask->shape(1) != lk))
+      throw std::invalid_argument("Mask shape must match the last two dimensions of the score tensor.");
+    if (bias && (bias->shape(0) != lq || bias->shape(1) != lk))
+      throw std::invalid_argument("Bias shape must match the last two dimensions of the score tensor.");
+    const bool dq = on_device(q);
+    if (dq != on_device(k) || dq != on_device(v))
+      throw std::invalid_argument("scaledDotProductAttention: operands must all be host- or all device-resident");
+    // mask and bias are small [lq, lk] host tensors in the reference's API: upload them for the call
+    std::vector<uint8_t> m8;
+    DeviceBuffer dmask(mask ? static_cast<size_t>(lq) * lk : 16);
+    if (mask) {
+      m8.resize(static_cast<size_t>(lq) * lk);
+      for (int r = 0; r < lq; ++r)
+        for (int c = 0; c < lk; ++c) m8[static_cast<size_t>(r) * lk + c] = mask->at(r, c) ? 1 : 0;
+      dmask.upload(m8.data());
+    }
+    std::vector<float> bf;
+    DeviceBuffer dbias(bias ? static_cast<size_t>(lq) * lk * sizeof(float) : 16);
+    if (bias) {
+      bf.resize(static_cast<size_t>(lq) * lk);
+      for (int r = 0; r < lq; ++r)
+        for (int c = 0; c < lk; ++c) bf[static_cast<size_t>(r) * lk + c] = static_cast<float>(bias->at(r, c));
+      dbias.upload(bf.data());
+    }
+    const uint8_t* mp = mask ? static_cast<const uint8_t*>(dmask.get()) : nullptr;
+    const float* bp = bias ? static_cast<const float*>(dbias.get()) : nullptr;
+    if (dq) {
+      auto out = dev::sdpa(q, k, v, scale, mask_kind, causal_offset, mp, bp);
+      check(ytcuda_stream_sync(nullptr));  // dmask / dbias leave scope
+      return out;
+    }
+    // host operands: one upload each (a zero-stride group repeat of K / V is uploaded once, not g times)
+    auto qd = to_device(q);
+    yt::YTensor<T, dim> kd, vd;
+    bool repeated = false;
+    if constexpr (dim == 5) repeated = k.stride_(2) == 0 && v.stride_(2) == 0 && k.shape(2) > 1;
+    if (repeated) {
+      if constexpr (dim == 5) {
+        auto k1 = to_device(yt::YTensor<T, 5>(k.slice(2, 0, 1)));
+        auto v1 = to_device(yt::YTensor<T, 5>(v.slice(2, 0, 1)));
+        kd = k1.repeat(1, 1, k.shape(2), 1, 1);
+        vd = v1.repeat(1, 1, v.shape(2), 1, 1);
+      }
+    } else {
+      kd = to_device(k);
+      vd = to_device(v);
+    }
+    return to_host(dev::sdpa(qd, kd, vd, scale, mask_kind, causal_offset, mp, bp));
+  }
+}
+
+// a predicate mask: Causal is evaluated on the device; any other callable (r, c) -> bool is materialised once on the
+// host into a bool tensor (device code cannot call a host lambda)
+template <typename T, int dim, typename MaskFunc>
+yt::YTensor<T, dim> sdpa_pred(yt::YTensor<T, dim>& q, yt::YTensor<T, dim>& k, yt::YTensor<T, dim>& v, T scale,
+                              MaskFunc&& pred, const yt::YTensor<T, 2>* bias) {
+  if constexpr (std::is_same_v<std::decay_t<MaskFunc>, Causal>) {
+    return sdpa<T, dim>(q, k, v, scale, 1, pred.offset, nullptr, bias);
+  } else {
+    const int lq = q.shape(-2), lk = k.shape(-2);
+    yt::YTensor<bool, 2> m(lq, lk);
+    for (int r = 0; r < lq; ++r)
+      for (int c = 0; c < lk; ++c) m.at(r, c) = static_cast<bool>(pred(r, c));
+    return sdpa<T, dim>(q, k, v, scale, 2, 0, &m, bias);
+  }
+}
+
+// in-place operator on a device-resident left operand; false = not ours (host tensor or a type the device has not)
+template <typename T, int dim, int dim1>
+bool inplace_op(const char* op, yt::YTensor<T, dim>& a, const yt::YTensor<T, dim1>& b) {
+  if constexpr (device_type_v<T> && dim1 <= dim) {
+    if (!on_device(a)) return false;
+    const int code = op[0] == '+' ? 0 : op[0] == '-' ? 1 : op[0] == '*' ? 2 : op[0] == '/' ? 3 : -1;
+    if (code < 0 || op[1] != 0) throw std::invalid_argument(std::string("operator ") + op + "= has no device kernel");
+    if (!on_device(b)) throw std::invalid_argument("in-place operator: the right operand is not device-resident");
+    dev::binary_(code, a, b);
+    return true;
+  } else {
+    return false;
+  }
+}
+
+// YTensor::copy_(src) when either side is device-resident. dst and src on the device: strided copy with dtype
+// conversion (float / bfloat16 / float16). One side on the host: a plain upload or download of equal element type and
+// shape (a strided side is staged through a contiguous tensor). Both on the host: false, the reference's own copy_ runs.
+template <typename T, int dim>
+bool copy_any(yt::YTensor<T, dim>& dst, const yt::YTensorBase& src) {
+  const bool dd = on_device(dst);
+  const bool sd = src.size() > 0 && ytcuda_pointer_is_device(src.template data<char>()) != 0;
+  if (!dd && !sd) return false;
+  if (src.ndim() != dim || src.shape() != dst.shape()) throw std::invalid_argument("copy_: shapes do not match");
+  const std::string st = src.dtype();
+  auto as = [&](auto tag) {
+    using S = decltype(tag);
+    return yt::YTensor<S, dim>(src);
+  };
+  if (dd && sd) {
+    if (st == yt::types::getTypeName<float>()) dev::copy_(dst, as(float{}));
+    else if (st == yt::types::getTypeName<yt::bfloat16>()) dev::copy_(dst, as(yt::bfloat16{}));
+    else if (st == yt::types::getTypeName<yt::float16>()) dev::copy_(dst, as(yt::float16{}));
+    else throw std::invalid_argument("copy_: the device converts between float32, bfloat16 and float16 only");
+    return true;
+  }
+  if (st != yt::types::getTypeName<T>())
+    throw std::invalid_argument("copy_: a copy between host and device keeps the element type (convert on the device)");
+  yt::YTensor<T, dim> s(src);
+  if (dd) {  // host -> device
+    auto staged = to_device(s);
+    if (dst.isContiguous()) check(ytcuda_memcpy_d2d(dst.data(), staged.data(), staged.size() * sizeof(T), nullptr));
+    else dev::copy_(dst, staged);
+    check(ytcuda_stream_sync(nullptr));
+  } else {   // device -> host
+    auto h = to_host(s);
+    if (dst.isContiguous()) std::memcpy(dst.data(), h.data(), h.size() * sizeof(T));
+    else dst.copy_(h);
+  }
+  return true;
+}
+}  // namespace seam
 
 }  // namespace yt::cuda

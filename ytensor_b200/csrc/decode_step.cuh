@@ -46,7 +46,6 @@ constexpr int DS_MAX_G = 4;        // query heads per kv head
 constexpr int DS_MAX_TP = 8;       // tensor-parallel ranks (one GPU each, peers reached by NVLink loads / stores)
 // attention scratch of a CTA: q of the group, and per warp (m, l, o[128]) for every head of the group
 constexpr int DS_ATT_FLOATS = DS_MAX_G * 128 + 2 * DS_WARPS * DS_MAX_G + DS_WARPS * DS_MAX_G * 128;  // for G = DS_MAX_G
-constexpr long long DS_WAIT_CYCLES = 2000000000ll;
 
 struct DsLayer {
   const uint16_t *qkv, *o, *gate_up, *down;
@@ -84,6 +83,7 @@ struct DecodeStepParams {
   unsigned int* flags[DS_MAX_TP];
   unsigned int* go;
   unsigned int ar_base;  // exchanges completed before this launch
+  long long wait_cycles;  // budget of every bounded wait (ytcuda_set_wait_limit)
 };
 
 __device__ __forceinline__ float ds_ldcg(const float* p) { return __ldcg(p); }
@@ -102,7 +102,7 @@ __device__ __forceinline__ bool ds_grid_sync(const DecodeStepParams& p, unsigned
     while (true) {
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sync) : "memory");
       if (v >= epoch) break;  // also true once any CTA has set the give-up bit
-      if (clock64() - t0 > DS_WAIT_CYCLES) {
+      if (clock64() - t0 > p.wait_cycles) {
         atomicExch(p.status, YTC_TIMEOUT);
         atomicOr(p.sync, 0x80000000u);  // releases every waiting CTA at once
         v = 0x80000000u;
@@ -130,7 +130,7 @@ __device__ __forceinline__ bool ds_cross_sync(const DecodeStepParams& p, unsigne
       while (true) {  // every CTA of this GPU has written its part of the mailbox
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sync) : "memory");
         if (v >= epoch) break;
-        if (clock64() - t0 > DS_WAIT_CYCLES) {
+        if (clock64() - t0 > p.wait_cycles) {
           v = 0x80000000u;
           break;
         }
@@ -146,7 +146,7 @@ __device__ __forceinline__ bool ds_cross_sync(const DecodeStepParams& p, unsigne
             unsigned int f;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(p.flags[p.tp_rank] + q) : "memory");
             if (f >= seq) break;
-            if (clock64() - t0 > DS_WAIT_CYCLES) {
+            if (clock64() - t0 > p.wait_cycles) {
               v = 0x80000000u;
               break;
             }
@@ -166,7 +166,7 @@ __device__ __forceinline__ bool ds_cross_sync(const DecodeStepParams& p, unsigne
         if (v >= seq) break;
         unsigned int c;
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(p.sync) : "memory");
-        if ((c & 0x80000000u) || clock64() - t0 > DS_WAIT_CYCLES) {
+        if ((c & 0x80000000u) || clock64() - t0 > p.wait_cycles) {
           atomicExch(p.status, YTC_TIMEOUT);
           atomicOr(p.sync, 0x80000000u);
           ok = 0;

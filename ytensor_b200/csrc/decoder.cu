@@ -467,7 +467,7 @@ static int gemm_pieces(Qwen3Model* m, const uint16_t* W, int64_t M, int N, int K
     if (blocks % d == 0 && tiles * d <= sm_count()) splits = d;
   const int kc = K / splits;
   const size_t part_elems = static_cast<size_t>(2) * splits * M * N;
-  float* part = static_cast<float*>(device_workspace(part_elems * sizeof(float)));
+  float* part = static_cast<float*>(device_workspace(part_elems * sizeof(float), st));
   if (!part) {
     set_last_error("linear: cannot allocate %zu bytes for split-k partial sums", part_elems * sizeof(float));
     return YTC_CUDA_ERROR;
@@ -502,20 +502,12 @@ static int linear_w16(Qwen3Model* m, const float* x, int64_t x_rs, const uint16_
     else if (Mi <= 4) SK_LAUNCH(4);
     else if (Mi <= 8) SK_LAUNCH(8);
     else if (Mi <= 16) {
-      static bool attr = false;
-      if (!attr) {
-        YTC_CUDA(cudaFuncSetAttribute(skinny_linear_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      16 * SK_KC * 4));
-        attr = true;
-      }
+      const int sa = ensure_dynamic_smem(reinterpret_cast<const void*>(skinny_linear_kernel<16>), 16 * SK_KC * 4);
+      if (sa != YTC_OK) return sa;
       SK_LAUNCH(16);
     } else {
-      static bool attr = false;
-      if (!attr) {
-        YTC_CUDA(cudaFuncSetAttribute(skinny_linear_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      32 * SK_KC * 4));
-        attr = true;
-      }
+      const int sa = ensure_dynamic_smem(reinterpret_cast<const void*>(skinny_linear_kernel<32>), 32 * SK_KC * 4);
+      if (sa != YTC_OK) return sa;
       SK_LAUNCH(32);
     }
 #undef SK_LAUNCH
@@ -689,9 +681,42 @@ void* ytcuda_qwen3_create(int hidden, int layers, int vocab, int inter, int head
   return m;
 }
 
+// Tear-down of a tensor-parallel model is three steps: (1) every rank waits for its own kernels and closes the
+// peers' exchange buffers (ytcuda_qwen3_tp_disconnect), (2) the caller runs a barrier over the group, (3) every rank
+// destroys its model, which frees the buffer it exported. Freeing an exported buffer while a peer still has it open,
+// or while a slower peer's last step kernel may still read its mailbox, is undefined behaviour.
+int ytcuda_qwen3_tp_disconnect(void* handle) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m, "ytcuda_qwen3_tp_disconnect: null handle");
+  YTC_CUDA(cudaDeviceSynchronize());
+  for (char*& peer : m->tp_peer)
+    if (peer) {
+      cudaIpcCloseMemHandle(peer);
+      peer = nullptr;
+    }
+  m->tp_ready = false;
+  return YTC_OK;
+}
+
+// After a step kernel gave up on a peer (YTC_TIMEOUT) the ranks' exchange counters disagree. Recovery: every rank
+// waits for its own kernels, the caller runs a barrier over the group (no kernel anywhere can write a flag any
+// more), every rank calls this, and a second barrier follows before the next forward. The arrival words and the
+// exchange counter start again from zero; the KV caches are reset as by ytcuda_qwen3_reset.
+int ytcuda_qwen3_tp_resync(void* handle) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m, "ytcuda_qwen3_tp_resync: null handle");
+  YTC_CUDA(cudaDeviceSynchronize());
+  if (m->tp_comm) YTC_CUDA(cudaMemset(m->tp_comm + tp_flags_offset(m->hidden), 0, 256));
+  m->ar_seq = 0;
+  m->cur_len = 0;
+  m->total_written = 0;
+  return YTC_OK;
+}
+
 void ytcuda_qwen3_destroy(void* handle) {
   auto* m = static_cast<Qwen3Model*>(handle);
   if (!m) return;
+  cudaDeviceSynchronize();
   for (char* peer : m->tp_peer)
     if (peer) cudaIpcCloseMemHandle(peer);
   for (void* p : m->owned) cudaFree(p);
@@ -904,6 +929,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   p.cos_t = m->cos_t; p.sin_t = m->sin_t; p.k_cache = m->k_cache; p.v_cache = m->v_cache;
   p.cache_layer = static_cast<size_t>(B) * m->l_kv_heads * m->max_pos * D;
   p.tp_rank = m->tp_rank; p.tp_world = m->tp_world; p.ar_base = m->ar_seq;
+  p.wait_cycles = wait_cycle_limit();
   if (m->tp_world > 1) {
     const size_t flags_at = tp_flags_offset(m->hidden);
     for (int r = 0; r < m->tp_world; ++r) {
@@ -947,17 +973,11 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   else DS_PICK(32);
 #undef DS_PICK_G
 #undef DS_PICK
+  // the limit belongs to the (device, kernel) pair, not to the model: several models (other paths, other sizes)
+  // share a kernel, and a smaller request must not lower what another model's launches need
   {
-    // the limit belongs to the kernel, not to the model: several models (other paths, other sizes) share a kernel,
-    // and a smaller request must not lower what another model's launches need
-    static std::mutex mu;
-    static std::unordered_map<const void*, int> limit;
-    std::lock_guard<std::mutex> lock(mu);
-    int& cur = limit[fn];
-    if (cur < smem) {
-      YTC_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      cur = smem;
-    }
+    const int sa = ensure_dynamic_smem(fn, smem);
+    if (sa != YTC_OK) return sa;
   }
   YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(DS_THREADS), args, smem, st));
   count_launch();

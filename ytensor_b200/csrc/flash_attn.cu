@@ -1451,20 +1451,12 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
     p.n_items = static_cast<int>(items);
     const dim3 grid(static_cast<unsigned>(p.n_items < sm_count() ? p.n_items : sm_count()));
     if (head_dim == 128) {
-      static bool attr = false;
-      if (!attr) {
-        YTC_CUDA(cudaFuncSetAttribute(flash_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      FaSmem<128>::DYN_BYTES));
-        attr = true;
-      }
+      const int sa = ensure_dynamic_smem(reinterpret_cast<const void*>(flash_tc_kernel<128>), FaSmem<128>::DYN_BYTES);
+      if (sa != YTC_OK) return sa;
       flash_tc_kernel<128><<<grid, FA_THREADS, FaSmem<128>::DYN_BYTES, st>>>(tmQ, tmK, tmV, p);
     } else {
-      static bool attr = false;
-      if (!attr) {
-        YTC_CUDA(cudaFuncSetAttribute(flash_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      FaSmem<64>::DYN_BYTES));
-        attr = true;
-      }
+      const int sa = ensure_dynamic_smem(reinterpret_cast<const void*>(flash_tc_kernel<64>), FaSmem<64>::DYN_BYTES);
+      if (sa != YTC_OK) return sa;
       flash_tc_kernel<64><<<grid, FA_THREADS, FaSmem<64>::DYN_BYTES, st>>>(tmQ, tmK, tmV, p);
     }
     count_launch();
@@ -1505,7 +1497,7 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
     dp.keys_per_split = (kv_len + splits - 1) / splits;
     dp.splits = (kv_len + dp.keys_per_split - 1) / dp.keys_per_split;
     const size_t need = static_cast<size_t>(bk) * dp.splits * groups * q_len * (2 + value_dim) * sizeof(float);
-    dp.part = static_cast<float*>(device_workspace(need));
+    dp.part = static_cast<float*>(device_workspace(need, st));
     if (!dp.part) {
       set_last_error("ytcuda_flash_attn_fwd: cannot allocate %zu bytes of scratch", need);
       return YTC_CUDA_ERROR;
@@ -1529,11 +1521,8 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
       vec_ok && head_dim % 4 == 0 && value_dim % 4 == 0 && q_strides[0] % 4 == 0 && q_strides[1] % 4 == 0 &&
       q_strides[2] % 4 == 0 && (reinterpret_cast<uint64_t>(Q) & 15) == 0) {
     dim3 grid((q_len + T64_BM - 1) / T64_BM, heads, batch);
-    static bool attr64 = false;
-    if (!attr64) {
-      YTC_CUDA(cudaFuncSetAttribute(attn_tile64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T64_SMEM));
-      attr64 = true;
-    }
+    const int sa = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_tile64_kernel), T64_SMEM);
+    if (sa != YTC_OK) return sa;
     attn_tile64_kernel<<<grid, 256, T64_SMEM, st>>>(p);
     count_launch();
     YTC_CUDA(cudaGetLastError());
@@ -1542,11 +1531,8 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
   if (head_dim <= TL_D && value_dim <= TL_D && heads <= 65535 && batch <= 65535) {
     dim3 grid((q_len + TL_BM - 1) / TL_BM, heads, batch);
     constexpr int TL_SMEM = ((TL_BM + 2 * TL_BN) * (TL_D + TL_PAD) + TL_BM * (TL_BN + 1)) * 4;
-    static bool attr = false;
-    if (!attr) {
-      YTC_CUDA(cudaFuncSetAttribute(attn_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM));
-      attr = true;
-    }
+    const int sa = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_tile_kernel), TL_SMEM);
+    if (sa != YTC_OK) return sa;
     attn_tile_kernel<<<grid, 128, TL_SMEM, st>>>(p);
     count_launch();
     YTC_CUDA(cudaGetLastError());

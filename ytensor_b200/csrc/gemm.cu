@@ -794,10 +794,9 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
     p.total_tiles = static_cast<int>(static_cast<int64_t>(p.tiles_m) * p.tiles_n * batch);
     int clusters = sm_count() / 2;
     if (clusters > p.total_tiles) clusters = p.total_tiles;
-    static bool attr2 = false;
-    if (!attr2) {
-      YTC_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc2Smem::DYN_BYTES));
-      attr2 = true;
+    {
+      const int s = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc2_kernel), Tc2Smem::DYN_BYTES);
+      if (s != YTC_OK) return s;
     }
     gemm_tc2_kernel<<<clusters * 2, TC_THREADS, Tc2Smem::DYN_BYTES, st>>>(tmA, tmB, p);
     count_launch();
@@ -806,20 +805,12 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
   }
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   if (BN == 256) {
-    static bool attr = false;
-    if (!attr) {
-      YTC_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    TcSmem<256>::DYN_BYTES));
-      attr = true;
-    }
+    const int s = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc_kernel<256>), TcSmem<256>::DYN_BYTES);
+    if (s != YTC_OK) return s;
     gemm_tc_kernel<256><<<grid, TC_THREADS, TcSmem<256>::DYN_BYTES, st>>>(tmA, tmB, p);
   } else {
-    static bool attr = false;
-    if (!attr) {
-      YTC_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    TcSmem<128>::DYN_BYTES));
-      attr = true;
-    }
+    const int s = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc_kernel<128>), TcSmem<128>::DYN_BYTES);
+    if (s != YTC_OK) return s;
     gemm_tc_kernel<128><<<grid, TC_THREADS, TcSmem<128>::DYN_BYTES, st>>>(tmA, tmB, p);
   }
   count_launch();
@@ -953,7 +944,7 @@ static int launch_f32_split(const float* A, const float* B, float* C, int m, int
   if (per_item * chunk > budget) chunk = budget / per_item > 0 ? budget / per_item : 1;
   const size_t a_bytes = (static_cast<size_t>(2) * a_per * chunk + 255) / 256 * 256;
   const size_t b_bytes = static_cast<size_t>(2) * b_per * (b_shared ? 1 : chunk);
-  char* ws = static_cast<char*>(device_workspace(a_bytes + b_bytes));
+  char* ws = static_cast<char*>(device_workspace(a_bytes + b_bytes, st));
   if (!ws) {
     set_last_error("ytcuda_gemm: could not allocate %zu bytes for the bf16 form of an fp32 product", a_bytes + b_bytes);
     return YTC_CUDA_ERROR;
@@ -978,6 +969,7 @@ static int launch_f32_split(const float* A, const float* B, float* C, int m, int
                             /*b_mn=*/1, n, rsc, csc, nb, a_per, b_shared ? 0 : b_per, bsc, st);
     if (s != YTC_OK) return s;
   }
+  device_workspace_release(st);  // large expanded operands do not stay resident
   return YTC_OK;
 }
 

@@ -47,20 +47,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #define YTK_WAIT_CYCLES (4000000000ll)
 #endif
 
-// Waits for the phase with the given parity. `abort_word` lives in shared
+// Waits for the phase with the given parity, for at most `limit` cycles. `abort_word` lives in shared
 // memory: once any role has timed out every later wait gives up at once.
 // Returns false on give-up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_word,
+                                                long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_word) return false;
-    if (clock64() - t0 > YTK_WAIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       *abort_word = 1;
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+  return mbar_wait_limit(bar, parity, abort_word, YTK_WAIT_CYCLES);
 }
 
 // ---------------------------------------------------------------- TMA

@@ -16,6 +16,7 @@
 // (src/ytensor_math.inl:414-692).
 #include <math_constants.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "ytc_common.cuh"
@@ -805,7 +806,7 @@ static int run_nd(int op, int dt_in, int dt_out, int dt_w, const void* x, void* 
     }
     sp.contiguous = contig ? 1 : 0;
     const size_t need = static_cast<size_t>(lines) * chunks;
-    void* ws = scratch ? scratch : device_workspace(need * 8);
+    void* ws = scratch ? scratch : device_workspace(need * 8, st);
     if (!ws) {
       set_last_error("%s: cannot allocate %zu bytes of scratch", who, need * 8);
       return YTC_CUDA_ERROR;
@@ -843,6 +844,8 @@ static int run_nd(int op, int dt_in, int dt_out, int dt_w, const void* x, void* 
 // workspace: 8192 (value, index) pairs. Every GPU that loads the library carries these 64 KiB until exit.
 constexpr size_t NOALLOC_SCRATCH_BYTES = 64 * 1024;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+// Bytes of the array a call may use (ytcuda_reduce_noalloc_set_limit); never more than the array holds.
+static std::atomic<size_t> g_noalloc_limit{NOALLOC_SCRATCH_BYTES};
 
 // The array's name is only a host-side handle here: the device address has to be asked for, once per device,
 // while that device is current.
@@ -894,7 +897,14 @@ int ytcuda_reduce_noalloc(int op, int dt_in, int dt_out, const void* x, void* y,
   NdArgs a{shape, xstrides, ys, ndim, axes, naxes};
   const int rop = op == 0 ? OP_SUM : op == 1 ? OP_MEAN : OP_MAX;
   return run_nd(rop, dt_in, dt_out, YTC_F32, x, y, nullptr, nullptr, index, a, 0.f, true,
-                static_cast<cudaStream_t>(stream), "ytcuda_reduce_noalloc", scratch, NOALLOC_SCRATCH_BYTES);
+                static_cast<cudaStream_t>(stream), "ytcuda_reduce_noalloc", scratch, g_noalloc_limit.load());
+}
+
+int ytcuda_reduce_noalloc_set_limit(uint64_t bytes) {
+  YTC_REQUIRE(bytes <= NOALLOC_SCRATCH_BYTES, "ytcuda_reduce_noalloc_set_limit: %llu bytes asked for, the array holds %zu",
+              static_cast<unsigned long long>(bytes), NOALLOC_SCRATCH_BYTES);
+  g_noalloc_limit.store(bytes == 0 ? NOALLOC_SCRATCH_BYTES : static_cast<size_t>(bytes));
+  return YTC_OK;
 }
 
 int ytcuda_softmax(int dt_in, int dt_out, const void* x, void* y, const int64_t* shape, const int64_t* xstrides,

@@ -9,11 +9,13 @@
 #include <mutex>
 
 #include "ytc_common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace ytk {
 
 static thread_local char g_err[512] = {0};
 static std::atomic<uint64_t> g_launches{0};
+static std::atomic<uint64_t> g_h2d{0}, g_d2h{0};
 void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void set_last_error(const char* fmt, ...) {
@@ -75,26 +77,88 @@ int read_device_status(cudaStream_t st) {
   return h;
 }
 
-static void* g_ws[kMaxDev] = {nullptr};
-static size_t g_ws_cap[kMaxDev] = {0};
+// Scratch memory of the allocating entry points: one buffer per (device, stream), so that calls on different streams
+// never share scratch. Growing is stream-ordered (cudaFreeAsync / cudaMallocAsync on the caller's stream): work
+// already queued on the stream keeps the old buffer until it has run, and nothing synchronises the device.
+struct WsKey {
+  int dev;
+  cudaStream_t st;
+  bool operator==(const WsKey& o) const { return dev == o.dev && st == o.st; }
+};
+struct WsKeyHash {
+  size_t operator()(const WsKey& k) const {
+    return std::hash<uint64_t>()(reinterpret_cast<uint64_t>(k.st) * 31u + static_cast<uint64_t>(k.dev));
+  }
+};
+struct WsBuf {
+  void* ptr = nullptr;
+  size_t cap = 0;
+};
+static std::unordered_map<WsKey, WsBuf, WsKeyHash> g_ws;
+// Buffers above this size are handed back after the call that asked for them (device_workspace_release).
+static constexpr size_t kWsKeep = 256u << 20;
 
-void* device_workspace(size_t bytes) {
+void* device_workspace(size_t bytes, cudaStream_t st) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
   std::lock_guard<std::mutex> lk(g_mu);
-  if (g_ws_cap[dev] < bytes) {
-    if (g_ws[dev]) {
-      cudaDeviceSynchronize();
-      cudaFree(g_ws[dev]);
-      g_ws[dev] = nullptr;
-      g_ws_cap[dev] = 0;
+  WsBuf& b = g_ws[WsKey{dev, st}];
+  if (b.cap < bytes) {
+    if (b.ptr) {
+      cudaFreeAsync(b.ptr, st);
+      b.ptr = nullptr;
+      b.cap = 0;
     }
     size_t cap = bytes < (1u << 20) ? (1u << 20) : bytes;
-    if (cudaMalloc(&g_ws[dev], cap) != cudaSuccess) return nullptr;
-    g_ws_cap[dev] = cap;
+    if (cudaMallocAsync(&b.ptr, cap, st) != cudaSuccess) {
+      b.ptr = nullptr;
+      cudaGetLastError();
+      return nullptr;
+    }
+    b.cap = cap;
   }
-  return g_ws[dev];
+  return b.ptr;
 }
+
+void device_workspace_release(cudaStream_t st) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_ws.find(WsKey{dev, st});
+  if (it == g_ws.end() || it->second.cap <= kWsKeep) return;
+  cudaFreeAsync(it->second.ptr, st);  // stream-ordered: the kernels queued before this keep their scratch
+  g_ws.erase(it);
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to (device, kernel): a process that uses several GPUs has to
+// raise it on each of them, and a smaller request must never lower what another caller of the same kernel needs.
+struct FnKey {
+  int dev;
+  const void* fn;
+  bool operator==(const FnKey& o) const { return dev == o.dev && fn == o.fn; }
+};
+struct FnKeyHash {
+  size_t operator()(const FnKey& k) const {
+    return std::hash<uint64_t>()(reinterpret_cast<uint64_t>(k.fn) * 31u + static_cast<uint64_t>(k.dev));
+  }
+};
+static std::unordered_map<FnKey, int, FnKeyHash> g_smem_limit;
+
+int ensure_dynamic_smem(const void* fn, int bytes) {
+  int dev = 0;
+  YTC_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_mu);
+  int& cur = g_smem_limit[FnKey{dev, fn}];
+  if (cur < bytes) {
+    YTC_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    cur = bytes;
+  }
+  return YTC_OK;
+}
+
+// Cycle budget of the bounded device-side waits (mbarrier, grid and cross-GPU barriers), settable at run time.
+static std::atomic<long long> g_wait_cycles{2000000000ll};
+long long wait_cycle_limit() { return g_wait_cycles.load(std::memory_order_relaxed); }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -185,6 +249,26 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, c
   return YTC_OK;
 }
 
+// One CTA waits on an mbarrier that nothing ever arrives on, with the run-time cycle budget: the wait gives up,
+// the kernel raises the device status word and returns. This is the give-up path of every bounded wait of the
+// library (TMA / MMA / epilogue roles, grid and cross-GPU barriers) on its own, so that a test can watch it.
+__global__ void wait_probe_kernel(int* status, long long limit, long long* waited) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    const bool ok = mbar_wait_limit(&bar, 0u, &abort_word, limit);
+    if (waited) *waited = clock64() - t0;
+    if (!ok) atomicExch(status, YTC_TIMEOUT);
+  }
+}
+
 }  // namespace ytk
 
 using namespace ytk;
@@ -220,14 +304,31 @@ int ytcuda_host_free(void* hptr) {
 int ytcuda_memcpy_h2d(void* dst, const void* src, uint64_t bytes, void* stream) {
   if (bytes == 0) return YTC_OK;
   YTC_REQUIRE(dst && src, "ytcuda_memcpy_h2d: null pointer");
+  g_h2d.fetch_add(1, std::memory_order_relaxed);
   YTC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
   return YTC_OK;
 }
 int ytcuda_memcpy_d2h(void* dst, const void* src, uint64_t bytes, void* stream) {
   if (bytes == 0) return YTC_OK;
   YTC_REQUIRE(dst && src, "ytcuda_memcpy_d2h: null pointer");
+  g_d2h.fetch_add(1, std::memory_order_relaxed);
   YTC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   return YTC_OK;
+}
+int ytcuda_memcpy_d2d(void* dst, const void* src, uint64_t bytes, void* stream) {
+  if (bytes == 0) return YTC_OK;
+  YTC_REQUIRE(dst && src, "ytcuda_memcpy_d2d: null pointer");
+  YTC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return YTC_OK;
+}
+int ytcuda_pointer_is_device(const void* p) {
+  if (!p) return 0;
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return (a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged) ? 1 : 0;
 }
 int ytcuda_stream_sync(void* stream) {
   YTC_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
@@ -235,5 +336,24 @@ int ytcuda_stream_sync(void* stream) {
 }
 int ytcuda_device_status(void* stream) { return read_device_status(static_cast<cudaStream_t>(stream)); }
 uint64_t ytcuda_launch_count(void) { return g_launches.load(); }
+void ytcuda_copy_counts(uint64_t* h2d, uint64_t* d2h) {
+  if (h2d) *h2d = g_h2d.load();
+  if (d2h) *d2h = g_d2h.load();
+}
+int ytcuda_set_wait_limit(int64_t cycles) {
+  YTC_REQUIRE(cycles > 0, "ytcuda_set_wait_limit: the limit must be positive");
+  g_wait_cycles.store(cycles, std::memory_order_relaxed);
+  return YTC_OK;
+}
+int64_t ytcuda_get_wait_limit(void) { return g_wait_cycles.load(std::memory_order_relaxed); }
+int ytcuda_wait_probe(int64_t* waited_cycles_dev, void* stream) {
+  int* status = device_status_word();
+  YTC_REQUIRE(status != nullptr, "ytcuda_wait_probe: no device status word");
+  wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, wait_cycle_limit(),
+                                                                    reinterpret_cast<long long*>(waited_cycles_dev));
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
 
 }  // extern "C"

@@ -162,9 +162,15 @@ int* device_status_word();
 // Reads and clears the device status word (synchronises the stream).
 int read_device_status(cudaStream_t st);
 
-// Per-device scratch buffer owned by the library (grown on demand, never shrunk). One buffer per
-// device: calls that use it and overlap on different streams would race.
-void* device_workspace(size_t bytes);
+// Scratch buffer owned by the library, one per (device, stream), grown on demand with stream-ordered allocation:
+// calls on different streams never share scratch, calls on one stream are ordered by the stream itself.
+void* device_workspace(size_t bytes, cudaStream_t st);
+// Hands a buffer above 256 MiB back (stream-ordered) once the kernels using it have been queued; smaller ones stay.
+void device_workspace_release(cudaStream_t st);
+// Raises the dynamic shared-memory limit of `fn` on the current device to at least `bytes` (once per device).
+int ensure_dynamic_smem(const void* fn, int bytes);
+// Cycle budget of bounded device-side waits (ytcuda_set_wait_limit).
+long long wait_cycle_limit();
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup, so that
 // the library has no link-time dependency on libcuda.

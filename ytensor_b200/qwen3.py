@@ -198,6 +198,16 @@ class Qwen3ForCausalLM:
     def get_kv_cache_len(self) -> int:
         return self.L.ytcuda_qwen3_cache_len(self.h)
 
+    def decode_kernel_name(self) -> str:
+        """Name of the kernel(s) an automatic-path decode step (one new token per sequence) of this model runs:
+        the persistent step kernel up to 6 sequences (8 under tensor parallelism), its FFMA form below 5 sequences,
+        the operator path with tcgen05 linears beyond."""
+        limit = 6 if self.tp_world == 1 else 8
+        if self.batch <= limit:
+            return ("decode_step_kernel (FFMA linear phases)" if self.batch < 5 else
+                    "decode_step_kernel (mma.sync linear phases)")
+        return "gemm_tc_kernel (hi + lo planes, split-k pieces) + attn_decode_fast_kernel + fused glue kernels"
+
     def forward(self, ids):
         """ids int32 [batch, len] on the device -> fp32 logits [batch, this rank's vocab rows] of the last position."""
         torch = self.torch
@@ -226,8 +236,29 @@ class Qwen3ForCausalLM:
         tok = torch.stack(idxs, 1).gather(1, which.reshape(-1, 1).long()).reshape(-1)
         return tok.to(torch.int32), best.reshape(-1)
 
+    def check_status(self) -> None:
+        """Reads the device status word (synchronises the stream). A bounded wait that ran out - under tensor
+        parallelism: a peer that never arrived at an exchange - raises; the KV caches are then half written and the
+        group has to call recover() before the next forward."""
+        st = self.L.ytcuda_device_status(self.torch.cuda.current_stream().cuda_stream)
+        if st != _lib.OK:
+            raise _lib.YtCudaError(st, _lib.last_error() or "a bounded device-side wait ran out")
+
+    def recover(self) -> None:
+        """After check_status raised on some rank: EVERY rank of the group calls this. Kernels are waited for,
+        exchange counters and arrival words are zeroed between two barriers, the KV caches are reset."""
+        self.torch.cuda.synchronize()
+        if self.tp_world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.group)
+            check(self.L.ytcuda_qwen3_tp_resync(self.h))
+            dist.barrier(group=self.group)
+        else:
+            self.reset_kv_cache()
+
     def generate_greedy(self, prompt_ids, steps: int):
-        """prompt_ids int32 [batch, len] (device). Returns int32 [batch, steps] greedy tokens."""
+        """prompt_ids int32 [batch, len] (device). Returns int32 [batch, steps] greedy tokens. The device status is
+        checked once at the end, so that a step kernel that gave up on a peer raises instead of yielding tokens."""
         torch = self.torch
         out = torch.empty(self.batch, steps, dtype=torch.int32, device=prompt_ids.device)
         logits = self.forward(prompt_ids)
@@ -236,6 +267,7 @@ class Qwen3ForCausalLM:
             out[:, s] = tok
             if s + 1 < steps:
                 logits = self.forward(tok.reshape(self.batch, 1).contiguous())
+        self.check_status()
         return out
 
     def generate_topk(self, prompt_ids, steps: int, k: int = 20, seed: int = 42):
@@ -258,7 +290,17 @@ class Qwen3ForCausalLM:
         return out
 
     def close(self):
+        """Destroys the model. Under tensor parallelism every rank must call it (it runs a barrier over the group
+        between closing the peers' exchange buffers and freeing its own, as CUDA IPC requires)."""
         if self.h:
+            if self.tp_world > 1:
+                self.L.ytcuda_qwen3_tp_disconnect(self.h)
+                try:
+                    import torch.distributed as dist
+                    if dist.is_initialized():
+                        dist.barrier(group=self.group)
+                except Exception:  # the group is already gone (interpreter exit): nothing left to wait for
+                    pass
             self.L.ytcuda_qwen3_destroy(self.h)
             self.h = None
 
