@@ -296,7 +296,9 @@ int ytcuda_qwen3_cache_len(void* handle);
  * ytcuda_qwen3_tp_export),
  * 1 = one launch per operator as for longer inputs, 2 = the persistent kernel (batch <= 32) or YTC_UNSUPPORTED.
  * 3 = as 2, with the FFMA form of the kernel's linear phases even where the tensor-core form (five or more
- * sequences, hidden <= 1024) applies.
+ * sequences, hidden <= 1024) applies. Up to four sequences the kernel streams its weights through a ring of
+ * shared-memory slots filled by bulk async copies that run ahead of the phases; 4 = as 3 without that ring (every
+ * phase loads its weights after the barrier before it).
  * Both forms compute the operator sequence of Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has
  * no counterpart in the reference. */
 int ytcuda_qwen3_set_decode_path(void* handle, int path);

@@ -84,6 +84,7 @@ struct DecodeStepParams {
   unsigned int* go;
   unsigned int ar_base;  // exchanges completed before this launch
   long long wait_cycles;  // budget of every bounded wait (ytcuda_set_wait_limit)
+  int dw_xs_bytes, dw_nslot;  // decode_stream_kernel: bytes of its activation area, slots of its weight ring
 };
 
 __device__ __forceinline__ float ds_ldcg(const float* p) { return __ldcg(p); }

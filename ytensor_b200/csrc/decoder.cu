@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "decode_step.cuh"
+#include "decode_stream.cuh"
 #include "ytc_common.cuh"
 
 namespace ytk {
@@ -814,7 +815,7 @@ int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64) {
 int ytcuda_qwen3_set_decode_path(void* handle, int path) {
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m, "ytcuda_qwen3_set_decode_path: null handle");
-  YTC_REQUIRE(path >= 0 && path <= 3, "ytcuda_qwen3_set_decode_path: path must be 0, 1, 2 or 3");
+  YTC_REQUIRE(path >= 0 && path <= 4, "ytcuda_qwen3_set_decode_path: path must be 0 .. 4");
   m->decode_path = path;
   return YTC_OK;
 }
@@ -956,6 +957,37 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   YTC_CUDA(cudaMemsetAsync(m->ds_sync, 0, sync_words * sizeof(unsigned int), st));
   void* args[] = {&p};
   const void* fn = nullptr;
+  // Up to four sequences: the form of the kernel that streams its weights through a shared-memory ring
+  // (decode_stream.cuh), unless decode_path 4 asks for the older form or a size does not fit its chunks.
+  if (!mma && mt <= 4 && m->decode_path != 4 && m->layers <= DW_MAX_LAYERS) {
+    const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128);
+    int xs_bytes = mt * kmax * static_cast<int>(sizeof(float));
+    if (xs_bytes < att) xs_bytes = att;
+    xs_bytes = (xs_bytes + 127) / 128 * 128;
+    int nslot = (227 * 1024 - head - xs_bytes) / DW_CHUNK;
+    if (nslot > DW_MAX_SLOTS) nslot = DW_MAX_SLOTS;
+    const bool fits = nslot >= 2 && kmax * 2 <= DW_CHUNK && m->hidden * 4 <= DW_CHUNK && m->hidden % 8 == 0 &&
+                      m->l_inter % 8 == 0;
+    if (fits) {
+      p.dw_xs_bytes = xs_bytes;
+      p.dw_nslot = nslot;
+      const int dsmem = head + xs_bytes + nslot * DW_CHUNK;
+#define DW_PICK(MT)                                                                             \
+  fn = groups == 1   ? reinterpret_cast<const void*>(decode_stream_kernel<MT, 1>)               \
+       : groups == 2 ? reinterpret_cast<const void*>(decode_stream_kernel<MT, 2>)               \
+                     : reinterpret_cast<const void*>(decode_stream_kernel<MT, 4>)
+      if (mt == 1) DW_PICK(1);
+      else if (mt == 2) DW_PICK(2);
+      else DW_PICK(4);
+#undef DW_PICK
+      const int sa = ensure_dynamic_smem(fn, dsmem);
+      if (sa != YTC_OK) return sa;
+      YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(DS_THREADS), args, dsmem, st));
+      count_launch();
+      if (m->tp_world > 1) m->ar_seq += 2u * static_cast<unsigned int>(m->layers);
+      return YTC_OK;
+    }
+  }
 #define DS_PICK_G(MT, MMA)                                                                    \
   fn = groups == 1   ? reinterpret_cast<const void*>(decode_step_kernel<MT, 1, MMA>)          \
        : groups == 2 ? reinterpret_cast<const void*>(decode_step_kernel<MT, 2, MMA>)          \

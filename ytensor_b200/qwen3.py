@@ -192,7 +192,7 @@ class Qwen3ForCausalLM:
 
     def set_decode_path(self, path: int) -> None:
         """0: automatic, 1: one launch per operator, 2: the single persistent kernel per decode step (or an error),
-        3: as 2 with FFMA linear phases at every batch size."""
+        3: as 2 with FFMA linear phases at every batch size, 4: as 3 without the shared-memory weight ring."""
         check(self.L.ytcuda_qwen3_set_decode_path(self.h, int(path)))
 
     def get_kv_cache_len(self) -> int:
