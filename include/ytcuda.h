@@ -297,11 +297,17 @@ int ytcuda_qwen3_cache_len(void* handle);
  * 1 = one launch per operator as for longer inputs, 2 = the persistent kernel (batch <= 32) or YTC_UNSUPPORTED.
  * 3 = as 2, with the FFMA form of the kernel's linear phases even where the tensor-core form (five or more
  * sequences, hidden <= 1024) applies. Up to four sequences the kernel streams its weights through a ring of
- * shared-memory slots filled by bulk async copies that run ahead of the phases; 4 = as 3 without that ring (every
- * phase loads its weights after the barrier before it).
+ * shared-memory slots filled by bulk async copies that run ahead of the phases and, on one GPU, has no grid barriers:
+ * the activations that cross between phases are stored as {value, tag} pairs that the consumers poll; 4 = as 3 without
+ * the ring (every phase loads its weights after the barrier before it); 5 = the ring with grid barriers.
  * Both forms compute the operator sequence of Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has
  * no counterpart in the reference. */
 int ytcuda_qwen3_set_decode_path(void* handle, int path);
+/* Timeline of the single-kernel decode step, for tuning: with a device buffer of 2 * slots_per_cta int64 set, the first
+ * and the last CTA of every following step kernel write their SM's cycle counter at slot 4 * b + k of their half of
+ * the buffer: k = 0 on arriving at grid barrier number b, 1 on leaving it, 2 once the linear phase after it has staged
+ * its activations (streaming form only). NULL / 0 switches it off (the default). No counterpart in the reference. */
+int ytcuda_qwen3_set_trace(void* handle, int64_t* dev_buf, int slots_per_cta);
 /* Tensor-parallel decode steps without a host-side collective: every rank exports the CUDA IPC handle (64 bytes) of
  * its exchange buffer, the caller distributes the handles (one all-gather at start-up), and every rank imports its
  * peers'. From then on a forward of one token per sequence (batch <= 8) is ONE kernel per rank that all-reduces the

@@ -57,8 +57,9 @@ def test_small_model_logits_match_reference(Q, qwen3_golden, B):
 
 @pytest.mark.parametrize("B", [1, 2, 3, 5, 8, 13, 16, 32])
 def test_single_kernel_decode_step_matches_operator_path(Q, B):
-    """The persistent step kernel (path 2: weights streamed through a shared-memory ring up to four sequences,
-    tensor-core linear phases from five on; path 3: FFMA linear phases; path 4: the form without the weight ring)
+    """The persistent step kernel (path 2: up to four sequences without grid barriers, activations exchanged as
+    tagged pairs and weights streamed through a shared-memory ring, tensor-core linear phases from five sequences on;
+    path 3: FFMA linear phases; path 4: the form without the weight ring; path 5: the ring with grid barriers)
     and the one-launch-per-operator forward compute the same logits and leave the same KV cache behind: 70 steps
     after a 40-token prompt (the attention of the step kernel goes from 2 to 4 key chunks), every model fed the
     tokens of the operator path."""
@@ -69,7 +70,7 @@ def test_single_kernel_decode_step_matches_operator_path(Q, B):
     w = Q.random_weights(cfg, seed=11, std=0.05)
     ids = dev_ids(np.random.default_rng(B).integers(0, cfg.vocab_size, (B, 40)))
     ms = []
-    for path in (1, 2, 3, 4):
+    for path in (1, 2, 3, 4, 5):
         m = Q.Qwen3ForCausalLM(cfg, batch=B)
         m.load_weights(w)
         m.set_decode_path(path)

@@ -65,6 +65,7 @@ SIGNATURES = {
     "ytcuda_qwen3_reset": (_i, [_vp]),
     "ytcuda_qwen3_cache_len": (_i, [_vp]),
     "ytcuda_qwen3_set_decode_path": (_i, [_vp, _i]),
+    "ytcuda_qwen3_set_trace": (_i, [_vp, _vp, _i]),
     "ytcuda_qwen3_tp_export": (_i, [_vp, _vp]),
     "ytcuda_qwen3_tp_import": (_i, [_vp, _i, _vp]),
     "ytcuda_qwen3_tp_disconnect": (_i, [_vp]),

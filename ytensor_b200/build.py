@@ -25,6 +25,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
     "-I", str(REPO_DIR / "include"),
+    *os.environ.get("YTK_NVCC_EXTRA", "").split(),
 ]
 
 

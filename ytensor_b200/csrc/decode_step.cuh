@@ -85,16 +85,33 @@ struct DecodeStepParams {
   unsigned int ar_base;  // exchanges completed before this launch
   long long wait_cycles;  // budget of every bounded wait (ytcuda_set_wait_limit)
   int dw_xs_bytes, dw_nslot;  // decode_stream_kernel: bytes of its activation area, slots of its weight ring
+  // Optional timeline (ytcuda_qwen3_set_trace): the first and the last CTA write their SM's cycle counter into
+  // trace[cta ? trace_cap : 0 + 4 * barrier + k], k = 0 on arriving at grid barrier number `barrier`, 1 on leaving it,
+  // 2 once the following linear phase has staged its activations.
+  long long* trace;
+  int trace_cap;
+  // decode_ll_kernel: activations and attention partial results exchanged as {bits, tag} pairs, and the tag base of
+  // this launch
+  uint2 *ll_x, *ll_qkv, *ll_att, *ll_act, *ll_part;
+  unsigned int ll_base;
 };
 
 __device__ __forceinline__ float ds_ldcg(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ float4 ds_ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+
+__device__ __forceinline__ void ds_trace(const DecodeStepParams& p, unsigned int barrier, int k) {
+  if (p.trace && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x + 1 == gridDim.x)) {
+    const int idx = 4 * static_cast<int>(barrier) + k;
+    if (idx < p.trace_cap) p.trace[(blockIdx.x ? p.trace_cap : 0) + idx] = clock64();
+  }
+}
 
 // Grid-wide barrier; false when the wait gave up (the caller returns).
 __device__ __forceinline__ bool ds_grid_sync(const DecodeStepParams& p, unsigned int& epoch) {
   __syncthreads();
   int ok = 1;
   if (threadIdx.x == 0) {
+    ds_trace(p, epoch / gridDim.x, 0);
     epoch += gridDim.x;
     // release: the CTA's writes (ordered before this by the barrier above) are visible to whoever reads the count
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
@@ -111,6 +128,7 @@ __device__ __forceinline__ bool ds_grid_sync(const DecodeStepParams& p, unsigned
       }
     }
     if (v & 0x80000000u) ok = 0;
+    ds_trace(p, epoch / gridDim.x - 1, 1);
   }
   return __syncthreads_and(ok) != 0;
 }

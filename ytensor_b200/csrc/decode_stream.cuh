@@ -41,6 +41,14 @@ struct DwPhase {
   int K;
 };
 
+struct DwDesc {  // one chunk of a layer, the same for every layer up to the weight's base address
+  int64_t off;    // element offset of its first row in the weight
+  int64_t off2;   // element offset of the up rows of a gate / up chunk
+  uint32_t bytes; // bytes of one copy
+  int kind;
+};
+constexpr int DW_MAX_DESC = 24;
+
 struct DwShared {
   uint64_t full[DW_MAX_SLOTS];
   int done[DW_MAX_SLOTS];
@@ -51,7 +59,9 @@ struct DwShared {
   int nslot;
   int pad[3];
   DwPhase ph[DW_KINDS];
+  DwDesc desc[DW_MAX_DESC];             // the chunks of one layer in order (when they fit the table)
   const uint16_t* w[DW_MAX_LAYERS][4];  // qkv, o, gate_up, down of every layer
+  const float* nw[DW_MAX_LAYERS][4];    // q_norm, k_norm, norm1, norm2 of every layer
 };
 
 __device__ __forceinline__ void dw_bulk_copy(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -99,11 +109,69 @@ __device__ __forceinline__ void dw_issue(DwShared& S, const DecodeStepParams& p,
   char* dst = ring + static_cast<size_t>(slot) * DW_CHUNK;
   const uint32_t bytes = static_cast<uint32_t>(ci.nrows) * static_cast<uint32_t>(ci.K) * 2u;
   const bool pair = ci.kind == 2;
-  fence_proxy_async_smem();  // the warps' reads of the slot (generic proxy) come before the copy's writes
+  // (the warps' reads of the slot precede this call through a block-wide or warp-level synchronisation; a copy that
+  // overwrites data which has only been READ needs no proxy fence)
   mbar_expect_tx(&S.full[slot], pair ? 2u * bytes : bytes);
   dw_bulk_copy(dst, ci.W + static_cast<int64_t>(ci.n0) * ci.K, bytes, &S.full[slot]);
   if (pair) dw_bulk_copy(dst + bytes, ci.W + static_cast<int64_t>(p.inter + ci.n0) * ci.K, bytes, &S.full[slot]);
   atomicMax(&S.issued, c + 1);
+}
+
+// The issuing side of the ring when ONE thread issues every chunk in order: it keeps the position of the next chunk
+// (layer, index within the layer, slot) in registers and reads the layer-independent part from the table in shared
+// memory, so that issuing a chunk costs a few dozen instructions.
+struct DwIssuer {
+  int layer, idx, slot, next;  // next = number of the next chunk to issue
+};
+__device__ __forceinline__ void dw_fill_desc(DwShared& S, const DecodeStepParams& p) {
+  int n = 0;
+  for (int kind = 0; kind < 4; ++kind) {
+    const DwPhase& ph = S.ph[kind];
+    for (int j = 0; j < ph.nchunks; ++j, ++n) {
+      if (n >= DW_MAX_DESC) continue;
+      const int n0 = ph.r0 + j * ph.rpc;
+      const int left = ph.r0 + ph.rows - n0;
+      const int nrows = left < ph.rpc ? left : ph.rpc;
+      DwDesc d;
+      d.off = static_cast<int64_t>(n0) * ph.K;
+      d.off2 = static_cast<int64_t>(p.inter + n0) * ph.K;
+      d.bytes = static_cast<uint32_t>(nrows) * static_cast<uint32_t>(ph.K) * 2u;
+      d.kind = kind;
+      S.desc[n] = d;
+    }
+  }
+}
+__device__ __forceinline__ void dw_issue_next(DwShared& S, const DecodeStepParams& p, char* ring, DwIssuer& it) {
+  if (it.next >= S.total) return;
+  if (S.per_layer > DW_MAX_DESC) {  // (a shape with more chunks per layer than the table holds: the general form)
+    dw_issue(S, p, ring, it.next);
+  } else {
+    char* dst = ring + static_cast<size_t>(it.slot) * DW_CHUNK;
+    uint64_t* bar = &S.full[it.slot];
+    if (it.layer < p.layers) {
+      const DwDesc d = S.desc[it.idx];
+      const uint16_t* W = S.w[it.layer][d.kind];
+      const bool pair = d.kind == 2;
+      mbar_expect_tx(bar, pair ? 2u * d.bytes : d.bytes);
+      dw_bulk_copy(dst, W + d.off, d.bytes, bar);
+      if (pair) dw_bulk_copy(dst + d.bytes, W + d.off2, d.bytes, bar);
+      if (++it.idx == S.per_layer) {
+        it.idx = 0;
+        ++it.layer;
+      }
+    } else {
+      const DwPhase& ph = S.ph[4];
+      const int n0 = ph.r0 + it.idx * ph.rpc;
+      const int left = ph.r0 + ph.rows - n0;
+      const uint32_t bytes = static_cast<uint32_t>(left < ph.rpc ? left : ph.rpc) * static_cast<uint32_t>(ph.K) * 2u;
+      mbar_expect_tx(bar, bytes);
+      dw_bulk_copy(dst, p.lm_head + static_cast<int64_t>(n0) * ph.K, bytes, bar);
+      ++it.idx;
+    }
+    S.issued = it.next + 1;
+  }
+  ++it.next;
+  if (++it.slot == S.nslot) it.slot = 0;
 }
 
 // One linear phase: stage the activations (they depend on the barrier just passed), then walk this CTA's chunks of
@@ -112,13 +180,15 @@ __device__ __forceinline__ void dw_issue(DwShared& S, const DecodeStepParams& p,
 // epi: 0 dst = y, 1 dst += y, 2 dst = swish(y_gate) * y_up.
 template <int MT>
 __device__ __noinline__ bool dw_linear(const DecodeStepParams& p, DwShared& S, char* ring, float* xs, int kind, int stage,
-                                       const float* src, const float* norm_w, int epi, float* dst, int ld, int& c) {
+                                       const float* src, const float* norm_w, int epi, float* dst, int ld,
+                                       unsigned int barrier_no, int& c) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const DwPhase ph = S.ph[kind];
   const int K = ph.K, B = p.B;
   if (stage == 0) ds_stage_rmsnorm(xs, K, src, norm_w, B, K, p.eps, warp, lane);
   else if (stage == 1) ds_stage_copy(xs, K, src, B, K, 0, K);
   else ds_stage_attention(xs, K, src, B, p.heads, p.kv_heads, p.chunks, 0, K);
+  ds_trace(p, barrier_no, 2);
   const bool pair = kind == 2;
   for (int j = 0; j < ph.nchunks; ++j, ++c) {
     const int slot = c % S.nslot;
@@ -188,7 +258,7 @@ __device__ __noinline__ bool dw_linear(const DecodeStepParams& p, DwShared& S, c
 
 // After a give-up: raise the status, release everyone at the grid barrier, and wait (bounded) for the copies that are
 // still on their way into this CTA's shared memory.
-__device__ __forceinline__ void dw_abort(const DecodeStepParams& p, DwShared& S, int c) {
+__device__ __noinline__ void dw_abort(const DecodeStepParams& p, DwShared& S, int c) {
   __syncthreads();
   if (threadIdx.x == 0) {
     atomicExch(p.status, YTC_TIMEOUT);
@@ -200,6 +270,8 @@ __device__ __forceinline__ void dw_abort(const DecodeStepParams& p, DwShared& S,
   }
   __syncthreads();
 }
+
+__device__ __noinline__ bool dw_grid_sync(const DecodeStepParams& p, unsigned int& epoch) { return ds_grid_sync(p, epoch); }
 
 template <int MT, int G>
 __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const DecodeStepParams p) {
@@ -273,14 +345,14 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_stream_kernel(const Deco
   }
 #define DW_SYNC()                     \
   do {                                \
-    if (!ds_grid_sync(p, epoch)) {    \
+    if (!dw_grid_sync(p, epoch)) {    \
       dw_abort(p, S, c);              \
       return;                         \
     }                                 \
   } while (0)
 #define DW_LINEAR(...)                          \
   do {                                          \
-    if (!dw_linear<MT>(p, S, ring, xs, __VA_ARGS__, c)) { \
+    if (!dw_linear<MT>(p, S, ring, xs, __VA_ARGS__, epoch / gridDim.x - 1, c)) { \
       dw_abort(p, S, c);                        \
       return;                                   \
     }                                           \

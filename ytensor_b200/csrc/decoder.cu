@@ -24,6 +24,7 @@
 
 #include "decode_step.cuh"
 #include "decode_stream.cuh"
+#include "decode_ll.cuh"
 #include "ytc_common.cuh"
 
 namespace ytk {
@@ -410,6 +411,11 @@ struct Qwen3Model {
   void* allreduce_user = nullptr;
   // single-kernel decode step (decode_step.cuh)
   int decode_path = 0;              // 0 automatic, 1 one launch per operator, 2 the persistent step kernel or fail
+  long long* trace = nullptr;       // optional timeline buffer of the step kernel (ytcuda_qwen3_set_trace)
+  char* ll_buf = nullptr;           // pair buffers of the barrier-free step kernel (decode_ll.cuh) + unit counters
+  size_t ll_bytes = 0;
+  unsigned int ll_base = 1;         // tag base of the next launch
+  int trace_cap = 0;
   DsLayer* ds_lw = nullptr;         // device copy of the per-layer weight pointers
   bool ds_lw_stale = true;
   float* ds_part = nullptr;         // attention partials
@@ -815,8 +821,16 @@ int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64) {
 int ytcuda_qwen3_set_decode_path(void* handle, int path) {
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m, "ytcuda_qwen3_set_decode_path: null handle");
-  YTC_REQUIRE(path >= 0 && path <= 4, "ytcuda_qwen3_set_decode_path: path must be 0 .. 4");
+  YTC_REQUIRE(path >= 0 && path <= 5, "ytcuda_qwen3_set_decode_path: path must be 0 .. 5");
   m->decode_path = path;
+  return YTC_OK;
+}
+int ytcuda_qwen3_set_trace(void* handle, int64_t* dev_buf, int slots_per_cta) {
+  auto* m = static_cast<Qwen3Model*>(handle);
+  YTC_REQUIRE(m, "ytcuda_qwen3_set_trace: null handle");
+  YTC_REQUIRE(slots_per_cta >= 0 && (dev_buf || slots_per_cta == 0), "ytcuda_qwen3_set_trace: bad buffer");
+  m->trace = slots_per_cta > 0 ? reinterpret_cast<long long*>(dev_buf) : nullptr;
+  m->trace_cap = slots_per_cta;
   return YTC_OK;
 }
 int ytcuda_qwen3_cache_len(void* handle) {
@@ -931,6 +945,8 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   p.cache_layer = static_cast<size_t>(B) * m->l_kv_heads * m->max_pos * D;
   p.tp_rank = m->tp_rank; p.tp_world = m->tp_world; p.ar_base = m->ar_seq;
   p.wait_cycles = wait_cycle_limit();
+  p.trace = m->trace;
+  p.trace_cap = m->trace_cap;
   if (m->tp_world > 1) {
     const size_t flags_at = tp_flags_offset(m->hidden);
     for (int r = 0; r < m->tp_world; ++r) {
@@ -957,17 +973,63 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   YTC_CUDA(cudaMemsetAsync(m->ds_sync, 0, sync_words * sizeof(unsigned int), st));
   void* args[] = {&p};
   const void* fn = nullptr;
-  // Up to four sequences: the form of the kernel that streams its weights through a shared-memory ring
-  // (decode_stream.cuh), unless decode_path 4 asks for the older form or a size does not fit its chunks.
+  // Up to four sequences: the forms of the kernel that stream their weights through a shared-memory ring, unless
+  // decode_path 4 asks for the older form or a size does not fit the chunks. One GPU: no grid barriers, activations
+  // exchanged as tagged pairs (decode_ll.cuh); tensor parallel, or decode_path 5: barriers kept (decode_stream.cuh).
   if (!mma && mt <= 4 && m->decode_path != 4 && m->layers <= DW_MAX_LAYERS) {
-    const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128);
-    int xs_bytes = mt * kmax * static_cast<int>(sizeof(float));
+    // (a CTA holds at most one attention unit unless there is a single key chunk: the collecting unit of the
+    // barrier-free form never waits for a unit of its own CTA)
+    const bool ll = m->tp_world == 1 && m->decode_path != 5 && (m->hidden + sm_count() - 1) / sm_count() + 1 <= LL_MAX_OWN &&
+                    (p.chunks == 1 || B * m->l_kv_heads * p.chunks <= sm_count()) && p.chunks <= DS_MAX_CHUNKS_LL;
+    const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128) + (ll ? (DS_WARPS * 4 + 4 * LL_MAX_OWN) * 4 : 0);
+    int xs_bytes = mt * ll_row_floats(kmax) * static_cast<int>(sizeof(float));  // (rows padded to whole 256-column blocks)
     if (xs_bytes < att) xs_bytes = att;
     xs_bytes = (xs_bytes + 127) / 128 * 128;
     int nslot = (227 * 1024 - head - xs_bytes) / DW_CHUNK;
     if (nslot > DW_MAX_SLOTS) nslot = DW_MAX_SLOTS;
     const bool fits = nslot >= 2 && kmax * 2 <= DW_CHUNK && m->hidden * 4 <= DW_CHUNK && m->hidden % 8 == 0 &&
                       m->l_inter % 8 == 0;
+    if (fits && ll) {
+      const int qkv_w = (m->l_heads + 2 * m->l_kv_heads) * D;
+      const size_t part_pairs = static_cast<size_t>(B) * m->l_kv_heads * DS_MAX_CHUNKS_LL * groups * (2 + D);
+      const size_t pairs = static_cast<size_t>(B) * (m->hidden + qkv_w + m->l_heads * D + m->l_inter) + part_pairs;
+      const size_t need = pairs * sizeof(uint2);
+      if (!m->ll_buf || m->ll_bytes < need) {
+        int s = dev_alloc(m, reinterpret_cast<void**>(&m->ll_buf), need);
+        if (s != YTC_OK) return s;
+        m->ll_bytes = need;
+        m->ll_base = 0xFFFFFFFFu;  // forces the clearing below
+      }
+      const unsigned int per_step = 2u + 5u * static_cast<unsigned int>(m->layers);
+      if (m->ll_base > 0xF0000000u) {  // first use, or the tags are about to wrap: start again from clean buffers
+        YTC_CUDA(cudaMemsetAsync(m->ll_buf, 0, m->ll_bytes, st));
+        m->ll_base = 1;
+      }
+      uint2* q = reinterpret_cast<uint2*>(m->ll_buf);
+      p.ll_x = q;
+      p.ll_qkv = p.ll_x + static_cast<size_t>(B) * m->hidden;
+      p.ll_att = p.ll_qkv + static_cast<size_t>(B) * qkv_w;
+      p.ll_act = p.ll_att + static_cast<size_t>(B) * m->l_heads * D;
+      p.ll_part = p.ll_act + static_cast<size_t>(B) * m->l_inter;
+      p.ll_base = m->ll_base;
+      p.dw_xs_bytes = xs_bytes;
+      p.dw_nslot = nslot;
+      const int dsmem = head + xs_bytes + nslot * DW_CHUNK;
+#define LL_PICK(MT)                                                                         \
+  fn = groups == 1   ? reinterpret_cast<const void*>(decode_ll_kernel<MT, 1>)               \
+       : groups == 2 ? reinterpret_cast<const void*>(decode_ll_kernel<MT, 2>)               \
+                     : reinterpret_cast<const void*>(decode_ll_kernel<MT, 4>)
+      if (mt == 1) LL_PICK(1);
+      else if (mt == 2) LL_PICK(2);
+      else LL_PICK(4);
+#undef LL_PICK
+      const int sa = ensure_dynamic_smem(fn, dsmem);
+      if (sa != YTC_OK) return sa;
+      YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(DS_THREADS), args, dsmem, st));
+      count_launch();
+      m->ll_base += per_step;
+      return YTC_OK;
+    }
     if (fits) {
       p.dw_xs_bytes = xs_bytes;
       p.dw_nslot = nslot;

@@ -192,7 +192,8 @@ class Qwen3ForCausalLM:
 
     def set_decode_path(self, path: int) -> None:
         """0: automatic, 1: one launch per operator, 2: the single persistent kernel per decode step (or an error),
-        3: as 2 with FFMA linear phases at every batch size, 4: as 3 without the shared-memory weight ring."""
+        3: as 2 with FFMA linear phases at every batch size, 4: as 3 without the shared-memory weight ring, 5: the
+        ring with grid barriers (2 on one GPU with up to four sequences has neither barriers nor a cold ring)."""
         check(self.L.ytcuda_qwen3_set_decode_path(self.h, int(path)))
 
     def get_kv_cache_len(self) -> int:
@@ -204,8 +205,10 @@ class Qwen3ForCausalLM:
         the operator path with tcgen05 linears beyond."""
         limit = 6 if self.tp_world == 1 else 8
         if self.batch <= limit:
-            return ("decode_step_kernel (FFMA linear phases)" if self.batch < 5 else
-                    "decode_step_kernel (mma.sync linear phases)")
+            if self.batch < 5:
+                return ("decode_ll_kernel (no grid barriers: tagged-pair activations, weights through a shared-memory "
+                        "ring)" if self.tp_world == 1 else "decode_stream_kernel (weights through a shared-memory ring)")
+            return "decode_step_kernel (mma.sync linear phases)"
         return "gemm_tc_kernel (hi + lo planes, split-k pieces) + attn_decode_fast_kernel + fused glue kernels"
 
     def forward(self, ids):
