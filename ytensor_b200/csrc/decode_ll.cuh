@@ -36,9 +36,16 @@
 
 namespace ytk {
 
+constexpr int LL_WARPS = 7;                  // worker warps
+constexpr int LL_WORKERS = LL_WARPS * 32;
+constexpr int LL_THREADS = LL_WORKERS + 32;  // the eighth warp only issues the weight copies (eight warps of 224
+                                             // registers would not fit a ninth: registers are per scheduler)
 constexpr int LL_MAX_OWN = 64;  // rows of x one CTA may own (hidden / CTAs, rounded up)
 constexpr int DS_MAX_CHUNKS_LL = 64;  // key chunks per (sequence, kv head) the partial-result buffer holds
 constexpr int LL_GROUP = 4;     // chunks of the weight ring a linear phase takes at a time
+
+// Synchronises the worker threads (named barrier 1); the issuing warp never takes part.
+__device__ __forceinline__ void ll_sync() { asm volatile("bar.sync 1, %0;" ::"n"(LL_WORKERS) : "memory"); }
 
 __device__ __forceinline__ uint4 ll_ld2(const uint2* p) {  // two pairs; L1 is bypassed (another SM wrote them)
   uint4 v;
@@ -91,7 +98,7 @@ __device__ __forceinline__ void ll_trace(const DecodeStepParams& p, int& idx) {
 }
 
 // xs[b][0 .. n) = value of pair src[b][i] (times scale[i] when given) once every tag equals `tag`; ss[b] += sum of
-// squares of the unscaled values. All loads of a pass are in flight together; 256 threads, n even.
+// squares of the unscaled values. All loads of a pass are in flight together; the worker threads, n even.
 template <int MT, bool NORM>
 __device__ __forceinline__ void ll_stage(const DecodeStepParams& p, int* abort_word, float* xs, int ld,
                                          const uint2* src, int n, unsigned int tag, const float* scale, float* red) {
@@ -101,11 +108,11 @@ __device__ __forceinline__ void ll_stage(const DecodeStepParams& p, int* abort_w
 #pragma unroll
   for (int b = 0; b < MT; ++b) ss[b] = 0.f;
   const long long t0 = clock64();
-  for (int base = 0; base < n; base += U * 2 * DS_THREADS) {
+  for (int base = 0; base < n; base += U * 2 * LL_WORKERS) {
     float2 g[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int i = base + (u * DS_THREADS + tid) * 2;
+      const int i = base + (u * LL_WORKERS + tid) * 2;
       g[u] = make_float2(1.f, 1.f);
       if (NORM && i < n) g[u] = __ldg(reinterpret_cast<const float2*>(scale + i));
     }
@@ -116,13 +123,13 @@ __device__ __forceinline__ void ll_stage(const DecodeStepParams& p, int* abort_w
       uint4 v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int i = base + (u * DS_THREADS + tid) * 2;
+        const int i = base + (u * LL_WORKERS + tid) * 2;
         v[u] = make_uint4(0u, tag, 0u, tag);
         if (i < n) v[u] = ll_ld2(row + i);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int i = base + (u * DS_THREADS + tid) * 2;
+        const int i = base + (u * LL_WORKERS + tid) * 2;
         if (i >= n) continue;
         int spins = 0;
         while (v[u].y != tag || v[u].w != tag) {
@@ -143,10 +150,10 @@ __device__ __forceinline__ void ll_stage(const DecodeStepParams& p, int* abort_w
 #pragma unroll
     for (int b = 0; b < MT; ++b) {
       const float s = ds_warp_sum(ss[b]);
-      if (lane == 0) red[warp * MT + b] = s;
+      if (lane == 0) red[b * 8 + warp] = s;
     }
   }
-  __syncthreads();
+  ll_sync();
 }
 
 // One linear phase without barriers. stage 0: xs = x * norm_w with the row factors 1 / sqrt(mean(x^2) + eps) applied
@@ -156,7 +163,7 @@ template <int MT>
 __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S, char* ring, float* xs, float* red,
                                        float* x_own, int kind, int stage, const uint2* src, unsigned int src_tag,
                                        const float* norm_w, int epi, uint2* dst, unsigned int dst_tag, float* out, int ld,
-                                       int& c, int& slot, unsigned int& parity, DwIssuer& iss, int& tr) {
+                                       int& c, int& slot, unsigned int& parity, int& tr) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const DwPhase ph = S.ph[kind];
   const int K = ph.K, B = p.B;
@@ -170,9 +177,10 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
   for (int b = 0; b < MT; ++b) {
     inv[b] = 1.f;
     if (stage == 0 || stage == 3) {
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < DS_WARPS; ++w) s += red[w * MT + b];
+      // red is [MT][8] (the eighth entry of a row is zero): two 128-bit loads per sequence
+      const float4 r0 = *reinterpret_cast<const float4*>(&red[b * 8]);
+      const float4 r1 = *reinterpret_cast<const float4*>(&red[b * 8 + 4]);
+      const float s = ((r0.x + r0.y) + (r0.z + r0.w)) + ((r1.x + r1.y) + (r1.z + r1.w));
       inv[b] = rsqrtf(s * (1.0f / static_cast<float>(K)) + p.eps);
     }
   }
@@ -211,7 +219,7 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
     int Rg = ph.rows - g0;
     if (Rg > gc * ph.rpc) Rg = gc * ph.rpc;
     const int rb_rows = pair ? RB / 2 : RB;  // tasks (rows or pairs) per block: RB weight rows either way
-    for (int t0 = warp; t0 < Rg; t0 += DS_WARPS * rb_rows) {
+    for (int t0 = warp; t0 < Rg; t0 += LL_WARPS * rb_rows) {
       const char* wp[RB];   // weight rows of the block (pairs: gate rows, then up rows)
       int nidx[RB];         // output index of task i (-1: none)
 #pragma unroll
@@ -222,7 +230,7 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
 #pragma unroll
       for (int i = 0; i < RB; ++i) {
         if (i >= rb_rows) break;
-        const int r = t0 + i * DS_WARPS;
+        const int r = t0 + i * LL_WARPS;
         if (r >= Rg) break;
         int jr = 0, rr = r;
         while (rr >= ph.rpc) {
@@ -238,25 +246,50 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
           wp[i + RB / 2] = base + (left < ph.rpc ? left : ph.rpc) * row_bytes;  // the up rows follow the chunk's gate rows
         }
       }
-      float acc[RB][MT];
+      // weight rows in use: tasks 0 .. nt - 1 (and their up rows); the others are skipped (uniform per warp)
+      int nt = 0;
+#pragma unroll
+      for (int i = 0; i < RB; ++i) nt += nidx[i] >= 0 ? 1 : 0;
+      bool use[RB];
+#pragma unroll
+      for (int i = 0; i < RB; ++i) use[i] = pair ? (i % (RB / 2)) < nt : i < nt;
+      // even and odd pieces go to separate accumulators: two independent FMA chains per row
+      float acc[RB][MT], acc2[RB][MT];
 #pragma unroll
       for (int i = 0; i < RB; ++i)
 #pragma unroll
-        for (int m = 0; m < MT; ++m) acc[i][m] = 0.f;
-#pragma unroll 2
-      for (int i = 0; i < np; ++i) {
-        if ((lane + 32 * i) * 8 >= K) break;  // (only in the last piece of a row whose length is not a multiple of 256)
-        uint4 w[RB];
+        for (int m = 0; m < MT; ++m) acc[i][m] = acc2[i][m] = 0.f;
+      for (int i = 0; i < np; i += 2) {
+        const bool in0 = (lane + 32 * i) * 8 < K, in1 = i + 1 < np && (lane + 32 * (i + 1)) * 8 < K;
+        uint4 w[RB], w2[RB];
 #pragma unroll
-        for (int rI = 0; rI < RB; ++rI) w[rI] = *reinterpret_cast<const uint4*>(wp[rI] + i * 512);
+        for (int rI = 0; rI < RB; ++rI) {
+          w[rI] = w2[rI] = make_uint4(0u, 0u, 0u, 0u);
+          if (use[rI] && in0) w[rI] = *reinterpret_cast<const uint4*>(wp[rI] + i * 512);
+          if (use[rI] && in1) w2[rI] = *reinterpret_cast<const uint4*>(wp[rI] + (i + 1) * 512);
+        }
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           const float4 xa = *reinterpret_cast<const float4*>(&xs[m * KP + ((2 * i) * 32 + lane) * 4]);
           const float4 xb = *reinterpret_cast<const float4*>(&xs[m * KP + ((2 * i + 1) * 32 + lane) * 4]);
+          float4 ya = xa, yb = xb;
+          if (i + 1 < np) {
+            ya = *reinterpret_cast<const float4*>(&xs[m * KP + ((2 * i + 2) * 32 + lane) * 4]);
+            yb = *reinterpret_cast<const float4*>(&xs[m * KP + ((2 * i + 3) * 32 + lane) * 4]);
+          }
 #pragma unroll
-          for (int rI = 0; rI < RB; ++rI) acc[rI][m] = ds_dot8(w[rI], xa, xb, acc[rI][m]);
+          for (int rI = 0; rI < RB; ++rI) {
+            if (use[rI]) {
+              acc[rI][m] = ds_dot8(w[rI], xa, xb, acc[rI][m]);
+              acc2[rI][m] = ds_dot8(w2[rI], ya, yb, acc2[rI][m]);
+            }
+          }
         }
       }
+#pragma unroll
+      for (int i = 0; i < RB; ++i)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[i][m] += acc2[i][m];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
@@ -288,10 +321,9 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
         }
       }
     }
-    __syncthreads();  // every warp has finished with the group's slots (and, after the last group, with xs)
-    if (threadIdx.x == 0)
-      for (int j = 0; j < gc; ++j) dw_issue_next(S, p, ring, iss);
+    ll_sync();  // every warp has finished with the group's slots (and, after the last group, with xs)
     c += gc;
+    if (threadIdx.x == 0) *reinterpret_cast<volatile int*>(&S.consumed) = c;  // the issuing warp refills them
   }
   ll_trace(p, tr);
   return true;
@@ -312,9 +344,9 @@ __device__ __forceinline__ bool ll_attention(const DecodeStepParams& p, DwShared
   const float* cr = p.cos_t + static_cast<int64_t>(p.rope_pos) * D;
   const float* sr = p.sin_t + static_cast<int64_t>(p.rope_pos) * D;
   float* qs = xs;                 // [G][128] query heads of the group, normalised and rotated
-  float* pm = qs + G * D;         // [DS_WARPS][G] running maxima of the warps
-  float* pl = pm + DS_WARPS * G;  // sums
-  float* po = pl + DS_WARPS * G;  // [DS_WARPS][G][128] unnormalised outputs
+  float* pm = qs + G * D;         // [LL_WARPS][G] running maxima of the warps
+  float* pl = pm + LL_WARPS * G;  // sums
+  float* po = pl + LL_WARPS * G;  // [LL_WARPS][G][128] unnormalised outputs
   ll_trace(p, tr);
   for (int u = blockIdx.x; u < units; u += gridDim.x) {
     const int chunk = u % p.chunks;
@@ -366,7 +398,7 @@ __device__ __forceinline__ bool ll_attention(const DecodeStepParams& p, DwShared
         }
       }
     }
-    __syncthreads();
+    ll_sync();
     if (*reinterpret_cast<volatile int*>(&S.abort_word)) return false;
     ll_trace(p, tr);
     const float* kb = kc + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.max_pos * D;
@@ -386,7 +418,7 @@ __device__ __forceinline__ bool ll_attention(const DecodeStepParams& p, DwShared
     for (int g = 0; g < G; ++g)
 #pragma unroll
       for (int i = 0; i < 4; ++i) qreg[g][i] = *reinterpret_cast<const float4*>(&qs[g * D + (j8 + 8 * i) * 4]);
-    for (int key0 = k_begin + warp * DS_KB; key0 < k_end; key0 += DS_WARPS * DS_KB) {
+    for (int key0 = k_begin + warp * DS_KB; key0 < k_end; key0 += LL_WARPS * DS_KB) {
       float sc[G][DS_KB / 4];
       float4 vv[DS_KB];
 #pragma unroll
@@ -470,20 +502,20 @@ __device__ __forceinline__ bool ll_attention(const DecodeStepParams& p, DwShared
       }
       *reinterpret_cast<float4*>(&po[(warp * G + g) * D + lane * 4]) = acc[g];
     }
-    __syncthreads();
+    ll_sync();
     ll_trace(p, tr);
     uint2* att_row = p.ll_att + static_cast<int64_t>(b) * attn_w;
     if (warp < G) {
       // warp g combines the 8 warps' results of query head g
       const int g = warp;
-      const float mw = lane < DS_WARPS ? pm[lane * G + g] : -CUDART_INF_F;
-      const float lw = lane < DS_WARPS ? pl[lane * G + g] : 0.f;
+      const float mw = lane < LL_WARPS ? pm[lane * G + g] : -CUDART_INF_F;
+      const float lw = lane < LL_WARPS ? pl[lane * G + g] : 0.f;
       float m = ds_warp_max(mw);
       const float fw = (mw == -CUDART_INF_F) ? 0.f : __expf(mw - m);
       float lsum = ds_warp_sum(lw * fw);
       float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-      for (int w = 0; w < DS_WARPS; ++w) {
+      for (int w = 0; w < LL_WARPS; ++w) {
         const float f = __shfl_sync(0xffffffffu, fw, w);
         const float4 ow = *reinterpret_cast<const float4*>(&po[(w * G + g) * D + lane * 4]);
         o.x = fmaf(ow.x, f, o.x);
@@ -557,19 +589,19 @@ __device__ __forceinline__ bool ll_attention(const DecodeStepParams& p, DwShared
         ll_st(d + 3, o.w * inv, att_tag);
       }
     }
-    __syncthreads();  // the scratch is reused by this CTA's next unit
+    ll_sync();  // the scratch is reused by this CTA's next unit
     ll_trace(p, tr);
   }
   return true;
 }
 
 template <int MT, int G>
-__global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeStepParams p) {
+__global__ void __launch_bounds__(LL_THREADS, 1) decode_ll_kernel(const DecodeStepParams p) {
   extern __shared__ __align__(128) char dw_smem[];
-  // layout: DwShared | red [8][MT] | x_own [MT][LL_MAX_OWN] | xs | ring (128-byte aligned)
+  // layout: DwShared | red [4][8] | x_own [4][LL_MAX_OWN] | xs | ring
   DwShared& S = *reinterpret_cast<DwShared*>(dw_smem);
   float* red = reinterpret_cast<float*>(dw_smem + ((sizeof(DwShared) + 127) / 128) * 128);
-  float* x_own = red + DS_WARPS * 4;
+  float* x_own = red + 32;  // (red holds up to 8 warps x 4 sequences)
   float* xs = x_own + 4 * LL_MAX_OWN;
   char* ring = reinterpret_cast<char*>(xs) + p.dw_xs_bytes;
   constexpr int D = 128;
@@ -580,6 +612,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeSt
   if (threadIdx.x == 0) {
     S.abort_word = 0;
     S.issued = 0;
+    S.consumed = 0;
+    S.issuer_done = 0;
     S.nslot = p.dw_nslot;
     for (int s = 0; s < DW_MAX_SLOTS; ++s) {
       mbar_init(&S.full[s], 1);
@@ -604,7 +638,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeSt
     S.total = per_layer * p.layers + S.ph[4].nchunks;
     dw_fill_desc(S, p);
   }
-  for (int i = threadIdx.x; i < p.layers; i += DS_THREADS) {
+  if (threadIdx.x < 32) red[threadIdx.x] = 0.f;  // [4 sequences][8]: the entries of warps that do not exist stay zero
+  for (int i = threadIdx.x; i < p.layers; i += LL_THREADS) {
     const DsLayer W = p.lw[i];
     S.w[i][0] = W.qkv;
     S.w[i][1] = W.o;
@@ -615,11 +650,28 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeSt
     S.nw[i][2] = W.norm1;
     S.nw[i][3] = W.norm2;
   }
-  __syncthreads();
-  DwIssuer iss{0, 0, 0, 0};
-  if (threadIdx.x == 0) {  // the ring fills while the embedding is gathered
-    const int first = S.total < S.nslot ? S.total : S.nslot;
-    for (int c0 = 0; c0 < first; ++c0) dw_issue_next(S, p, ring, iss);
+  __syncthreads();  // (the only synchronisation of all nine warps)
+  if (threadIdx.x >= LL_WORKERS) {
+    // The issuing warp: one lane keeps the ring full. Chunk number n may be issued once chunk n - nslot has been
+    // consumed (the workers publish the count after the synchronisation that ends a group of chunks), so the copies
+    // run ahead of the phases by the depth of the ring and never sit on a worker's critical path.
+    if (threadIdx.x == LL_WORKERS) {
+      DwIssuer iss{0, 0, 0, 0};
+      const long long t0 = clock64();
+      long long last = t0;
+      while (iss.next < S.total) {
+        if (*reinterpret_cast<volatile int*>(&S.abort_word)) break;
+        const int consumed = *reinterpret_cast<volatile int*>(&S.consumed);
+        if (iss.next < consumed + S.nslot) {
+          dw_issue_next(S, p, ring, iss);
+          last = clock64();
+        } else if (clock64() - last > p.wait_cycles) {  // the workers are stuck: they will have raised the status
+          break;
+        }
+      }
+      *reinterpret_cast<volatile int*>(&S.issuer_done) = 1;
+    }
+    return;
   }
   int c = 0, slot = 0, tr = 0;
   unsigned int parity = 0;
@@ -636,7 +688,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeSt
         int id = p.ids[b];
         id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
         const uint16_t* erow = p.embed + static_cast<int64_t>(id) * H;
-        for (int i = threadIdx.x * 2; i < H; i += 2 * DS_THREADS) {
+        for (int i = threadIdx.x * 2; i < H; i += 2 * LL_WORKERS) {
           const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(erow + i));
           const float2 g = __ldg(reinterpret_cast<const float2*>(g0 + i));
           const float a = __uint_as_float(w << 16), c2 = __uint_as_float(w & 0xFFFF0000u);
@@ -648,9 +700,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeSt
         }
       }
       ss = ds_warp_sum(ss);
-      if (lane == 0) red[warp * MT + b] = ss;
+      if (lane == 0) red[b * 8 + warp] = ss;
     }
-    __syncthreads();
+    ll_sync();
   }
 
   // K / V rows of this CTA's first attention unit, requested into the L2 one phase ahead
@@ -692,7 +744,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeSt
         if (kv_lines > 0) {
           const char* kr = reinterpret_cast<const char*>(p.k_cache + static_cast<size_t>(l) * p.cache_layer + kv_off);
           const char* vr = reinterpret_cast<const char*>(p.v_cache + static_cast<size_t>(l) * p.cache_layer + kv_off);
-          for (int i = threadIdx.x; i < kv_lines; i += DS_THREADS) {
+          for (int i = threadIdx.x; i < kv_lines; i += LL_WORKERS) {
             asm volatile("prefetch.global.L2 [%0];" ::"l"(kr + i * 128));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(vr + i * 128));
           }
@@ -705,10 +757,25 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_ll_kernel(const DecodeSt
         kind = 3; stage = 1; src = p.ll_act; st = t + 3; epi = 1; dst = p.ll_x; dt = t + 4; ld = H;
       }
       ok = ll_linear<MT>(p, S, ring, xs, red, x_own, kind, stage, src, st, nw, epi, dst, dt, p.logits, ld, c, slot, parity,
-                         iss, tr);
+                         tr);
     }
     if (!ok) {
-      dw_abort(p, S, c);
+      // give up: raise the status, stop everyone, and wait (bounded) for the copies still on their way into this CTA's
+      // shared memory once the issuing warp has stopped
+      *reinterpret_cast<volatile int*>(&S.abort_word) = 1;
+      ll_sync();
+      if (threadIdx.x == 0) {
+        atomicExch(p.status, YTC_TIMEOUT);
+        atomicOr(p.sync, 0x80000000u);
+        const long long t0 = clock64();
+        while (!*reinterpret_cast<volatile int*>(&S.issuer_done) && clock64() - t0 < p.wait_cycles) {
+        }
+        const int issued = *reinterpret_cast<volatile int*>(&S.issued);
+        int dummy = 0;
+        for (int x = c; x < issued; ++x)
+          mbar_wait_limit(&S.full[x % S.nslot], static_cast<uint32_t>((x / S.nslot) & 1), &dummy, p.wait_cycles);
+      }
+      ll_sync();
       return;
     }
     if (++sub == 5) {

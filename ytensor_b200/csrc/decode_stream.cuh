@@ -57,7 +57,9 @@ struct DwShared {
   int per_layer;    // chunks of this CTA per layer
   int total;        // chunks of this CTA per step
   int nslot;
-  int pad[3];
+  int consumed;     // barrier-free kernel: chunks the workers have finished with
+  int issuer_done;  // barrier-free kernel: the issuing warp has stopped
+  int pad[1];
   DwPhase ph[DW_KINDS];
   DwDesc desc[DW_MAX_DESC];             // the chunks of one layer in order (when they fit the table)
   const uint16_t* w[DW_MAX_LAYERS][4];  // qkv, o, gate_up, down of every layer

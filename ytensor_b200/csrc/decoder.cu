@@ -961,12 +961,15 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   const int keys = p.n_keys;
   // Key chunks of 128 keys (8 per warp), fewer and longer ones when that would be more units than CTAs or more
   // than DS_MAX_CHUNKS chunks.
-  int n_chunks = (keys + 127) / 128;
+  // (The barrier-free form has seven worker warps of 16 keys each: chunks of 112 keys keep every warp at one pass.)
+  const bool ll_shape = !mma && mt <= 4 && m->tp_world == 1 && m->decode_path != 4 && m->decode_path != 5;
+  const int unit_keys = ll_shape ? LL_WARPS * DS_KB : 128;
+  int n_chunks = (keys + unit_keys - 1) / unit_keys;
   const int fit = sm_count() / (B * m->l_kv_heads);
   if (n_chunks > fit) n_chunks = fit > 0 ? fit : 1;
   if (n_chunks > DS_MAX_CHUNKS) n_chunks = DS_MAX_CHUNKS;
   int per = (keys + n_chunks - 1) / n_chunks;
-  per = (per + 31) / 32 * 32;  // whole blocks of 32 keys
+  per = ll_shape ? (per + 15) / 16 * 16 : (per + 31) / 32 * 32;  // whole blocks of keys
   p.keys_per_chunk = per;
   p.chunks = (keys + per - 1) / per;
   p.xs_cols = xs_cols;
@@ -1025,12 +1028,12 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
 #undef LL_PICK
       const int sa = ensure_dynamic_smem(fn, dsmem);
       if (sa != YTC_OK) return sa;
-      YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(DS_THREADS), args, dsmem, st));
+      YTC_CUDA(cudaLaunchCooperativeKernel(fn, dim3(sm_count()), dim3(LL_THREADS), args, dsmem, st));
       count_launch();
       m->ll_base += per_step;
       return YTC_OK;
     }
-    if (fits) {
+    if (fits && m->decode_path == 5) {  // (on request only: with its barriers kept, the ring alone does not pay)
       p.dw_xs_bytes = xs_bytes;
       p.dw_nslot = nslot;
       const int dsmem = head + xs_bytes + nslot * DW_CHUNK;
