@@ -126,7 +126,7 @@ class Dist:
             import datetime
 
             import torch.distributed as dist
-            dist.init_process_group("nccl", device_id=self.dev, timeout=datetime.timedelta(seconds=180))
+            dist.init_process_group("nccl", device_id=self.dev, timeout=datetime.timedelta(seconds=120))
             self.dist = dist
 
     def barrier(self):
@@ -831,6 +831,9 @@ def run_secondary(args, names, budget_s: float) -> list:
             continue
         env = dict(os.environ)
         env["MASTER_PORT"] = str(base_port + 17 + i)
+        # under torch.distributed.run the ranks are clients of the launcher's own store on MASTER_PORT; the children
+        # rendezvous on another port, where the child of rank 0 has to host the store itself
+        env["TORCHELASTIC_USE_AGENT_STORE"] = "False"
         cmd = [sys.executable, str(Path(__file__).resolve()), "--child", name, "--gpus", str(args.gpus),
                "--steps", str(max(3, min(args.steps, 10))), "--warmup", str(args.warmup)]
         if args.no_cpu_baseline:
