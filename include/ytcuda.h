@@ -28,7 +28,17 @@ typedef enum {
 } ytc_status;
 
 /* Element types, named like the reference's dtype strings (include/ytensor_types.hpp:125-153). */
-typedef enum { YTC_F32 = 0, YTC_BF16 = 1, YTC_F16 = 2 } ytc_dtype;
+typedef enum {
+  YTC_F32 = 0,
+  YTC_BF16 = 1,
+  YTC_F16 = 2,
+  /* 8-bit storage types (yt::float8_e5m2 / float8_e4m3 / float8_e8m0, include/types/float_spec.hpp:534-536): accepted
+   * by ytcuda_cast only. They follow the reference's generic FloatSpec rules, not the OCP "fn" variants: the largest
+   * exponent is infinity / NaN in every format, results below the smallest normal flush to zero, e8m0 has no sign. */
+  YTC_F8_E5M2 = 3,
+  YTC_F8_E4M3 = 4,
+  YTC_F8_E8M0 = 5
+} ytc_dtype;
 
 /* ---------------------------------------------------------------- utilities */
 /* Text of the last error raised on the calling thread ("" if none). */
@@ -121,12 +131,22 @@ int ytcuda_gemm_host(int dtype_in, int dtype_out, const void* A, const void* B, 
 /* C[b][i][j] = (A[b] . B[b])[i][j] where mask[i][j] != 0, masked_value elsewhere; mask is a bool / uint8 matrix
  * [m, n] (row stride in bytes = elements) shared by every batch item. Replaces YTensor::masked_matmul with a bool
  * mask (src/ytensor_math.inl:318-366, 1053-1090; yt::kernel::avx2::sgemm_masked, src/kernel/avx2/sgemm.inl:342-584).
- * The product runs as ytcuda_gemm does (alpha 1, beta 0), a second pass writes masked_value; a predicate mask is
- * materialised by the caller. */
+ * The product runs as ytcuda_gemm does (alpha 1, beta 0) but passes over every output tile in which the mask holds
+ * nowhere (the counterpart of the reference's tileAllFalse pruning, src/kernel/avx2/sgemm.inl:449-475); a second pass
+ * writes masked_value wherever the mask does not hold. */
 int ytcuda_gemm_masked(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
                        int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc, int64_t batch,
                        int64_t bsa, int64_t bsb, int64_t bsc, const void* mask, int64_t mask_row_stride,
                        float masked_value, void* stream);
+
+/* The predicate form of YTensor::masked_matmul (src/ytensor_math.inl:368-412, sgemm_masked with a predicate,
+ * src/kernel/avx2/sgemm.inl:342-584) for the causal predicate, evaluated on the device: element (i, j) is computed iff
+ * j <= i + causal_offset. No mask is read; tiles entirely above the diagonal are skipped. Any other predicate is
+ * materialised into a bool matrix by the caller (device code cannot call a host lambda). */
+int ytcuda_gemm_masked_causal(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
+                              int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc,
+                              int64_t batch, int64_t bsa, int64_t bsb, int64_t bsc, int causal_offset,
+                              float masked_value, void* stream);
 
 /* ---------------------------------------------------------------- reductions over axes
  * All N-d entry points take `ndim` (1..8) extents and ELEMENT strides; `axes` lists the reduced axes
@@ -145,6 +165,12 @@ int ytcuda_softmax(int dt_in, int dt_out, const void* x, void* y, const int64_t*
 int ytcuda_rmsnorm(int dt_in, int dt_out, int dt_w, const void* x, const void* weight, void* y, const int64_t* shape,
                    const int64_t* xstrides, const int64_t* ystrides, int ndim, const int* axes, int naxes, float eps,
                    void* stream);
+
+/* y = x / (sum_axes |x|^p + eps)^(1/p): the Lp normalisation of yt::function::normalize / normalize_
+ * (include/function/normalization.hpp, src/function/normalization.inl:56-85, 278-318); p > 0. The affine forms apply
+ * gamma and bias afterwards with ytcuda_binary, as the reference's _applyScale_ / _applyBias_ do (:88-116). */
+int ytcuda_normalize(int dt_in, int dt_out, const void* x, void* y, const int64_t* shape, const int64_t* xstrides,
+                     const int64_t* ystrides, int ndim, const int* axes, int naxes, float p, float eps, void* stream);
 
 /* y = (x - mean) / sqrt(var + eps) * gamma + beta (gamma and beta both NULL for the plain form).
  * Replaces yt::function::layerNorm / layerNorm_ (include/function/normalization.hpp:8-53,
@@ -202,7 +228,8 @@ int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const v
 int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
                  const int64_t* xstrides, const int64_t* ystrides, float param, void* stream);
 
-/* Strided dtype conversion with the reference's own rounding: yt::bfloat16(float) adds half an ulp only when
+/* Strided dtype conversion with the reference's own rounding (the 8-bit types YTC_F8_* included, through the same
+ * FloatSpec rule as float16, include/types/float_spec.hpp:299-371, 435-491): yt::bfloat16(float) adds half an ulp only when
  * the kept LSB is 1 (include/types/bfloat16.hpp:78-80); yt::float16 rounds to nearest even and flushes results
  * below the smallest normal to zero (include/types/float_spec.hpp:435-491). Bit-exact with the reference.
  * Replaces YTensorBase::copy_ / cast (src/ytensor_base.inl:257-430, include/ytensor_base.hpp:399-404). */
@@ -326,9 +353,11 @@ int ytcuda_qwen3_tp_disconnect(void* handle);
 int ytcuda_qwen3_tp_resync(void* handle);
 /* ids [batch, len] int32 (device) -> logits of the last position [batch, rank's vocab rows] fp32 (device); appends
  * len tokens to the KV caches (Qwen3ForCausalLM::forward, qwen3.cpp:449-457). The caches are ring buffers as in the
- * reference (qwen3.cpp:70-126): once max_position_embeddings tokens are cached, a call with len == 1 overwrites the
- * oldest slot, attends to every slot and uses rotary position 0 (the reference's position rule, :365-375); a call
- * with len > 1 that would run past the end returns YTC_UNSUPPORTED. */
+ * reference (qwen3.cpp:70-126): a token written past the end overwrites the oldest slot. A call with len == 1 into a
+ * full cache attends to every slot and uses rotary position 0 (the reference's position rule, :365-375); a call with
+ * len > 1 that runs over the end appends all its tokens first and lets every query see the slots that are not younger
+ * than itself (KVCache::get_mask), with the rotary positions restarting at the cache length or at 0 as that rule
+ * says. len > max_position_embeddings returns YTC_UNSUPPORTED. */
 int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream);
 
 #ifdef __cplusplus

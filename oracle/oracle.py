@@ -132,6 +132,38 @@ class _Backend:
         assert rc == 0, rc
         return y
 
+    def norm(self, kind, x, axes, gamma=None, bias=None, groups=1, p=2.0, eps=1e-5):
+        """kind: 'normalize' (Lp over axes) | 'instanceNorm' | 'batchNorm' | 'groupNorm' (axes = [channel axis])
+        (reference yt::function::normalize / instanceNorm / batchNorm / groupNorm, src/function/normalization.inl:
+        278-577). Reference back-end only."""
+        x = _f32(x)
+        y = np.empty_like(x)
+        axes = _ints(np.atleast_1d(axes))
+        g = None if gamma is None else _f32(gamma)
+        b = None if bias is None else _f32(bias)
+        k = {"normalize": 0, "instanceNorm": 1, "batchNorm": 2, "groupNorm": 3}[kind]
+        rc = self._fn("norm_f32")(k, _opt(x), _opt(g), _opt(b), _opt(y), _opt(_ints(x.shape)), x.ndim, _opt(axes),
+                                  axes.size, int(groups), C.c_float(p), C.c_float(eps))
+        assert rc == 0, rc
+        return y
+
+    def fp8(self, kind, x):
+        """float32 -> bits of yt::float8_e5m2 / float8_e4m3 / float8_e8m0 (kind 'float8_e5m2' ...). Reference only."""
+        x = _f32(x)
+        out = np.empty(x.shape, np.uint8)
+        k = {"float8_e5m2": 3, "float8_e4m3": 4, "float8_e8m0": 5}[kind]
+        rc = self._fn("f32_to_fp8")(k, _opt(x), _opt(out), C.c_int64(x.size))
+        assert rc == 0, rc
+        return out
+
+    def fp8_to_f32(self, kind, bits):
+        bits = np.ascontiguousarray(bits, np.uint8)
+        out = np.empty(bits.shape, np.float32)
+        k = {"float8_e5m2": 3, "float8_e4m3": 4, "float8_e8m0": 5}[kind]
+        rc = self._fn("fp8_to_f32")(k, _opt(bits), _opt(out), C.c_int64(bits.size))
+        assert rc == 0, rc
+        return out
+
     def reduce(self, x, axes, op):
         """op: 'sum' | 'mean' | 'max'. Returns keep-dim result (and int32 indices for max)."""
         x = _f32(x)
@@ -258,6 +290,63 @@ class _Qwen3Handle:
 class PortOracle(_Backend):
     prefix = "yto_"
 
+    def norm(self, kind, x, axes, gamma=None, bias=None, groups=1, p=2.0, eps=1e-5):
+        """Restatement of yt::function::normalize / instanceNorm / batchNorm / groupNorm
+        (src/function/normalization.inl:56-116, 278-577) on top of the port's standardisation (layernorm without
+        affine) and broadcast operators: the channel norms standardise over the axes the reference's _instanceAxes /
+        _batchAxes name; groupNorm does it on the [n, groups, channels / groups, ...] view of the channel-first
+        tensor; gamma and bias are applied afterwards along the channel axis (or the single normalised axis)."""
+        x = _f32(x)
+        nd = x.ndim
+        axes = [int(a) % nd for a in np.atleast_1d(axes)]
+
+        def affine(y, ax):
+            if gamma is None:
+                return y
+            view = [1] * nd
+            view[ax] = x.shape[ax]
+            g, b = _f32(gamma).reshape(view), _f32(bias).reshape(view)
+            return self.binary(self.binary(y, np.broadcast_to(g, [1 if i != ax else x.shape[ax] for i in range(nd)]),
+                                           "mul"), b, "add")
+
+        if kind == "normalize":
+            ap = np.abs(x).astype(np.float32) ** np.float32(p)
+            s = self.reduce(ap.astype(np.float32), axes, "sum")
+            y = (x / (s + np.float32(eps)) ** np.float32(1.0 / p)).astype(np.float32)
+            return affine(y, axes[0]) if gamma is not None else y
+        c = axes[0]
+        if kind == "instanceNorm":
+            y = self.layernorm(x, None, None, [a for a in range(nd) if a not in (0, c)], eps)
+        elif kind == "batchNorm":
+            y = self.layernorm(x, None, None, [a for a in range(nd) if a != c], eps)
+        else:
+            xc = np.ascontiguousarray(np.moveaxis(x, c, 1))
+            grouped = xc.reshape((xc.shape[0], groups, xc.shape[1] // groups) + xc.shape[2:])
+            yg = self.layernorm(grouped, None, None, list(range(2, grouped.ndim)), eps)
+            y = np.ascontiguousarray(np.moveaxis(yg.reshape(xc.shape), 1, c))
+        return affine(y, c)
+
+    def fp8(self, kind, x):
+        x = _f32(x)
+        out = np.empty(x.shape, np.uint8)
+        rc = self.lib.yto_f32_to_fp8({"float8_e5m2": 3, "float8_e4m3": 4, "float8_e8m0": 5}[kind], _opt(x), _opt(out),
+                                     C.c_int64(x.size))
+        assert rc == 0, rc
+        return out
+
+    def fp8_to_f32(self, kind, bits):
+        bits = np.ascontiguousarray(bits, np.uint8)
+        out = np.empty(bits.shape, np.float32)
+        rc = self.lib.yto_fp8_to_f32({"float8_e5m2": 3, "float8_e4m3": 4, "float8_e8m0": 5}[kind], _opt(bits),
+                                     _opt(out), C.c_int64(bits.size))
+        assert rc == 0, rc
+        return out
+
+    def masked_matmul_causal(self, a, b, offset, masked_value=0.0):
+        m, n = np.asarray(a).shape[-2], np.asarray(b).shape[-1]
+        mask = np.arange(n)[None, :] <= np.arange(m)[:, None] + int(offset)
+        return self.masked_matmul(a, b, mask, masked_value)
+
     def __init__(self):
         if not PORT_LIB.exists():
             build_port()
@@ -346,6 +435,17 @@ class RefOracle(_Backend):
         c = np.empty((batch, m, n), np.float32)
         rc = self.lib.ytref_masked_matmul_f32(_opt(a3), _opt(b), _opt(mk), C.c_float(masked_value), _opt(c), batch, m,
                                               n, k, int(b.ndim == 3), backend)
+        assert rc == 0, rc
+        return c.reshape(a.shape[:-1] + (n,))
+
+    def masked_matmul_causal(self, a, b, offset, masked_value=0.0):
+        a, b = _f32(a), _f32(b)
+        a3 = a.reshape((-1,) + a.shape[-2:])
+        batch, m, k = a3.shape
+        n = b.shape[-1]
+        c = np.empty((batch, m, n), np.float32)
+        rc = self.lib.ytref_masked_matmul_causal_f32(_opt(a3), _opt(b), int(offset), C.c_float(masked_value), _opt(c),
+                                                     batch, m, n, k)
         assert rc == 0, rc
         return c.reshape(a.shape[:-1] + (n,))
 

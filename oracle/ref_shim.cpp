@@ -280,6 +280,44 @@ int ln_n(const float* x, const float* gamma, const float* beta, float* y, const 
   }
   return 0;
 }
+// kind 0 normalize (Lp over `axes`), 1 instanceNorm, 2 batchNorm, 3 groupNorm (channel axis = axes[0] for 1..3);
+// gamma / bias: per channel for 1..3, one dim (naxes == 1) for 0; null = the plain form.
+template <int N>
+int norm_n(int kind, const float* x, const float* gamma, const float* bias, float* y, const int* shape, const int* axes,
+           int naxes, int groups, float p, float eps) {
+  auto t = make<N>(x, shape);
+  std::vector<int> ax(axes, axes + naxes);
+  const int c = ((ax[0] % N) + N) % N;
+  const int ws[1] = {shape[c]};
+  YTensor<float, 1> g, b;
+  if (gamma) {
+    g = make<1>(gamma, ws);
+    b = make<1>(bias, ws);
+  }
+  switch (kind) {
+    case 0:
+      if (gamma) {
+        if (naxes != 1) return 2;
+        dump(yt::function::normalize(t, g, b, ax, p, eps), y);
+      } else {
+        dump(yt::function::normalize(t, ax, p, eps), y);
+      }
+      return 0;
+    case 1:
+      if (gamma) dump(yt::function::instanceNorm(t, g, b, ax[0], eps), y);
+      else dump(yt::function::instanceNorm(t, ax[0], eps), y);
+      return 0;
+    case 2:
+      if (gamma) dump(yt::function::batchNorm(t, g, b, ax[0], eps), y);
+      else dump(yt::function::batchNorm(t, ax[0], eps), y);
+      return 0;
+    case 3:
+      if (gamma) dump(yt::function::groupNorm(t, g, b, groups, ax[0], eps), y);
+      else dump(yt::function::groupNorm(t, groups, ax[0], eps), y);
+      return 0;
+    default: return 2;
+  }
+}
 template <int N>
 int reduce_n(const float* x, float* y, int* idx, const int* shape, const int* axes, int naxes, int op) {
   auto t = make<N>(x, shape);
@@ -345,6 +383,45 @@ int ytref_layernorm_f32(const float* x, const float* gamma, const float* beta, f
 #define CALL(N) ln_n<N>(x, gamma, beta, y, shape, axes, naxes, eps)
   RANK_SWITCH(ndim, CALL)
 #undef CALL
+}
+int ytref_norm_f32(int kind, const float* x, const float* gamma, const float* bias, float* y, const int* shape,
+                   int ndim, const int* axes, int naxes, int groups, float p, float eps) {
+#define CALL(N) norm_n<N>(kind, x, gamma, bias, y, shape, axes, naxes, groups, p, eps)
+  RANK_SWITCH(ndim, CALL)
+#undef CALL
+}
+// The reference's 8-bit float types (include/types/float_spec.hpp:534-536): kind 3 e5m2, 4 e4m3, 5 e8m0.
+int ytref_f32_to_fp8(int kind, const float* x, uint8_t* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    if (kind == 3) { yt::float8_e5m2 v(x[i]); std::memcpy(out + i, &v, 1); }
+    else if (kind == 4) { yt::float8_e4m3 v(x[i]); std::memcpy(out + i, &v, 1); }
+    else if (kind == 5) { yt::float8_e8m0 v(x[i]); std::memcpy(out + i, &v, 1); }
+    else return 2;
+  }
+  return 0;
+}
+int ytref_fp8_to_f32(int kind, const uint8_t* in, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    if (kind == 3) { yt::float8_e5m2 v; std::memcpy(&v, in + i, 1); out[i] = static_cast<float>(v); }
+    else if (kind == 4) { yt::float8_e4m3 v; std::memcpy(&v, in + i, 1); out[i] = static_cast<float>(v); }
+    else if (kind == 5) { yt::float8_e8m0 v; std::memcpy(&v, in + i, 1); out[i] = static_cast<float>(v); }
+    else return 2;
+  }
+  return 0;
+}
+// masked_matmul with the causal predicate j <= i + offset (tile-pruning form, src/ytensor_math.inl:368-412)
+int ytref_masked_matmul_causal_f32(const float* a, const float* b, int offset, float masked_value, float* c, int batch,
+                                   int m, int n, int k) {
+  try {
+    const int as[3] = {batch, m, k}, bs[2] = {k, n};
+    auto ta = make<3>(a, as);
+    auto tb = make<2>(b, bs);
+    CausalPred pred{offset};
+    dump(ta.masked_matmul(tb, pred, masked_value), c);
+    return 0;
+  } catch (const std::exception&) {
+    return 1;
+  }
 }
 // op: 0 sum, 1 mean, 2 max (idx receives the int index tensor, may be null)
 int ytref_reduce_f32(const float* x, float* y, int* idx, const int* shape, int ndim, const int* axes, int naxes,

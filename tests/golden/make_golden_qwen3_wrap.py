@@ -1,7 +1,8 @@
 """Generates tests/golden/golden_qwen3_wrap.npz: the reference decoder (unmodified, behind oracle/ref_shim.cpp) run
 past the end of its KV cache, which is a ring buffer (example/qwen3/src/qwen3.cpp:70-126): a 9-token prompt and 19
 single-token steps with max_position_embeddings = 16, so the cache fills at step 7 and the later steps overwrite the
-oldest slots. Run from the repository root: make -C oracle ref && python tests/golden/make_golden_qwen3_wrap.py
+oldest slots; and a second run that feeds SEVERAL tokens per call across the end of the ring (two sequences).
+Run from the repository root: make -C oracle ref && python tests/golden/make_golden_qwen3_wrap.py
 """
 from __future__ import annotations
 
@@ -31,7 +32,16 @@ def main():
     for _ in range(19):
         logits.append(m.forward(logits[-1].argmax(1).astype(np.int32).reshape(1, 1)))
     m.close()
-    np.savez_compressed(OUT, wrap_ids=ids, wrap_logits=np.stack(logits))  # [20, 1, vocab]
+    # several tokens per call across the end of the ring: 9 + 5 (fits), + 6 (runs over the end), + 3 (already full),
+    # + 1, + 10 (more than half the ring), for two sequences
+    m = R.qwen3(cfg.oracle_dict(), 2)
+    load(m, w)
+    rng = np.random.default_rng(22)
+    chunks = [rng.integers(0, cfg.vocab_size, (2, n)).astype(np.int32) for n in (9, 5, 6, 3, 1, 10)]
+    multi = [m.forward(c) for c in chunks]
+    m.close()
+    extra = {f"multi_ids_{i}": c for i, c in enumerate(chunks)}
+    np.savez_compressed(OUT, wrap_ids=ids, wrap_logits=np.stack(logits), multi_logits=np.stack(multi), **extra)
     print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB)")
 
 

@@ -152,8 +152,27 @@ def test_ring_buffer_cache_past_its_end_matches_reference(Q, path):
         assert m.get_kv_cache_len() == min(9 + step, 16)
         if step < 19:
             logits = m.forward(dev_ids(want[step].argmax(1).reshape(1, 1)))
-    with pytest.raises(_lib.YtCudaInvalidArgument):  # several tokens at once past the end: refused
-        m.forward(dev_ids(np.zeros((1, 3), np.int32)))
+    with pytest.raises(_lib.YtCudaInvalidArgument):  # more tokens at once than the ring has slots: refused
+        m.forward(dev_ids(np.zeros((1, 17), np.int32)))
+    m.close()
+
+
+def test_several_tokens_per_call_across_the_end_of_the_ring(Q):
+    """A forward of several tokens that runs over the end of the cache: every token is appended (the later ones
+    overwrite the oldest slots), each query sees the slots that are not younger than itself, and the rotary positions
+    restart as in Qwen3Model::forward (reference qwen3.cpp:70-126, 365-375). Golden logits: calls of 9, 5, 6, 3, 1 and
+    10 tokens into a ring of 16 slots, two sequences."""
+    from pathlib import Path
+    g = np.load(Path(__file__).resolve().parent / "golden" / "golden_qwen3_wrap.npz")
+    cfg = Q.Qwen3Config(**{**SMALL, "max_position_embeddings": 16})
+    m = Q.Qwen3ForCausalLM(cfg, batch=2)
+    m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
+    want = g["multi_logits"]
+    for i in range(want.shape[0]):
+        got = m.forward(dev_ids(g[f"multi_ids_{i}"])).cpu().numpy()
+        assert normwise(got, want[i]) < 1e-4, i
+        assert np.array_equal(got.argmax(1), want[i].argmax(1)), i
+    assert m.get_kv_cache_len() == 16
     m.close()
 
 
@@ -163,8 +182,10 @@ def test_cache_overflow_is_reported(Q):
     m = Q.Qwen3ForCausalLM(cfg, batch=1)
     m.load_weights(Q.random_weights(cfg, seed=4, std=0.05))
     m.forward(dev_ids(np.zeros((1, 60), np.int32)))
-    with pytest.raises(_lib.YtCudaInvalidArgument):  # the device has no ring-buffer wrap: it refuses instead
-        m.forward(dev_ids(np.zeros((1, 5), np.int32)))
+    m.forward(dev_ids(np.zeros((1, 5), np.int32)))  # runs over the end of the 64-slot ring: allowed
+    assert m.get_kv_cache_len() == 64
+    with pytest.raises(_lib.YtCudaInvalidArgument):  # more tokens than the ring has slots
+        m.forward(dev_ids(np.zeros((1, 65), np.int32)))
     m.close()
 
 

@@ -177,3 +177,46 @@ def test_port_matches_reference_live(port, ref):
     v = rng.standard_normal((1, 2, 70, 64)).astype(np.float32)
     assert normwise(port.sdpa(q, k, v, causal=True), ref.sdpa(q, k, v, causal=True)) < 1e-6
     assert normwise(port.sdpa(q, k, v, causal=True), ref.sdpa(q, k, v, causal=True, backend=0)) < 1e-5
+
+
+# ------------------------------------------------------------------ later operators (golden_ext.npz)
+@pytest.fixture(scope="module")
+def golden_ext():
+    from pathlib import Path
+    return np.load(Path(__file__).resolve().parent / "golden" / "golden_ext.npz")
+
+
+@pytest.mark.parametrize("kind", ["float8_e5m2", "float8_e4m3", "float8_e8m0"])
+def test_port_fp8_conversions_are_the_references(port, golden_ext, kind):
+    assert np.array_equal(port.fp8(kind, golden_ext["fp8_in"]), golden_ext[f"fp8_{kind}_bits"])
+    table = port.fp8_to_f32(kind, np.arange(256, dtype=np.uint8))
+    assert np.array_equal(table.view(np.uint32), golden_ext[f"fp8_{kind}_table"].view(np.uint32))
+
+
+def test_port_norm_family_matches_reference(port, golden_ext):
+    g = golden_ext
+    X = g["norm_x"]
+    exact = [
+        (port.norm("normalize", X, [-1], p=2.0, eps=1e-12), "norm_l2_m1"),
+        (port.norm("normalize", X, [1], g["norm_gamma6"], g["norm_bias6"], p=2.0, eps=1e-12), "norm_l2_a1_affine"),
+        (port.norm("instanceNorm", X, [1]), "norm_inst_c1"),
+        (port.norm("instanceNorm", X, [1], g["norm_gamma6"], g["norm_bias6"]), "norm_inst_c1_affine"),
+        (port.norm("instanceNorm", X, [2], g["norm_gamma5"], g["norm_bias5"]), "norm_inst_c2_affine"),
+        (port.norm("batchNorm", X, [1]), "norm_batch_c1"),
+        (port.norm("batchNorm", X, [1], g["norm_gamma6"], g["norm_bias6"]), "norm_batch_c1_affine"),
+        (port.norm("batchNorm", X, [-1]), "norm_batch_cm1"),
+        (port.norm("groupNorm", X, [1], groups=2), "norm_group2_c1"),
+        (port.norm("groupNorm", X, [1], g["norm_gamma6"], g["norm_bias6"], groups=3), "norm_group3_c1_affine"),
+        (port.norm("groupNorm", g["norm_xg"], [2], g["norm_gamma4"], g["norm_bias4"], groups=2), "norm_group2_c2_affine"),
+    ]
+    for got, name in exact:
+        assert np.array_equal(got, g[name]), name
+    # p = 1.5 goes through pow(): one ulp of libm against numpy
+    got = port.norm("normalize", X, [1, 3], p=1.5, eps=1e-6)
+    assert np.abs(got - g["norm_l15_a13"]).max() / np.abs(g["norm_l15_a13"]).max() < 1e-6
+
+
+def test_port_causal_masked_matmul_matches_reference(port, golden_ext):
+    g = golden_ext
+    assert np.array_equal(port.masked_matmul_causal(g["mmc_a"], g["mmc_b"], 0, -1e9), g["mmc_off0"])
+    assert np.array_equal(port.masked_matmul_causal(g["mmc_a"], g["mmc_b"], 20, 0.5), g["mmc_off20"])

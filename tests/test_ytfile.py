@@ -123,3 +123,15 @@ def test_decoder_loaded_from_yt_matches_decoder_loaded_from_arrays(tmp_path):
         e = f.to_device("model.embed_tokens.weight")
         assert e.dtype == torch.bfloat16 and tuple(e.shape) == (cfg.vocab_size, cfg.hidden_size)
         assert np.array_equal(e.view(torch.int16).cpu().numpy().view(np.uint16), w["embed"])
+
+
+def test_unknown_compression_name_falls_back_to_none(tmp_path):
+    """The reference names "zlibfloat" in a comment but implements only "" and "zlib": checkCompressMethod turns any
+    other name into "no compression" (src/ytensor_io.inl:11-22). Writer and reader here do the same."""
+    from ytensor_b200 import ytfile
+    a = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    p = tmp_path / "zf.yt"
+    ytfile.write_yt(p, {"a": a}, compress="zlibfloat")
+    with ytfile.YtFile(p) as f:
+        assert f.record("a").compress == ""
+        assert np.array_equal(f.load("a"), a)

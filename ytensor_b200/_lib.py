@@ -10,7 +10,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libytensor_cuda.so"
 
 OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, TIMEOUT, NOT_IMPLEMENTED = range(6)
-F32, BF16, F16 = 0, 1, 2
+F32, BF16, F16, F8_E5M2, F8_E4M3, F8_E8M0 = 0, 1, 2, 3, 4, 5
 
 _i, _i64, _f, _vp, _u64 = C.c_int, C.c_int64, C.c_float, C.c_void_p, C.c_uint64
 
@@ -34,6 +34,7 @@ SIGNATURES = {
     "ytcuda_wait_probe": (_i, [_vp, _vp]),
     "ytcuda_gemm": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4 + [_vp]),
     "ytcuda_gemm_masked": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i] + [_i64] * 6 + [_i64] * 4 + [_vp, _i64, _f, _vp]),
+    "ytcuda_gemm_masked_causal": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i] + [_i64] * 6 + [_i64] * 4 + [_i, _f, _vp]),
     "ytcuda_gemm_set_path": (_i, [_i]),
     "ytcuda_gemm_set_f32_mode": (_i, [_i]),
     "ytcuda_gemm_set_tuning": (_i, [_i, _i]),
@@ -41,6 +42,7 @@ SIGNATURES = {
     "ytcuda_gemm_host": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f] + [_i64] * 6 + [_i64] * 4),
     "ytcuda_softmax": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "ytcuda_rmsnorm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp]),
+    "ytcuda_normalize": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _f, _vp]),
     "ytcuda_layernorm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _f, _vp]),
     "ytcuda_reduce": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "ytcuda_reduce_noalloc": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),

@@ -92,14 +92,32 @@ def matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *,
     return out
 
 
-def masked_matmul(a: torch.Tensor, b: torch.Tensor, mask: torch.Tensor, masked_value: float = 0.0, *,
-                  out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """C[..., i, j] = (A . B)[..., i, j] where mask[i, j], masked_value elsewhere; mask is bool [m, n].
+class Causal:
+    """The predicate j <= i + offset, for the predicate forms of masked_matmul and scaledDotProductAttention
+    (reference src/ytensor_math.inl:368-412, src/function/ops.inl:427-503): evaluated on the device, no mask tensor."""
 
-    Mirrors YTensor<T,dim>::masked_matmul with a bool mask (reference src/ytensor_math.inl:318-366): a mask of
-    another shape is refused as the reference refuses it (std::invalid_argument, here ValueError).
+    def __init__(self, offset: int = 0):
+        self.offset = int(offset)
+
+    def __call__(self, i: int, j: int) -> bool:
+        return j <= i + self.offset
+
+
+def masked_matmul(a: torch.Tensor, b: torch.Tensor, mask, masked_value: float = 0.0, *,
+                  out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """C[..., i, j] = (A . B)[..., i, j] where mask[i, j], masked_value elsewhere; mask is bool [m, n], a `Causal`
+    predicate (evaluated on the device), or any callable (i, j) -> bool (materialised once into a bool mask).
+
+    Mirrors YTensor<T,dim>::masked_matmul with a bool mask or a predicate (reference src/ytensor_math.inl:318-412): a
+    mask of another shape is refused as the reference refuses it (std::invalid_argument, here ValueError). Output
+    tiles in which the mask holds nowhere are not computed.
     """
-    _require_cuda(a, b, mask)
+    causal = mask if isinstance(mask, Causal) else None
+    if causal is None and callable(mask) and not isinstance(mask, torch.Tensor):
+        mm, nn = a.shape[-2], b.shape[-1]
+        mask = torch.tensor([[bool(mask(i, j)) for j in range(nn)] for i in range(mm)], dtype=torch.bool,
+                            device=a.device)
+    _require_cuda(a, b, None if causal else mask)
     if a.dim() < 2 or b.dim() < 2:
         raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "masked_matmul: operands must have at least 2 dims")
     if a.shape[-1] != b.shape[-2]:
@@ -107,11 +125,12 @@ def masked_matmul(a: torch.Tensor, b: torch.Tensor, mask: torch.Tensor, masked_v
             _lib.INVALID_ARG, f"masked_matmul: inner dims differ ({a.shape[-1]} vs {b.shape[-2]})")
     m, k = a.shape[-2:]
     n = b.shape[-1]
-    if mask.dtype != torch.bool or tuple(mask.shape) != (m, n):
-        raise _lib.YtCudaInvalidArgument(
-            _lib.INVALID_ARG, f"masked_matmul: mask must be bool [{m}, {n}], got {mask.dtype} {tuple(mask.shape)}")
-    if mask.stride(1) != 1:
-        mask = mask.contiguous()
+    if causal is None:
+        if mask.dtype != torch.bool or tuple(mask.shape) != (m, n):
+            raise _lib.YtCudaInvalidArgument(
+                _lib.INVALID_ARG, f"masked_matmul: mask must be bool [{m}, {n}], got {mask.dtype} {tuple(mask.shape)}")
+        if mask.stride(1) != 1:
+            mask = mask.contiguous()
     bshape = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
     ae, be = a.expand(*bshape, m, k), b.expand(*bshape, k, n)
     out = torch.empty(*bshape, m, n, dtype=out_dtype or a.dtype, device=a.device)
@@ -121,6 +140,12 @@ def masked_matmul(a: torch.Tensor, b: torch.Tensor, mask: torch.Tensor, masked_v
             out[idx] = masked_matmul(ae[idx], be[idx], mask, masked_value, out_dtype=out_dtype)
         return out
     batch = builtins.max(av[0], bv[0], ov[0])
+    if causal is not None:
+        check(lib().ytcuda_gemm_masked_causal(_dt(ae), _dt(out), ae.data_ptr(), be.data_ptr(), out.data_ptr(), m, n, k,
+                                              ae.stride(-2), ae.stride(-1), be.stride(-2), be.stride(-1),
+                                              out.stride(-2), out.stride(-1), batch, av[1], bv[1], ov[1],
+                                              causal.offset, float(masked_value), _stream()))
+        return out
     check(lib().ytcuda_gemm_masked(_dt(ae), _dt(out), ae.data_ptr(), be.data_ptr(), out.data_ptr(), m, n, k,
                                    ae.stride(-2), ae.stride(-1), be.stride(-2), be.stride(-1), out.stride(-2),
                                    out.stride(-1), batch, av[1], bv[1], ov[1], mask.data_ptr(), mask.stride(0),
@@ -219,6 +244,113 @@ def layerNorm(x: torch.Tensor, gamma: torch.Tensor | None = None, bias: torch.Te
 
 def layerNorm_(x, gamma=None, bias=None, axes=-1, eps: float = 1e-5):
     return layerNorm(x, gamma, bias, axes, eps, out=x)
+
+
+def _affine_(y: torch.Tensor, gamma, bias, axes) -> torch.Tensor:
+    """y *= gamma; y += bias with gamma / bias holding one dim per axis (the reference's _applyScale_ / _applyBias_,
+    src/function/normalization.inl:88-116, through _makeAffineView)."""
+    if gamma is None and bias is None:
+        return y
+    if gamma is None or bias is None:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "gamma and bias come together")
+    ax = [a % y.dim() for a in axes]
+    want = [y.shape[a] for a in ax]
+    if list(gamma.shape) != want or list(bias.shape) != want:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "gamma/bias shape must match affine axes")
+    # the reference views the affine tensor's MEMORY with the axis sizes in ascending axis order, whatever order the
+    # axes were listed in (src/ytensor_function.inl:137-158): a plain reshape of the contiguous tensor does the same
+    view = [1] * y.dim()
+    for a in ax:
+        view[a] = y.shape[a]
+    g = gamma.contiguous().reshape(view)
+    b = bias.contiguous().reshape(view)
+    _binary("mul", y, g.to(y.dtype), y)
+    _binary("add", y, b.to(y.dtype), y)
+    return y
+
+
+def normalize(x: torch.Tensor, axes=-1, p: float = 2.0, eps: float = 1e-12, gamma=None, bias=None,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """x / (sum_axes |x|^p + eps)^(1/p) [* gamma + bias] (reference yt::function::normalize,
+    src/function/normalization.inl:56-85, 278-372)."""
+    _require_cuda(x, gamma, bias, out)
+    if p <= 0:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "yt::function::normalize: p must be positive")
+    ax = _axes(axes)
+    y = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
+    xx, shape, xs = _nd(x)
+    check(lib().ytcuda_normalize(_dt(x), _dt(y), x.data_ptr(), y.data_ptr(), shape, xs, _i64(y.stride() or (1,)),
+                                 xx.dim(), _i32(ax), len(ax), float(p), float(eps), _stream()))
+    return _affine_(y, gamma, bias, ax)
+
+
+def normalize_(x, axes=-1, p: float = 2.0, eps: float = 1e-12, gamma=None, bias=None):
+    return normalize(x, axes, p, eps, gamma, bias, out=x)
+
+
+def _channel_axis(x: torch.Tensor, channelAxis: int, who: str) -> int:
+    c = channelAxis % x.dim()
+    if x.dim() < 2:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, f"{who} requires dim >= 2")
+    if c == 0:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, f"{who}: channelAxis must not be batch axis 0")
+    return c
+
+
+def instanceNorm(x: torch.Tensor, gamma=None, bias=None, channelAxis: int = 1, eps: float = 1e-5,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+    """Standardises every (sample, channel) over the remaining axes (reference yt::function::instanceNorm,
+    src/function/normalization.inl:378-433); gamma / bias are per channel."""
+    c = _channel_axis(x, channelAxis, "yt::function::instanceNorm_")
+    axes = [a for a in range(x.dim()) if a not in (0, c)]
+    if not axes:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "yt::function::instanceNorm: requires at least one spatial axis")
+    y = layerNorm(x, None, None, axes, eps, out=out)
+    return _affine_(y, gamma, bias, [c])
+
+
+def instanceNorm_(x, gamma=None, bias=None, channelAxis: int = 1, eps: float = 1e-5):
+    return instanceNorm(x, gamma, bias, channelAxis, eps, out=x)
+
+
+def batchNorm(x: torch.Tensor, gamma=None, bias=None, channelAxis: int = 1, eps: float = 1e-5,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """Standardises every channel over all other axes, batch included (reference yt::function::batchNorm,
+    src/function/normalization.inl:435-489: statistics of the tensor itself, no running averages)."""
+    c = _channel_axis(x, channelAxis, "yt::function::batchNorm_")
+    axes = [a for a in range(x.dim()) if a != c]
+    y = layerNorm(x, None, None, axes, eps, out=out)
+    return _affine_(y, gamma, bias, [c])
+
+
+def batchNorm_(x, gamma=None, bias=None, channelAxis: int = 1, eps: float = 1e-5):
+    return batchNorm(x, gamma, bias, channelAxis, eps, out=x)
+
+
+def groupNorm(x: torch.Tensor, groups: int, gamma=None, bias=None, channelAxis: int = 1, eps: float = 1e-5,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """Standardises every (sample, group of channels) over the group's channels and the remaining axes (reference
+    yt::function::groupNorm, src/function/normalization.inl:491-577). The reference permutes the channel axis to the
+    front and copies; here the grouped tensor is a strided VIEW [n, groups, channels / groups, ...] of x and of the
+    output, handed to the generic-axes kernel as it is."""
+    c = _channel_axis(x, channelAxis, "yt::function::groupNorm_")
+    if groups <= 0:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "yt::function::groupNorm: groups must be positive")
+    ch = x.shape[c]
+    if ch % groups:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG,
+                                         "yt::function::groupNorm: channel count must be divisible by groups")
+    if x.dim() + 1 > 8:
+        raise _lib.YtCudaInvalidArgument(_lib.UNSUPPORTED, "groupNorm: at most 7 dims")
+    y = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
+    xg = x.movedim(c, 1).unflatten(1, (groups, ch // groups))
+    yg = y.movedim(c, 1).unflatten(1, (groups, ch // groups))
+    layerNorm(xg, None, None, list(range(2, xg.dim())), eps, out=yg)
+    return _affine_(y, gamma, bias, [c])
+
+
+def groupNorm_(x, groups: int, gamma=None, bias=None, channelAxis: int = 1, eps: float = 1e-5):
+    return groupNorm(x, groups, gamma, bias, channelAxis, eps, out=x)
 
 
 def rmsnorm_add_softmax_cast(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
@@ -371,6 +503,35 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _require_cuda(x)
     out = torch.empty(x.shape, dtype=dtype, device=x.device)
     return copy_(out, x)
+
+
+FP8_KINDS = {"float8_e5m2": _lib.F8_E5M2, "float8_e4m3": _lib.F8_E4M3, "float8_e8m0": _lib.F8_E8M0}
+
+
+def cast_to_fp8(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """float / bfloat16 / float16 -> the reference's 8-bit storage types (yt::float8_e5m2, float8_e4m3, float8_e8m0,
+    include/types/float_spec.hpp:534-536) as uint8 bit patterns, with FloatSpec::fromFloat32's rounding (:435-491).
+    These are the reference's own formats (the largest exponent is infinity / NaN), not the OCP fn variants, so the
+    result is a uint8 tensor rather than a torch float8 dtype."""
+    _require_cuda(x)
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    s_, d = (x.reshape(1), out.reshape(1)) if x.dim() == 0 else (x, out)
+    check(lib().ytcuda_cast(_dt(x), FP8_KINDS[kind], s_.data_ptr(), d.data_ptr(), d.dim(), _i64(d.shape),
+                            _i64(s_.stride()), _i64(d.stride()), _stream()))
+    return out
+
+
+def cast_from_fp8(bits: torch.Tensor, kind: str, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """uint8 bit patterns of one of the reference's 8-bit types -> float / bfloat16 / float16 (FloatSpec::toFloat32,
+    include/types/float_spec.hpp:299-371, then the target type's own constructor)."""
+    _require_cuda(bits)
+    if bits.dtype != torch.uint8:
+        raise _lib.YtCudaInvalidArgument(_lib.INVALID_ARG, "cast_from_fp8: uint8 bit patterns expected")
+    out = torch.empty(bits.shape, dtype=dtype, device=bits.device)
+    s_, d = (bits.reshape(1), out.reshape(1)) if bits.dim() == 0 else (bits, out)
+    check(lib().ytcuda_cast(FP8_KINDS[kind], _dt(out), s_.data_ptr(), d.data_ptr(), d.dim(), _i64(d.shape),
+                            _i64(s_.stride()), _i64(d.stride()), _stream()))
+    return out
 
 
 def copy_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:

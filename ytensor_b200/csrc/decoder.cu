@@ -313,7 +313,8 @@ __global__ void __launch_bounds__(256) sum_swiglu_split_kernel(const float* part
 // ------------------------------------------------------------------ per-head RMSNorm + RoPE + KV append
 // qkv [B, L, (H + 2*KVH) * D] fp32 (the fused projection output). One warp per (b, t, head) vector, D == 128:
 //   q heads: rmsNorm over D with q_norm, rotate-half RoPE at position pos0 + t -> q_out [B, H, L, D]
-//   k heads: rmsNorm with k_norm, RoPE -> k_cache [B, KVH, max_len, D] at slot slot0 + t
+//   k heads: rmsNorm with k_norm, RoPE -> k_cache [B, KVH, max_len, D] at slot (slot0 + t) % max_len (the cache is a
+//            ring buffer: KVCache::append, qwen3.cpp:70-88)
 //   v heads: copy -> v_cache at the same slot
 // (reference qwen3.cpp:237-247: slice/reshape/permute, HeadRMSNorm, ops::rope, KVCache::append; rope math :522-559).
 __global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* q_out, float* k_cache, float* v_cache,
@@ -343,7 +344,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* 
       for (int i = 0; i < 4; ++i) x[i] = src[lane + 32 * i];
     }
     if (hh >= H + KVH) {  // value head
-      float* dst = v_cache + ((static_cast<int64_t>(b) * KVH + (hh - H - KVH)) * max_len + slot0 + t) * D;
+      float* dst = v_cache + ((static_cast<int64_t>(b) * KVH + (hh - H - KVH)) * max_len + (slot0 + t) % max_len) * D;
 #pragma unroll
       for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = x[i];
       continue;
@@ -371,7 +372,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* 
       y[i + 2] = im * c + re * s;
     }
     float* dst = is_q ? q_out + ((static_cast<int64_t>(b) * H + hh) * L + t) * D
-                      : k_cache + ((static_cast<int64_t>(b) * KVH + (hh - H)) * max_len + slot0 + t) * D;
+                      : k_cache + ((static_cast<int64_t>(b) * KVH + (hh - H)) * max_len + (slot0 + t) % max_len) * D;
 #pragma unroll
     for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = y[i];
   }
@@ -411,6 +412,8 @@ struct Qwen3Model {
   void* allreduce_user = nullptr;
   // single-kernel decode step (decode_step.cuh)
   int decode_path = 0;              // 0 automatic, 1 one launch per operator, 2 the persistent step kernel or fail
+  uint8_t* ring_mask = nullptr;     // [len, max_pos] visibility of a multi-token forward that wraps the ring buffer
+  size_t ring_mask_bytes = 0;
   long long* trace = nullptr;       // optional timeline buffer of the step kernel (ytcuda_qwen3_set_trace)
   char* ll_buf = nullptr;           // pair buffers of the barrier-free step kernel (decode_ll.cuh) + unit counters
   size_t ll_bytes = 0;
@@ -628,8 +631,10 @@ static int qkv_post_launch(const float* qkv, int n_part, int64_t mn, float* q_ou
   }
   YTC_REQUIRE(qkv && q_out && k_cache && v_cache && q_norm && k_norm && cos_table && sin_table,
               "ytcuda_qwen3_qkv_post: null tensor");
-  YTC_REQUIRE(slot0 >= 0 && slot0 + len <= max_len, "ytcuda_qwen3_qkv_post: %d new tokens do not fit the cache at slot %d of %d",
-              len, slot0, max_len);
+  YTC_REQUIRE(slot0 >= 0 && slot0 < max_len && len <= max_len,
+              "ytcuda_qwen3_qkv_post: %d new tokens at slot %d do not fit a ring of %d slots", len, slot0, max_len);
+  YTC_REQUIRE(pos0 >= 0 && pos0 + len <= max_len, "ytcuda_qwen3_qkv_post: rotary positions %d .. %d outside the table of %d",
+              pos0, pos0 + len - 1, max_len);
   const int64_t vecs = static_cast<int64_t>(batch) * len * (heads + 2 * kv_heads);
   const int64_t blocks = (vecs + 3) / 4;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
@@ -647,6 +652,19 @@ int ytcuda_qwen3_qkv_post(const float* qkv, float* q_out, float* k_cache, float*
                           void* stream) {
   return qkv_post_launch(qkv, 0, 0, q_out, k_cache, v_cache, q_norm, k_norm, cos_table, sin_table, batch, len, heads,
                          kv_heads, head_dim, max_len, pos0, slot0, eps, stream);
+}
+
+// mask[qi][ki] of KVCache::get_mask for a full ring (reference qwen3.cpp:100-126): slot ki holds the token of logical
+// age (ki - write_pos + max_len) % max_len (0 = oldest), query qi of the len new tokens has logical position
+// max_len - len + qi, and sees the slots that are not younger than itself.
+__global__ void ring_mask_kernel(uint8_t* mask, int len, int max_len, int write_pos) {
+  const int64_t total = static_cast<int64_t>(len) * max_len;
+  for (int64_t e = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; e < total;
+       e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int qi = static_cast<int>(e / max_len), ki = static_cast<int>(e - static_cast<int64_t>(qi) * max_len);
+    const int k_logical = (ki - write_pos + max_len) % max_len;
+    mask[e] = k_logical <= max_len - len + qi ? 1 : 0;
+  }
 }
 
 // ---------------------------------------------------------------- model handle
@@ -1093,10 +1111,11 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   // Qwen3Model::forward, :365-375, falls back to 0 when the running position no longer fits the table). The device
   // follows that for one new token per call; a longer input that would run over the end of the cache is refused.
   const bool wrap_step = len == 1 && m->total_written >= m->max_pos;
-  if (!wrap_step && m->total_written + len > m->max_pos) {
-    set_last_error("ytcuda_qwen3_forward: %lld cached + %d new tokens exceed max_position_embeddings %d (past the end "
-                   "of the cache the device takes one token per call, as the ring buffer of the reference does)",
-                   static_cast<long long>(m->total_written), len, m->max_pos);
+  // several tokens that run over the end of the ring: every token is appended (the later ones overwrite the oldest
+  // slots), then each query sees the slots that are not younger than itself (KVCache::append / get_mask, :70-126)
+  const bool ring_multi = !wrap_step && m->total_written + len > m->max_pos;
+  if (ring_multi && len > m->max_pos) {
+    set_last_error("ytcuda_qwen3_forward: %d new tokens do not fit a cache of %d slots", len, m->max_pos);
     return YTC_UNSUPPORTED;
   }
   YTC_REQUIRE(m->embed && m->lm_head && m->final_norm, "ytcuda_qwen3_forward: embed / lm_head / norm not set");
@@ -1112,9 +1131,28 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   int s = ensure_activations(m, rows);
   if (s != YTC_OK) return s;
   // rotary position of the first new token, the slot it is written to, and the keys visible after the append
-  const int pos0 = wrap_step ? 0 : static_cast<int>(m->total_written);
+  // rotary position of the first new token (Qwen3Model::forward, :365-375): the running position while it fits the
+  // table, else the cache length, else 0
+  int pos0 = wrap_step ? 0 : static_cast<int>(m->total_written);
+  if (ring_multi) pos0 = m->cur_len + len <= m->max_pos ? m->cur_len : 0;
   const int slot0 = static_cast<int>(m->total_written % m->max_pos);
-  const int kv_len = wrap_step ? m->max_pos : pos0 + len;
+  const int kv_len = (wrap_step || ring_multi) ? m->max_pos : pos0 + len;
+  int mask_kind = wrap_step ? 0 : 1;
+  const uint8_t* mask_ptr = nullptr;
+  if (ring_multi) {
+    const size_t need = static_cast<size_t>(len) * m->max_pos;
+    if (m->ring_mask_bytes < need) {
+      if ((s = dev_alloc(m, reinterpret_cast<void**>(&m->ring_mask), need)) != YTC_OK) return s;
+      m->ring_mask_bytes = need;
+    }
+    const int write_pos = static_cast<int>((m->total_written + len) % m->max_pos);
+    ring_mask_kernel<<<static_cast<unsigned>((need + 255) / 256 < 1024 ? (need + 255) / 256 : 1024), 256, 0, st>>>(
+        m->ring_mask, len, m->max_pos, write_pos);
+    count_launch();
+    YTC_CUDA(cudaGetLastError());
+    mask_kind = 2;
+    mask_ptr = m->ring_mask;
+  }
   auto advance = [&]() {
     m->total_written += len;
     m->cur_len = m->total_written < m->max_pos ? static_cast<int>(m->total_written) : m->max_pos;
@@ -1158,7 +1196,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
       const int64_t ks[3] = {static_cast<int64_t>(m->l_kv_heads) * m->max_pos * D, static_cast<int64_t>(m->max_pos) * D, D};
       const int64_t os[3] = {static_cast<int64_t>(len) * m->l_heads * D, D, static_cast<int64_t>(m->l_heads) * D};
       if ((s = ytcuda_flash_attn_fwd(YTC_F32, m->q, kc, vc, m->attn, B, m->l_kv_heads, groups, len, kv_len, D, D, scale,
-                                     qs, ks, ks, os, wrap_step ? 0 : 1, kv_len - len, nullptr, 0, nullptr, 0, 0, st)) !=
+                                     qs, ks, ks, os, mask_kind, kv_len - len, mask_ptr, m->max_pos, nullptr, 0, 0, st)) !=
           YTC_OK)
         return s;
       if ((s = split_planes(m, m->attn, m->l_heads * D, rows, m->l_heads * D, st)) != YTC_OK) return s;
@@ -1194,7 +1232,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     const int64_t ks[3] = {static_cast<int64_t>(m->l_kv_heads) * m->max_pos * D, static_cast<int64_t>(m->max_pos) * D, D};
     const int64_t os[3] = {static_cast<int64_t>(len) * m->l_heads * D, D, static_cast<int64_t>(m->l_heads) * D};
     if ((s = ytcuda_flash_attn_fwd(YTC_F32, m->q, kc, vc, m->attn, B, m->l_kv_heads, groups, len, kv_len, D, D, scale, qs,
-                                   ks, ks, os, wrap_step ? 0 : 1, kv_len - len, nullptr, 0, nullptr, 0, 0, st)) != YTC_OK)
+                                   ks, ks, os, mask_kind, kv_len - len, mask_ptr, m->max_pos, nullptr, 0, 0, st)) != YTC_OK)
       return s;
     if (m->tp_world == 1) {  // x2 = attn + x: the projection accumulates into the residual stream
       if ((s = linear_w16(m, m->attn, m->l_heads * D, W.o, m->x, Hd, rows, Hd, m->l_heads * D, true, st)) != YTC_OK)

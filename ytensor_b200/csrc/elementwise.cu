@@ -128,6 +128,10 @@ __device__ __forceinline__ V4 ld4(const void* p, int64_t i, int dt) {
   if (dt == YTC_F32) {
     const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
     r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+  } else if (dt >= YTC_F8_E5M2) {
+    const uint32_t t = *reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p) + i);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) r.v[k] = f8_bits_to_f32(static_cast<uint8_t>(t >> (8 * k)), dt);
   } else {
     const uint2 t = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p) + i);
     const uint16_t h[4] = {static_cast<uint16_t>(t.x & 0xFFFF), static_cast<uint16_t>(t.x >> 16),
@@ -140,6 +144,11 @@ __device__ __forceinline__ V4 ld4(const void* p, int64_t i, int dt) {
 __device__ __forceinline__ void st4(void* p, int64_t i, const V4& r, int dt) {
   if (dt == YTC_F32) {
     *reinterpret_cast<float4*>(static_cast<float*>(p) + i) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  } else if (dt >= YTC_F8_E5M2) {
+    uint32_t t = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) t |= static_cast<uint32_t>(f32_to_f8_bits(r.v[k], dt)) << (8 * k);
+    *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p) + i) = t;
   } else {
     uint16_t h[4];
 #pragma unroll
@@ -253,6 +262,9 @@ using namespace ytk;
 
 extern "C" {
 
+static int unary_impl(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
+                      const int64_t* xstrides, const int64_t* ystrides, float param, void* stream);
+
 int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const void* b, void* out, int ndim,
                   const int64_t* shape, const int64_t* astrides, const int64_t* bstrides, const int64_t* ostrides,
                   void* stream) {
@@ -303,6 +315,12 @@ int ytcuda_binary(int op, int dt_a, int dt_b, int dt_out, const void* a, const v
 
 int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
                  const int64_t* xstrides, const int64_t* ystrides, float param, void* stream) {
+  YTC_REQUIRE(dt_in >= 0 && dt_in <= 2 && dt_out >= 0 && dt_out <= 2, "ytcuda_unary: bad dtype");
+  return unary_impl(op, dt_in, dt_out, x, y, ndim, shape, xstrides, ystrides, param, stream);
+}
+
+static int unary_impl(int op, int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape,
+                      const int64_t* xstrides, const int64_t* ystrides, float param, void* stream) {
   {
     const int base = op >= U_DERIV ? op - U_DERIV : op;
     YTC_REQUIRE(op >= 0 && base <= U_LAST && (op < U_DERIV || base == U_SWISH || base >= U_RELU),
@@ -310,7 +328,6 @@ int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim
   }
   YTC_REQUIRE(ndim >= 1 && ndim <= EW_MAXD, "ytcuda_unary: ndim %d outside [1, %d]", ndim, EW_MAXD);
   YTC_REQUIRE(shape && xstrides && ystrides, "ytcuda_unary: null shape/strides");
-  YTC_REQUIRE(dt_in >= 0 && dt_in <= 2 && dt_out >= 0 && dt_out <= 2, "ytcuda_unary: bad dtype");
   int64_t n = 1;
   for (int d = 0; d < ndim; ++d) {
     YTC_REQUIRE(shape[d] >= 0, "ytcuda_unary: negative extent");
@@ -340,7 +357,8 @@ int ytcuda_unary(int op, int dt_in, int dt_out, const void* x, void* y, int ndim
 
 int ytcuda_cast(int dt_in, int dt_out, const void* x, void* y, int ndim, const int64_t* shape, const int64_t* xstrides,
                 const int64_t* ystrides, void* stream) {
-  return ytcuda_unary(U_COPY, dt_in, dt_out, x, y, ndim, shape, xstrides, ystrides, 0.f, stream);
+  YTC_REQUIRE(dt_in >= 0 && dt_in <= YTC_F8_E8M0 && dt_out >= 0 && dt_out <= YTC_F8_E8M0, "ytcuda_cast: bad dtype");
+  return unary_impl(U_COPY, dt_in, dt_out, x, y, ndim, shape, xstrides, ystrides, 0.f, stream);
 }
 
 int ytcuda_swiglu(int dt_in, int dt_out, const void* gate_up, void* out, int64_t rows, int inter, int64_t gu_row_stride,

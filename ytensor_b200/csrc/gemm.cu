@@ -35,6 +35,9 @@ struct GemmTcParams {
   int a_prefetch;  // k-blocks by which an L2 prefetch of A runs ahead of the shared-memory loads (0 = off)
   int split_loads; // K-major tiles fetched as 64-row boxes
   int* status;
+  // masked product: tile_live[mb * tiles_n + nb] == 0 marks an output tile no element of which is asked for; every
+  // role of the kernel passes over it (no loads, no MMAs, no stores). NULL = every tile is computed.
+  const uint8_t* tile_live;
 };
 
 template <int BN>
@@ -204,6 +207,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
         const int b = tile / tiles_per_batch;
         const int rem = tile - b * tiles_per_batch;
+        if (p.tile_live && !p.tile_live[rem]) continue;
         const int mb = rem / p.tiles_n;
         const int nb = rem - mb * p.tiles_n;
         const int ba = p.a_bcast ? 0 : b;
@@ -281,6 +285,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        if (p.tile_live && !p.tile_live[tile % tiles_per_batch]) continue;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -323,6 +328,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
       const int b = tile / tiles_per_batch;
       const int rem = tile - b * tiles_per_batch;
+      if (p.tile_live && !p.tile_live[rem]) continue;
       const int mb = rem / p.tiles_n;
       const int nb = rem - mb * p.tiles_n;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_word)) break;
@@ -577,6 +583,7 @@ struct GemmSimtParams {
   float alpha, beta;
   int in_dtype, out_dtype;
   int tiles_m, tiles_n;
+  const uint8_t* tile_live;  // masked product: 0 marks a 128 x 128 output tile nobody asks for (NULL: all computed)
 };
 
 template <int IN_DT>
@@ -586,6 +593,7 @@ __global__ void __launch_bounds__(SM_THREADS) gemm_simt_kernel(const GemmSimtPar
 
   const int tid = threadIdx.x;
   const int tile = blockIdx.x;
+  if (p.tile_live && !p.tile_live[tile]) return;
   const int b = blockIdx.y;
   const int mb = tile / p.tiles_n, nb = tile - mb * p.tiles_n;
   const int m0 = mb * SM_BM, n0 = nb * SM_BN;
@@ -722,6 +730,56 @@ static int g_tc_split_loads = 0;
 // CTA-pair kernel: 0 = automatic, 1 = whenever the layout allows, 2 = never.
 static int g_tc_pair = 0;
 
+// Masked products (YTensor::masked_matmul): what the entry point asked for, seen by the launchers below.
+// kind 0: no mask; 1: bool matrix [m, n]; 2: the causal predicate j <= i + offset, evaluated on the device.
+struct MaskCtx {
+  int kind = 0;
+  const uint8_t* mask = nullptr;
+  int64_t row_stride = 0;
+  int offset = 0;
+};
+static thread_local MaskCtx g_mask;
+
+__device__ __forceinline__ bool mask_at(int kind, const uint8_t* mask, int64_t mrs, int offset, int i, int j) {
+  return kind == 2 ? (j <= i + offset) : (mask[static_cast<int64_t>(i) * mrs + j] != 0);
+}
+
+// live[mb * tiles_n + nb] = 1 when some element of output tile (mb, nb) is asked for. The counterpart of the
+// tileAllFalse test that lets the reference's sgemm_masked skip whole tiles (src/kernel/avx2/sgemm.inl:449-475).
+__global__ void __launch_bounds__(256) gemm_tile_live_kernel(uint8_t* live, int kind, const uint8_t* mask, int64_t mrs,
+                                                             int offset, int m, int n, int bm, int bn, int tiles_n) {
+  const int mb = blockIdx.x / tiles_n, nb = blockIdx.x - mb * tiles_n;
+  const int i0 = mb * bm, j0 = nb * bn;
+  const int i1 = i0 + bm < m ? i0 + bm : m, j1 = j0 + bn < n ? j0 + bn : n;
+  int any = 0;
+  if (kind == 2) {
+    any = j0 <= (i1 - 1) + offset;  // the tile's smallest column against its largest row
+  } else {
+    const int w = j1 - j0;
+    for (int e = threadIdx.x; e < (i1 - i0) * w && !any; e += 256) {
+      const int i = i0 + e / w, j = j0 + e % w;
+      any = mask[static_cast<int64_t>(i) * mrs + j] != 0;
+    }
+  }
+  any = __syncthreads_or(any);
+  if (threadIdx.x == 0) live[blockIdx.x] = any ? 1 : 0;
+}
+
+// Tile liveness for the current mask and a bm x bn tiling, in stream-ordered scratch (freed by the caller's launcher
+// after its kernel has been queued). NULL without a mask.
+static int make_tile_live(int m, int n, int bm, int bn, cudaStream_t st, uint8_t** out) {
+  *out = nullptr;
+  if (g_mask.kind == 0) return YTC_OK;
+  const int tiles_m = (m + bm - 1) / bm, tiles_n = (n + bn - 1) / bn;
+  uint8_t* live = nullptr;
+  YTC_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&live), static_cast<size_t>(tiles_m) * tiles_n, st));
+  gemm_tile_live_kernel<<<tiles_m * tiles_n, 256, 0, st>>>(live, g_mask.kind, g_mask.mask, g_mask.row_stride,
+                                                          g_mask.offset, m, n, bm, bn, tiles_n);
+  count_launch();
+  *out = live;
+  return YTC_OK;
+}
+
 static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
                      float alpha, float beta, int a_mn, int64_t lda, int b_mn, int64_t ldb, int64_t rsc, int64_t csc,
                      int64_t batch, int64_t bsa, int64_t bsb, int64_t bsc, cudaStream_t st) {
@@ -732,8 +790,10 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
   // 256-wide tiles unless the problem is narrow or would leave most SMs without a tile
   const int BN = (n <= 128 || static_cast<int64_t>((m + 127) / 128) * ((n + 255) / 256) * batch < sm_count() / 2) ? 128 : 256;
   // CTA pairs pay off on large problems; small ones keep one CTA per tile (more tiles to spread over the SMs)
-  const bool pair = g_tc_pair != 2 && (g_tc_pair == 1 || (m >= 512 && n >= 256 && k >= 256 &&
-                                                        static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) * batch >= 74));
+  // (a masked product keeps one CTA per tile: the tile-skipping form of the kernel)
+  const bool pair = g_mask.kind == 0 && g_tc_pair != 2 &&
+                    (g_tc_pair == 1 || (m >= 512 && n >= 256 && k >= 256 &&
+                                        static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) * batch >= 74));
   {
     const uint64_t nb = (a_bcast || batch == 1) ? 1 : static_cast<uint64_t>(batch);
     uint64_t dims[3], strides[2];
@@ -804,6 +864,12 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
     return YTC_OK;
   }
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+  uint8_t* live = nullptr;
+  {
+    const int s = make_tile_live(m, n, TC_BM, BN, st, &live);
+    if (s != YTC_OK) return s;
+    p.tile_live = live;
+  }
   if (BN == 256) {
     const int s = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc_kernel<256>), TcSmem<256>::DYN_BYTES);
     if (s != YTC_OK) return s;
@@ -814,6 +880,7 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
     gemm_tc_kernel<128><<<grid, TC_THREADS, TcSmem<128>::DYN_BYTES, st>>>(tmA, tmB, p);
   }
   count_launch();
+  if (live) cudaFreeAsync(live, st);
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
 }
@@ -830,6 +897,12 @@ static int launch_simt(int dtype_in, int dtype_out, const void* A, const void* B
   p.in_dtype = dtype_in; p.out_dtype = dtype_out;
   p.tiles_m = (m + SM_BM - 1) / SM_BM;
   p.tiles_n = (n + SM_BN - 1) / SM_BN;
+  uint8_t* live = nullptr;
+  {
+    const int s = make_tile_live(m, n, SM_BM, SM_BN, st, &live);
+    if (s != YTC_OK) return s;
+    p.tile_live = live;
+  }
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x7FFFFFFFll || batch > 65535) {
     // gridDim.y is limited to 65535: split the batch.
@@ -850,6 +923,7 @@ static int launch_simt(int dtype_in, int dtype_out, const void* A, const void* B
     else gemm_simt_kernel<YTC_F16><<<grid, SM_THREADS, 0, st>>>(q);
     count_launch();
   }
+  if (live) cudaFreeAsync(live, st);
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
 }
@@ -907,14 +981,16 @@ __global__ void __launch_bounds__(256) gemm_split3_kernel(const float* x, int64_
 // sgemm_masked write the masked-in products only).
 __global__ void __launch_bounds__(256) gemm_apply_mask_kernel(void* C, int dt, int m, int n, int64_t rsc, int64_t csc,
                                                               int64_t batch, int64_t bsc, const uint8_t* mask,
-                                                              int64_t mask_rs, float masked_value) {
+                                                              int64_t mask_rs, float masked_value, int causal,
+                                                              int offset) {
   const int64_t per = static_cast<int64_t>(m) * n;
   const int64_t total = per * batch;
   for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
        t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t b = t / per, r = t - b * per;
     const int i = static_cast<int>(r / n), j = static_cast<int>(r - static_cast<int64_t>(i) * n);
-    if (mask[static_cast<int64_t>(i) * mask_rs + j] == 0) store_from_f32(C, b * bsc + i * rsc + j * csc, masked_value, dt);
+    const bool keep = causal ? (j <= i + offset) : (mask[static_cast<int64_t>(i) * mask_rs + j] != 0);
+    if (!keep) store_from_f32(C, b * bsc + i * rsc + j * csc, masked_value, dt);
   }
 }
 
@@ -1109,6 +1185,41 @@ static int64_t span_of(int64_t r, int64_t c, int64_t rs, int64_t cs) { return (r
 
 }  // namespace ytk
 
+// The product skips the output tiles the mask leaves nothing in (the launchers read g_mask), then one pass writes
+// masked_value wherever the mask does not hold (dead tiles included).
+static int gemm_masked_impl(int kind, int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n,
+                            int k, int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc,
+                            int64_t batch, int64_t bsa, int64_t bsb, int64_t bsc, const void* mask,
+                            int64_t mask_row_stride, int offset, float masked_value, void* stream) {
+  ytk::g_mask.kind = kind;
+  ytk::g_mask.mask = static_cast<const uint8_t*>(mask);
+  ytk::g_mask.row_stride = mask_row_stride;
+  ytk::g_mask.offset = offset;
+  const int s = ytcuda_gemm(dtype_in, dtype_out, A, B, C, m, n, k, 1.0f, 0.0f, rsa, csa, rsb, csb, rsc, csc, batch, bsa,
+                            bsb, bsc, stream);
+  ytk::g_mask = ytk::MaskCtx{};
+  if (s != YTC_OK) return s;
+  const int64_t total = static_cast<int64_t>(m) * n * batch;
+  const int64_t blocks = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  gemm_apply_mask_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      C, dtype_out, m, n, rsc, csc, batch, bsc, static_cast<const uint8_t*>(mask), mask_row_stride, masked_value,
+      kind == 2 ? 1 : 0, offset);
+  count_launch();
+  YTC_CUDA(cudaGetLastError());
+  return YTC_OK;
+}
+
+int ytcuda_gemm_masked_causal(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
+                              int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc,
+                              int64_t batch, int64_t bsa, int64_t bsb, int64_t bsc, int causal_offset,
+                              float masked_value, void* stream) {
+  YTC_REQUIRE(m >= 0 && n >= 0 && k >= 0 && batch >= 0, "ytcuda_gemm_masked_causal: negative extent");
+  if (m == 0 || n == 0 || batch == 0) return YTC_OK;
+  return gemm_masked_impl(2, dtype_in, dtype_out, A, B, C, m, n, k, rsa, csa, rsb, csb, rsc, csc, batch, bsa, bsb, bsc,
+                          nullptr, 0, causal_offset, masked_value, stream);
+}
+
 int ytcuda_gemm_masked(int dtype_in, int dtype_out, const void* A, const void* B, void* C, int m, int n, int k,
                        int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc, int64_t batch,
                        int64_t bsa, int64_t bsb, int64_t bsc, const void* mask, int64_t mask_row_stride,
@@ -1118,17 +1229,8 @@ int ytcuda_gemm_masked(int dtype_in, int dtype_out, const void* A, const void* B
   YTC_REQUIRE(mask != nullptr, "ytcuda_gemm_masked: mask is null");
   YTC_REQUIRE(mask_row_stride >= n, "ytcuda_gemm_masked: mask row stride %lld shorter than n = %d",
               (long long)mask_row_stride, n);
-  const int s = ytcuda_gemm(dtype_in, dtype_out, A, B, C, m, n, k, 1.0f, 0.0f, rsa, csa, rsb, csb, rsc, csc, batch, bsa,
-                            bsb, bsc, stream);
-  if (s != YTC_OK) return s;
-  const int64_t total = static_cast<int64_t>(m) * n * batch;
-  const int64_t blocks = (total + 255) / 256;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-  gemm_apply_mask_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      C, dtype_out, m, n, rsc, csc, batch, bsc, static_cast<const uint8_t*>(mask), mask_row_stride, masked_value);
-  count_launch();
-  YTC_CUDA(cudaGetLastError());
-  return YTC_OK;
+  return gemm_masked_impl(1, dtype_in, dtype_out, A, B, C, m, n, k, rsa, csa, rsb, csb, rsc, csc, batch, bsa, bsb, bsc,
+                          mask, mask_row_stride, 0, masked_value, stream);
 }
 
 

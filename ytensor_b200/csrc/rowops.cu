@@ -23,7 +23,8 @@
 
 namespace ytk {
 
-enum RowOp { OP_SOFTMAX = 0, OP_RMSNORM = 1, OP_LAYERNORM = 2, OP_CHAIN = 3, OP_SUM = 4, OP_MEAN = 5, OP_MAX = 6 };
+enum RowOp { OP_SOFTMAX = 0, OP_RMSNORM = 1, OP_LAYERNORM = 2, OP_CHAIN = 3, OP_SUM = 4, OP_MEAN = 5, OP_MAX = 6,
+             OP_LPNORM = 7 };
 
 struct F4 {
   float v[4];
@@ -391,6 +392,7 @@ struct LineParams {
   int64_t rws[MAXD];                // stride of each reduced dim inside the weight (ascending-axis order layout)
   int64_t lines, R;
   float eps;
+  float lp;  // exponent of OP_LPNORM
   int dt_in, dt_out, dt_w;
 };
 
@@ -492,6 +494,19 @@ __global__ void __launch_bounds__(128) line_kernel(const LineParams p) {
         float v = load_as_f32(p.x, xb + xo, p.dt_in) * inv;
         if (p.w) v *= load_as_f32(p.w, wo, p.dt_w);
         store_from_f32(p.y, yb + yo, v, p.dt_out);
+      }
+    } else if constexpr (OP == OP_LPNORM) {
+      // yt::function::normalize (reference src/function/normalization.inl:56-85): x / (sum |x|^p + eps)^(1/p)
+      float s = 0.f;
+      for (int64_t r = r0; r < p.R; r += rstep) {
+        line_offsets(p, r, xo, yo, wo);
+        s += powf(fabsf(load_as_f32(p.x, xb + xo, p.dt_in)), p.lp);
+      }
+      s = bsum(s);
+      const float den = powf(s + p.eps, 1.0f / p.lp);
+      for (int64_t r = r0; r < p.R; r += rstep) {
+        line_offsets(p, r, xo, yo, wo);
+        store_from_f32(p.y, yb + yo, load_as_f32(p.x, xb + xo, p.dt_in) / den, p.dt_out);
       }
     } else if constexpr (OP == OP_LAYERNORM) {
       float s = 0.f;
@@ -685,6 +700,7 @@ static void launch_line_op(int op, const LineParams& p, bool per_thread, cudaStr
     case OP_SOFTMAX: launch_line<OP_SOFTMAX>(p, per_thread, st); break;
     case OP_RMSNORM: launch_line<OP_RMSNORM>(p, per_thread, st); break;
     case OP_LAYERNORM: launch_line<OP_LAYERNORM>(p, per_thread, st); break;
+    case OP_LPNORM: launch_line<OP_LPNORM>(p, per_thread, st); break;
     case OP_SUM: launch_line<OP_SUM>(p, per_thread, st); break;
     case OP_MEAN: launch_line<OP_MEAN>(p, per_thread, st); break;
     default: launch_line<OP_MAX>(p, per_thread, st); break;
@@ -695,7 +711,7 @@ static void launch_line_op(int op, const LineParams& p, bool per_thread, cudaStr
 // (sum / mean / max) instead of the input's shape (softmax / norms).
 static int run_nd(int op, int dt_in, int dt_out, int dt_w, const void* x, void* y, const void* w, const void* b,
                   int* idx, const NdArgs& a, float eps, bool reduce_out, cudaStream_t st, const char* who,
-                  void* scratch = nullptr, size_t scratch_bytes = 0) {
+                  void* scratch = nullptr, size_t scratch_bytes = 0, float lp = 2.f) {
   int ax[MAXD];
   bool used[MAXD];
   int s = normalize_axes(a, ax, used, who);
@@ -742,7 +758,7 @@ static int run_nd(int op, int dt_in, int dt_out, int dt_w, const void* x, void* 
     if (reduce_out && lines > 1 && y_rs != 1) trailing = false;
   }
   const int esz_in = dtype_size(dt_in), esz_out = dtype_size(dt_out);
-  if (trailing && R % 4 == 0 && R <= 16384 && x_rs >= 0 && y_rs >= 0 &&
+  if (op != OP_LPNORM && trailing && R % 4 == 0 && R <= 16384 && x_rs >= 0 && y_rs >= 0 &&
       (reinterpret_cast<uint64_t>(x) % (4 * esz_in)) == 0 && (x_rs * esz_in) % (4 * esz_in) == 0 &&
       (reduce_out || ((reinterpret_cast<uint64_t>(y) % (4 * esz_out)) == 0 && (y_rs * esz_out) % (4 * esz_out) == 0)) &&
       (!w || reinterpret_cast<uint64_t>(w) % (4 * dtype_size(dt_w)) == 0) &&
@@ -760,7 +776,7 @@ static int run_nd(int op, int dt_in, int dt_out, int dt_w, const void* x, void* 
   LineParams p;
   p.x = x; p.y = y; p.w = w; p.b = b; p.idx = idx;
   p.nk = 0; p.nr = a.naxes;
-  p.eps = eps; p.dt_in = dt_in; p.dt_out = dt_out; p.dt_w = dt_w;
+  p.eps = eps; p.lp = lp; p.dt_in = dt_in; p.dt_out = dt_out; p.dt_w = dt_w;
   p.lines = lines; p.R = R;
   for (int d = 0; d < a.ndim; ++d)
     if (!used[d]) {
@@ -913,6 +929,15 @@ int ytcuda_softmax(int dt_in, int dt_out, const void* x, void* y, const int64_t*
   NdArgs a{shape, xstrides, ystrides, ndim, axes, naxes};
   return run_nd(OP_SOFTMAX, dt_in, dt_out, YTC_F32, x, y, nullptr, nullptr, nullptr, a, 0.f, false,
                 static_cast<cudaStream_t>(stream), "ytcuda_softmax");
+}
+
+int ytcuda_normalize(int dt_in, int dt_out, const void* x, void* y, const int64_t* shape, const int64_t* xstrides,
+                     const int64_t* ystrides, int ndim, const int* axes, int naxes, float p, float eps, void* stream) {
+  YTC_REQUIRE(shape && xstrides && ystrides && axes, "ytcuda_normalize: null shape/strides/axes");
+  YTC_REQUIRE(p > 0.f, "yt::function::normalize: p must be positive");
+  NdArgs a{shape, xstrides, ystrides, ndim, axes, naxes};
+  return run_nd(OP_LPNORM, dt_in, dt_out, YTC_F32, x, y, nullptr, nullptr, nullptr, a, eps, false,
+                static_cast<cudaStream_t>(stream), "ytcuda_normalize", nullptr, 0, p);
 }
 
 int ytcuda_rmsnorm(int dt_in, int dt_out, int dt_w, const void* x, const void* weight, void* y, const int64_t* shape,

@@ -109,6 +109,87 @@ __host__ __device__ __forceinline__ float f16_bits_to_f32_ref(uint16_t h) {
 #endif
 }
 
+// The reference's generic small float FloatSpec<S, E, M> (include/types/float_spec.hpp): float -> spec (fromFloat32,
+// :435-491) and spec -> float (toFloat32, :299-371), the same rules as the float16 functions above for any sign /
+// exponent / mantissa widths with M <= 23: zero and fp32 subnormals -> signed zero; Inf / NaN -> exponent all ones,
+// mantissa 1 for NaN; biased exponent <= 0 flushes to zero; >= all ones overflows to infinity; otherwise round to
+// nearest even with carry into the exponent. An unsigned format (S = 0) drops the sign.
+template <int S, int E, int M>
+__host__ __device__ __forceinline__ uint32_t f32_to_spec_bits(float x) {
+#ifdef __CUDA_ARCH__
+  uint32_t bits = __float_as_uint(x);
+#else
+  uint32_t bits;
+  memcpy(&bits, &x, 4);
+#endif
+  constexpr int bias = (1 << (E - 1)) - 1;
+  constexpr uint32_t emax = (1u << E) - 1u;
+  const uint32_t s = S ? (bits >> 31) : 0u, e = (bits >> 23) & 0xFFu, m = bits & 0x7FFFFFu;
+  uint32_t ne = 0, nm = 0;
+  if (e == 0) {
+  } else if (e == 0xFFu) {
+    ne = emax;
+    nm = m ? 1u : 0u;
+  } else {
+    const int re = static_cast<int>(e) - 127 + bias;
+    if (re <= 0) {
+    } else if (re >= static_cast<int>(emax)) {
+      ne = emax;
+    } else {
+      ne = static_cast<uint32_t>(re);
+      nm = m >> (23 - M);
+      const uint32_t rem = m & ((1u << (23 - M)) - 1u), half = 1u << (22 - M);
+      if (rem > half || (rem == half && (nm & 1u))) {
+        ++nm;
+        if (nm >= (1u << M)) {
+          nm = 0;
+          ++ne;
+          if (ne >= emax) ne = emax;
+        }
+      }
+    }
+  }
+  return (s << (E + M)) | (ne << M) | nm;
+}
+template <int S, int E, int M>
+__host__ __device__ __forceinline__ float spec_bits_to_f32(uint32_t h) {
+  constexpr int bias = (1 << (E - 1)) - 1;
+  constexpr uint32_t emax = (1u << E) - 1u, mmask = (1u << M) - 1u;
+  const uint32_t s = S ? ((h >> (E + M)) & 1u) : 0u;
+  const uint32_t e = (h >> M) & emax;
+  uint32_t m = h & mmask;
+  uint32_t out;
+  if (e == 0) {
+    if (m == 0 || M == 0) {
+      out = s << 31;
+    } else {
+      // a subnormal encoding: normalised with the exponent set to 1 - shift (twice the IEEE value; followed as is)
+      int shift = 0;
+      while ((m & (1u << (M > 0 ? M - 1 : 0))) == 0 && shift < M) {
+        m <<= 1;
+        ++shift;
+      }
+      m = (m << 1) & mmask;
+      const int ne = 1 - shift - bias + 127;
+      out = ne <= 0 ? ((s << 31) | (m << (23 - M))) : ((s << 31) | (static_cast<uint32_t>(ne) << 23) | (m << (23 - M)));
+    }
+  } else if (e == emax) {
+    out = (s << 31) | 0x7F800000u | (m ? 1u : 0u);
+  } else {
+    const int ne = static_cast<int>(e) - bias + 127;
+    if (ne <= 0) out = s << 31;
+    else if (ne >= 255) out = (s << 31) | 0x7F800000u;
+    else out = (s << 31) | (static_cast<uint32_t>(ne) << 23) | (m << (23 - M));
+  }
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(out);
+#else
+  float f;
+  memcpy(&f, &out, 4);
+  return f;
+#endif
+}
+
 template <int DT>
 struct DType;
 template <>
@@ -138,17 +219,30 @@ struct DType<YTC_F16> {
   }
 };
 
-__host__ __device__ __forceinline__ int dtype_size(int dt) { return dt == YTC_F32 ? 4 : 2; }
+__host__ __device__ __forceinline__ int dtype_size(int dt) { return dt == YTC_F32 ? 4 : (dt >= YTC_F8_E5M2 ? 1 : 2); }
+
+__device__ __forceinline__ float f8_bits_to_f32(uint8_t b, int dt) {
+  if (dt == YTC_F8_E5M2) return spec_bits_to_f32<1, 5, 2>(b);
+  if (dt == YTC_F8_E4M3) return spec_bits_to_f32<1, 4, 3>(b);
+  return spec_bits_to_f32<0, 8, 0>(b);
+}
+__device__ __forceinline__ uint8_t f32_to_f8_bits(float v, int dt) {
+  if (dt == YTC_F8_E5M2) return static_cast<uint8_t>(f32_to_spec_bits<1, 5, 2>(v));
+  if (dt == YTC_F8_E4M3) return static_cast<uint8_t>(f32_to_spec_bits<1, 4, 3>(v));
+  return static_cast<uint8_t>(f32_to_spec_bits<0, 8, 0>(v));
+}
 
 __device__ __forceinline__ float load_as_f32(const void* p, int64_t i, int dt) {
   if (dt == YTC_F32) return DType<YTC_F32>::load(p, i);
   if (dt == YTC_BF16) return DType<YTC_BF16>::load(p, i);
-  return DType<YTC_F16>::load(p, i);
+  if (dt == YTC_F16) return DType<YTC_F16>::load(p, i);
+  return f8_bits_to_f32(static_cast<const uint8_t*>(p)[i], dt);
 }
 __device__ __forceinline__ void store_from_f32(void* p, int64_t i, float v, int dt) {
   if (dt == YTC_F32) DType<YTC_F32>::store(p, i, v);
   else if (dt == YTC_BF16) DType<YTC_BF16>::store(p, i, v);
-  else DType<YTC_F16>::store(p, i, v);
+  else if (dt == YTC_F16) DType<YTC_F16>::store(p, i, v);
+  else static_cast<uint8_t*>(p)[i] = f32_to_f8_bits(v, dt);
 }
 
 // ---- host-side plumbing -------------------------------------------------------

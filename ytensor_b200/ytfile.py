@@ -136,8 +136,9 @@ class YtFile:
         raw = memoryview(self._map)[r.data_offset:r.data_offset + r.stored_size]
         if r.compress == "zlib":
             raw = zlib.decompress(raw, wbits=47)  # zlib or gzip framing, as inflateInit2(15 + 32) accepts
-        elif r.compress != "":
-            raise YtFormatError(f"{name}: compression {r.compress!r} is not supported")
+        # any other method name ("zlibfloat" is named in the reference's header, include/ytensor_io.hpp:38-42, but has
+        # no implementation there): the reference's checkCompressMethod falls back to "no compression"
+        # (src/ytensor_io.inl:11-22), so the bytes are taken as they are
         if len(raw) != want:
             raise YtFormatError(f"{name}: {len(raw)} data bytes for shape {r.shape} of {r.type_name}")
         return np.frombuffer(raw, dtype=dt).reshape(r.shape)
@@ -175,9 +176,10 @@ def _string(s: str) -> bytes:
 
 def write_yt(path, tensors: dict, *, compress: str = "", bfloat16: tuple = (), metadata: str = "") -> None:
     """Writes numpy arrays as a `.yt` file YTensorIO reads. Names in `bfloat16` are uint16 arrays stored as
-    bfloat16 tensors. compress: "" or "zlib"."""
+    bfloat16 tensors. compress: "" or "zlib"; any other name (e.g. "zlibfloat", which the reference names but does not
+    implement) is stored uncompressed, as YTensorIO's checkCompressMethod does (src/ytensor_io.inl:11-22)."""
     if compress not in ("", "zlib"):
-        raise ValueError("compress must be '' or 'zlib'")
+        compress = ""
     names_of = {np.dtype(v).name: k for k, v in _NUMPY_OF.items() if k != "bfloat16"}
     with open(path, "wb") as f:
         f.write(MAGIC + struct.pack("<B", VERSION) + _string(metadata))
