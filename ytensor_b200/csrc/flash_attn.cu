@@ -18,6 +18,8 @@
 // (reference src/function/ops.inl:109-234,368-425, src/kernel/avx2/flash_attention.inl:202-443).
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "ptx_sm100.cuh"
 #include "ytc_common.cuh"
 
@@ -84,14 +86,43 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
+// 2^x for a packed pair on the FMA pipe instead of the special-function unit, which on this part retires far fewer
+// results per clock than the tensor pipe needs exponentials: round x to the nearest integer n with the 1.5 * 2^23
+// trick, evaluate a cubic minimax polynomial of 2^f on f = x - n in [-0.5, 0.5] (relative error 7.5e-5, well under
+// the rounding of the 16-bit P), and add n to the exponent field. x is clamped at -126 (the result is then ~1e-38
+// instead of 0).
+#ifndef FA_EMU_EVERY
+#define FA_EMU_EVERY 0  // every FA_EMU_EVERY-th pair of a full tile takes this path; 0 switches it off
+#endif
+__device__ __forceinline__ void exp2_emu2(uint64_t x2, float& p0, float& p1) {
+  constexpr float MAGIC = 12582912.f;  // 1.5 * 2^23
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  const uint64_t xc = f2_pack(x0, x1);
+  const uint64_t t2 = f2_add(xc, f2_pack(MAGIC, MAGIC));
+  const uint64_t j2 = f2_add(t2, f2_pack(-MAGIC, -MAGIC));
+  const uint64_t f2 = f2_fma(j2, f2_pack(-1.f, -1.f), xc);
+  uint64_t q2 = f2_fma(f2_pack(0.0551716685f, 0.0551716685f), f2, f2_pack(0.242611125f, 0.242611125f));
+  q2 = f2_fma(q2, f2, f2_pack(0.693260968f, 0.693260968f));
+  q2 = f2_fma(q2, f2, f2_pack(0.999928057f, 0.999928057f));
+  float t0, t1, q0, q1;
+  f2_unpack(t2, t0, t1);
+  f2_unpack(q2, q0, q1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
+
 template <int D>
 struct FaSmem {
   static constexpr int TILE_BYTES = FA_BM * D * 2;  // one Q / K / V tile
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = 2 * TILE_BYTES;
   static constexpr int BAR_OFF = KV_OFF + FA_STAGES * 2 * TILE_BYTES;
-  // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full[2], o_ready[2], q_free, o_free[2], tmem slot, abort
-  static constexpr int NBAR = 1 + 3 * FA_STAGES + 6 + 3;
+  // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], p_full[2], o_ready[2], q_free, o_free[2], p_half[2],
+  // tmem slot, abort
+  static constexpr int NBAR = 1 + 3 * FA_STAGES + 6 + 3 + 2;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -167,7 +198,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   uint64_t* o_ready = p_full + 2;
   uint64_t* q_free = o_ready + 2;   // the MMAs no longer read the Q tiles of the current item
   uint64_t* o_free = q_free + 1;    // [2] the epilogue has read O_t
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
+  uint64_t* p_half = o_free + 2;    // [2] the first 64 keys' columns of P_t are in tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_half + 2);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -183,6 +215,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
       mbar_init(&p_full[t], 4);  // one arrival per softmax warp
+      mbar_init(&p_half[t], 4);
       mbar_init(&o_ready[t], 1);
       mbar_init(&o_free[t], 4);
     }
@@ -266,13 +299,15 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       };
       // O_t (+)= P_t . V : A = P from tensor memory (16-bit pairs, 8 columns per 16 keys),
       // B = V, unit stride along the value dim (MN-major): 16 keys = 2048 bytes, 64-wide chunks 16 KiB apart
-      auto issue_pv = [&](int t, int stage, bool accumulate) {
+      // O_t (+)= P_t V in two halves of 64 keys: the first is issued as soon as the softmax warps have published the
+      // first half of P, while they still compute the second.
+      auto issue_pv = [&](int t, int stage, bool accumulate, int half) {
         const uint32_t va = smem_u32(smem + S::KV_OFF + stage * 2 * S::TILE_BYTES + S::TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < FA_BN / 16; ++kk)
+        for (int kk = half * (FA_BN / 32); kk < (half + 1) * (FA_BN / 32); ++kk)
           tc_mma_f16_ts(t_o[t], t_s[t] + kk * 8, umma_smem_desc_sw128(va + kk * 2048, FA_BM * 128, 1024), p.idesc_pv,
                         (accumulate || kk != 0) ? 1u : 0u);
-        tc_commit(&o_ready[t]);
+        if (half == 1) tc_commit(&o_ready[t]);
       };
       bool ok = true;
       int n_item = 0;
@@ -297,18 +332,24 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (j < it.n_tiles[t]) {
-              if (!mbar_wait(&p_full[t], static_cast<uint32_t>(p_cnt[t] & 1), abort_word)) {
+              if (!mbar_wait(&p_half[t], static_cast<uint32_t>(p_cnt[t] & 1), abort_word)) {
                 ok = false;
                 break;
               }
-              ++p_cnt[t];
               if (j == 0 && e_cnt[t] > 0 &&
                   !mbar_wait(&o_free[t], static_cast<uint32_t>((e_cnt[t] - 1) & 1), abort_word)) {
                 ok = false;  // the first P.V of an item overwrites O_t: the previous epilogue must have read it
                 break;
               }
               tc_fence_after();
-              issue_pv(t, s, j > 0);
+              issue_pv(t, s, j > 0, 0);
+              if (!mbar_wait(&p_full[t], static_cast<uint32_t>(p_cnt[t] & 1), abort_word)) {
+                ok = false;
+                break;
+              }
+              ++p_cnt[t];
+              tc_fence_after();
+              issue_pv(t, s, j > 0, 1);
             }
             if (j + 1 < it.n_tiles[t]) {
               if (!mbar_wait(&k_full[sn], ph_next, abort_word)) {
@@ -384,14 +425,23 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             uint32_t r[64];
             tmem_ld_32x32b_x64(ts + c0, r);
             tmem_ld_wait();
-            if (full && pos) {  // the common tile: one three-input max per two elements
+            if (full && pos) {  // the common tile: one three-input max per two elements, eight independent chains
+              float b0 = ident, b1 = ident, b2 = ident, b3 = ident;
 #pragma unroll
-              for (int e = 0; e < 64; e += 8) {
+              for (int e = 0; e < 64; e += 16) {
                 a0 = fmax3(a0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
                 a1 = fmax3(a1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
                 a2 = fmax3(a2, __uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
                 a3 = fmax3(a3, __uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+                b0 = fmax3(b0, __uint_as_float(r[e + 8]), __uint_as_float(r[e + 9]));
+                b1 = fmax3(b1, __uint_as_float(r[e + 10]), __uint_as_float(r[e + 11]));
+                b2 = fmax3(b2, __uint_as_float(r[e + 12]), __uint_as_float(r[e + 13]));
+                b3 = fmax3(b3, __uint_as_float(r[e + 14]), __uint_as_float(r[e + 15]));
               }
+              a0 = fmaxf(a0, b0);
+              a1 = fmaxf(a1, b1);
+              a2 = fmaxf(a2, b2);
+              a3 = fmaxf(a3, b3);
             } else {
               const int cc = full ? 64 : cl - c0;
 #pragma unroll
@@ -459,6 +509,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           const __half2 h = __floats2half2_rn(p0, p1);
           return *reinterpret_cast<const uint32_t*>(&h);
         };
+        auto publish_half = [&]() {  // columns of P for keys 0..63 are stored: the MMA warp may start P.V on them
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_half[t]);
+        };
         if (!elementwise_mask) {
 #pragma unroll 1
           for (int c0 = 0; c0 < FA_BN; c0 += 64) {
@@ -468,17 +524,36 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             uint32_t pk[32];
             if (full) {
               const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
-              uint64_t lacc = f2_pack(0.f, 0.f);
+              uint64_t lacc = f2_pack(0.f, 0.f), lacc2 = f2_pack(0.f, 0.f);
+              auto body = [&](auto is_bf) {
 #pragma unroll
-              for (int e = 0; e < 64; e += 2) {
-                float t0, t1;
-                f2_unpack(f2_fma(f2_pack(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc2, nm2), t0, t1);
-                const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-                lacc = f2_add(lacc, f2_pack(p0, p1));
-                pk[e >> 1] = pack2(p0, p1);
-              }
+                for (int e = 0; e < 64; e += 2) {
+                  const uint64_t x2 =
+                      f2_fma(f2_pack(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc2, nm2);
+                  float p0, p1;
+                  if (FA_EMU_EVERY > 0 && ((e >> 1) % (FA_EMU_EVERY > 0 ? FA_EMU_EVERY : 1)) == FA_EMU_EVERY - 1) {
+                    exp2_emu2(x2, p0, p1);
+                    lacc2 = f2_add(lacc2, f2_pack(p0, p1));
+                  } else {
+                    float t0, t1;
+                    f2_unpack(x2, t0, t1);
+                    p0 = fast_exp2(t0);
+                    p1 = fast_exp2(t1);
+                    lacc = f2_add(lacc, f2_pack(p0, p1));
+                  }
+                  if (decltype(is_bf)::value) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                  } else {
+                    const __half2 h = __floats2half2_rn(p0, p1);
+                    pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                  }
+                }
+              };
+              if (p.is_bf16) body(std::true_type{});
+              else body(std::false_type{});
               float la, lb;
-              f2_unpack(lacc, la, lb);
+              f2_unpack(f2_add(lacc, lacc2), la, lb);
               l0 += la;
               l1 += lb;
             } else {
@@ -495,6 +570,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
               }
             }
             tmem_st_32x32b_x32(ts + (c0 >> 1), pk);
+            if (c0 == 0) publish_half();
           }
         } else {
 #pragma unroll 1
@@ -512,6 +588,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
               pk[e >> 1] = pack2(p0, p1);
             }
             tmem_st_32x32b_x16(ts + (c0 >> 1), pk);
+            if (c0 == 32) publish_half();
           }
         }
         l_run += l0 + l1;

@@ -42,6 +42,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test, but the hardware may park the thread for up to `ns` nanoseconds while the phase is incomplete (it
+// wakes as soon as the phase completes): a parked warp leaves its scheduler's issue slots to the warps that compute.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+#ifndef YTK_PARK_NS
+#define YTK_PARK_NS 1000
+#endif
+
 // Cycle budget of one bounded wait (about 2 s at 2 GHz).
 #ifndef YTK_WAIT_CYCLES
 #define YTK_WAIT_CYCLES (4000000000ll)
@@ -55,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, 
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (YTK_PARK_NS > 0 ? mbar_try_wait_parked(bar, parity, YTK_PARK_NS) : mbar_try_wait(bar, parity)) return true;
     if (*abort_word) return false;
     if (clock64() - t0 > limit) {
       *abort_word = 1;
