@@ -86,13 +86,16 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
-// 2^x for a packed pair on the FMA pipe instead of the special-function unit, which on this part retires far fewer
-// results per clock than the tensor pipe needs exponentials: round x to the nearest integer n with the 1.5 * 2^23
+// 2^x for a packed pair on the FMA pipe instead of the special-function unit. That unit retires one ex2 warp
+// instruction per 8 cycles and scheduler (16 results per clock and SM), so the 2 x 128 x 128 exponentials of one
+// iteration keep it busy for as long as the tensor pipe needs for the four MMAs of the same iteration; the 16-bit
+// pack runs there as well. A quarter of the pairs is the measured optimum: the FMA and ALU pipes are nearly as full.
+// The method: round x to the nearest integer n with the 1.5 * 2^23
 // trick, evaluate a cubic minimax polynomial of 2^f on f = x - n in [-0.5, 0.5] (relative error 7.5e-5, well under
 // the rounding of the 16-bit P), and add n to the exponent field. x is clamped at -126 (the result is then ~1e-38
 // instead of 0).
 #ifndef FA_EMU_EVERY
-#define FA_EMU_EVERY 0  // every FA_EMU_EVERY-th pair of a full tile takes this path; 0 switches it off
+#define FA_EMU_EVERY 4  // every FA_EMU_EVERY-th pair of a full tile takes this path; 0 switches it off
 #endif
 __device__ __forceinline__ void exp2_emu2(uint64_t x2, float& p0, float& p1) {
   constexpr float MAGIC = 12582912.f;  // 1.5 * 2^23
