@@ -73,6 +73,24 @@ int main() {
     }
     report("masked_matmul mask shape mismatch throws", threw ? 0.0 : 1.0, 0.5);
   }
+  {  // masked_matmul with the causal predicate: evaluated on the device, empty tiles skipped
+    auto a = randn<3>({2, 300, 64});
+    auto b = randn<2>({64, 280});
+    const yt::cuda::Causal causal{-20};
+    report("masked_matmul (causal predicate, fill -inf-like)", normwise(yt::cuda::masked_matmul(a, b, causal, -7.0f),
+                                                                         a.masked_matmul(b, causal, -7.0f)), 1e-5);
+  }
+  {  // Lp normalisation and the instance / batch / group norms without affine part
+    auto x = randn<4>({3, 8, 5, 7});
+    report("normalize p=2 axis -1", normwise(yt::cuda::normalize(x, -1), yt::function::normalize(x, -1)), 1e-5);
+    report("normalize p=1 axes {1,3}", normwise(yt::cuda::normalize(x, std::vector<int>{1, 3}, 1.0f),
+                                                 yt::function::normalize(x, std::vector<int>{1, 3}, 1.0f)), 1e-5);
+    report("instanceNorm", normwise(yt::cuda::instanceNorm(x), yt::function::instanceNorm(x)), 1e-5);
+    report("batchNorm channel axis 2", normwise(yt::cuda::batchNorm(x, 2), yt::function::batchNorm(x, 2)), 1e-5);
+    report("groupNorm 4 groups", normwise(yt::cuda::groupNorm(x, 4), yt::function::groupNorm(x, 4)), 1e-5);
+    report("groupNorm 2 groups, channel axis 3 (-1)", normwise(yt::cuda::groupNorm(x, 7, -1),
+                                                                yt::function::groupNorm(x, 7, -1)), 1e-5);
+  }
   {  // bf16 storage: device accumulates in fp32; the CPU recipe is widen -> fp32 matmul -> narrow
     auto af = randn<2>({128, 256});
     auto bf = randn<2>({256, 192}, 0.0625f);

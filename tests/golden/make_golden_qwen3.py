@@ -5,7 +5,7 @@
 
 Two cases:
   small_* : a 2-layer toy configuration; full logits of the prefill and of 5 greedy steps, batch 1 and 2.
-  full_*  : the Qwen3-0.6B shape of BASELINE config 5 (28 layers, hidden 1024, 16 q / 8 kv heads, head_dim 128,
+  full_*  : the Qwen3-0.6B shape of benchmark configuration 5 (28 layers, hidden 1024, 16 q / 8 kv heads, head_dim 128,
             FFN 3072, vocab 151936, bf16 weights ~ N(0, 0.02) from seed 4, norm weights 1, tied vocabulary matrix),
             prompt = 512 token ids uniform in [0, vocab) from seed 4, 32 greedy steps: the tokens, the margin
             between the best and second-best logit at every step, and the 8 largest logits with their indices.

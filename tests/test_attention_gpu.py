@@ -177,7 +177,7 @@ def test_strided_views_of_fused_qkv(L, api, port):
 
 
 def test_config3_full_size_properties(L, api, port):
-    """BASELINE config 3: batch 16, 32 query / 8 kv heads, head_dim 128, seq 4096, causal, bf16.
+    """benchmark configuration 3: batch 16, 32 query / 8 kv heads, head_dim 128, seq 4096, causal, bf16.
     Full size through properties: (1) two batch items with the same inputs give the same bits, (2) the first
     256 and the last 128 query rows of one kv head against the oracle, (3) row 0 equals V[0]."""
     g = torch.Generator(device="cuda").manual_seed(2)

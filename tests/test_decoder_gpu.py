@@ -210,7 +210,7 @@ def test_linear_w16_kernels(Q, port):
 
 
 def test_full_model_greedy_tokens_match_reference(Q, qwen3_golden):
-    """BASELINE config 5, batch 1: 512-token prompt, 32 greedy steps, tokens identical to the reference's."""
+    """benchmark configuration 5, batch 1: 512-token prompt, 32 greedy steps, tokens identical to the reference's."""
     cfg = Q.Qwen3Config(max_position_embeddings=768)
     w = Q.random_weights(cfg, seed=4)
     assert hashlib.sha256(w["embed"].tobytes()).hexdigest() == str(qwen3_golden["full_embed_sha256"])
@@ -236,7 +236,7 @@ def test_full_model_greedy_tokens_match_reference(Q, qwen3_golden):
 
 
 def test_full_model_32_sequences_match_reference(Q):
-    """BASELINE config 5 at batch 32: the operator path that 32 sequences take (tcgen05 linears on hi + lo bf16 planes
+    """benchmark configuration 5 at batch 32: the operator path that 32 sequences take (tcgen05 linears on hi + lo bf16 planes
     with split-k pieces, attn_decode_fast_kernel, fused glue) against the reference run with 32 distinct prompts.
     The reference's prompt is 16 tokens per sequence (its prefill of 32 x 512 tokens would take most of an hour on the
     CPU); the 32 greedy decode steps are the full count. Tokens must be identical wherever the reference's own margin

@@ -83,7 +83,7 @@ def test_fp32_vs_oracle_shapes(L, api, port, m, n, k):
 
 
 def test_fp32_config1_seed0(L, api, port):
-    """BASELINE config 1: C[1024,1024] = A.B, A, B ~ N(0,1) from seed 0, rel err 1e-5 vs the CPU result."""
+    """benchmark configuration 1: C[1024,1024] = A.B, A, B ~ N(0,1) from seed 0, rel err 1e-5 vs the CPU result."""
     rng = np.random.default_rng(0)
     a = rng.standard_normal((1024, 1024)).astype(np.float32)
     b = rng.standard_normal((1024, 1024)).astype(np.float32)
@@ -300,7 +300,7 @@ def test_empty_and_invalid(L, api):
         api.matmul(torch.empty(3, 5), torch.empty(5, 2))  # host tensors: no CPU fallback
 
 
-# ------------------------------------------------------------------ full size (BASELINE config 2)
+# ------------------------------------------------------------------ full size (benchmark configuration 2)
 def test_config2_full_size_properties(L, api, port):
     """[64,2048,4096] x [4096,4096] bf16. The oracle needs about a minute per batch item, so the full size is
     checked through properties: (1) B = a permutation matrix moves columns exactly (bit-exact);

@@ -152,7 +152,7 @@ def test_chain_golden_and_oracle(api, port, golden):
 
 
 def test_chain_full_size_properties(api):
-    """BASELINE config 4 shape [32,4096,4096]: rows of a softmax sum to one and are non-negative; the residual
+    """benchmark configuration 4 shape [32,4096,4096]: rows of a softmax sum to one and are non-negative; the residual
     is shared by the batch, so equal x rows in different batch items give equal outputs."""
     g = torch.Generator(device="cuda").manual_seed(3)
     x = torch.randn(32, 4096, 4096, device="cuda", generator=g)

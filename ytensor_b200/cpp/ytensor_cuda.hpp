@@ -146,6 +146,29 @@ struct Causal {
   bool tileAllFalse(int r0, int c0, int mr, int) const { return c0 > r0 + mr - 1 + offset; }
 };
 
+// YTensor<T, dim>::masked_matmul with the predicate `c <= r + offset` (reference src/ytensor_math.inl:368-412 with a
+// functor that has tileAllTrue / tileAllFalse): the device evaluates the predicate itself and skips the 128 x 128
+// output tiles it leaves empty (ytcuda_gemm_masked_causal); no mask tensor is built or uploaded.
+template <typename T, int dim0>
+yt::YTensor<T, dim0> masked_matmul(const yt::YTensor<T, dim0>& a, const yt::YTensor<T, 2>& b, const Causal& mask,
+                                   const T& maskedValue = T{}) {
+  static_assert(dim0 >= 2, "masked_matmul needs a rank >= 2 left operand");
+  if (a.shape(-1) != b.shape(-2)) throw std::invalid_argument("masked_matmul: inner dimensions do not match");
+  const int m = a.shape(-2), k = a.shape(-1), n = b.shape(-1);
+  DeviceBuffer da = detail::to_device(a), db = detail::to_device(b);
+  std::vector<int> oshape = a.shape();
+  oshape[dim0 - 1] = n;
+  yt::YTensor<T, dim0> out(oshape);
+  DeviceBuffer dc(out.size() * sizeof(T));
+  int64_t batch = 1;
+  for (int d = 0; d < dim0 - 2; ++d) batch *= a.shape(d);
+  check(ytcuda_gemm_masked_causal(dtype_of<T>(), dtype_of<T>(), da.get(), db.get(), dc.get(), m, n, k, k, 1, n, 1, n, 1,
+                                  batch, static_cast<int64_t>(m) * k, 0, static_cast<int64_t>(m) * n, mask.offset,
+                                  static_cast<float>(maskedValue), nullptr));
+  dc.download(out.data());
+  return out;
+}
+
 namespace detail {
 template <typename T>
 yt::YTensor<T, 5> sdpa(yt::YTensor<T, 5>& q, yt::YTensor<T, 5>& k, yt::YTensor<T, 5>& v, T scale, int mask_kind,
@@ -263,6 +286,111 @@ yt::YTensor<T, dim> layerNorm(const yt::YTensor<T, dim>& x, const yt::YTensor<T,
   const auto st = detail::contiguous_strides(x.shape());
   check(ytcuda_layernorm(dtype_of<T>(), dtype_of<T>(), dtype_of<T>(), dx.get(), dg.get(), db.get(), dy.get(),
                          shape.data(), st.data(), st.data(), dim, axes.data(), gdim, static_cast<float>(eps), nullptr));
+  dy.download(y.data());
+  return y;
+}
+
+// yt::function::normalize without gamma / bias: x / (sum_axes |x|^p + eps)^(1/p)
+// (include/function/normalization.hpp:91-107, src/function/normalization.inl:56-85, 278-318)
+template <typename T, int dim>
+yt::YTensor<T, dim> normalize(const yt::YTensor<T, dim>& x, const std::vector<int>& axes, T p = static_cast<T>(2),
+                              T eps = static_cast<T>(1e-12)) {
+  if (!(static_cast<float>(p) > 0.f)) throw std::invalid_argument("yt::function::normalize: p must be positive");
+  DeviceBuffer dx = detail::to_device(x);
+  yt::YTensor<T, dim> y(x.shape());
+  DeviceBuffer dy(y.size() * sizeof(T));
+  const auto shape = detail::widen(x.shape());
+  const auto st = detail::contiguous_strides(x.shape());
+  check(ytcuda_normalize(dtype_of<T>(), dtype_of<T>(), dx.get(), dy.get(), shape.data(), st.data(), st.data(), dim,
+                         axes.data(), static_cast<int>(axes.size()), static_cast<float>(p), static_cast<float>(eps),
+                         nullptr));
+  dy.download(y.data());
+  return y;
+}
+template <typename T, int dim>
+yt::YTensor<T, dim> normalize(const yt::YTensor<T, dim>& x, int axis = -1, T p = static_cast<T>(2),
+                              T eps = static_cast<T>(1e-12)) {
+  return normalize(x, std::vector<int>{axis}, p, eps);
+}
+
+namespace detail {
+// (x - mean) / sqrt(var + eps) over `axes` of a tensor given by shape and element strides (any view), no affine part
+template <typename T>
+void standardize(const void* dx, void* dy, const std::vector<int64_t>& shape, const std::vector<int64_t>& strides,
+                 const std::vector<int>& axes, float eps) {
+  check(ytcuda_layernorm(dtype_of<T>(), dtype_of<T>(), dtype_of<T>(), dx, nullptr, nullptr, dy, shape.data(),
+                         strides.data(), strides.data(), static_cast<int>(shape.size()), axes.data(),
+                         static_cast<int>(axes.size()), eps, nullptr));
+}
+template <typename T, int dim>
+int channel_axis(const yt::YTensor<T, dim>&, int channelAxis, const char* who) {
+  static_assert(dim >= 2, "requires dim >= 2");
+  const int c = ((channelAxis % dim) + dim) % dim;
+  if (c == 0) throw std::invalid_argument(std::string(who) + ": channelAxis must not be batch axis 0");
+  return c;
+}
+}  // namespace detail
+
+// yt::function::instanceNorm without gamma / bias: every (sample, channel) standardised over the remaining axes
+// (include/function/normalization.hpp:166-172, src/function/normalization.inl:378-433)
+template <typename T, int dim>
+yt::YTensor<T, dim> instanceNorm(const yt::YTensor<T, dim>& x, int channelAxis = 1, T eps = static_cast<T>(1e-5)) {
+  const int c = detail::channel_axis(x, channelAxis, "yt::function::instanceNorm_");
+  std::vector<int> axes;
+  for (int a = 1; a < dim; ++a)
+    if (a != c) axes.push_back(a);
+  if (axes.empty()) throw std::invalid_argument("yt::function::instanceNorm: requires at least one spatial axis");
+  DeviceBuffer dx = detail::to_device(x);
+  yt::YTensor<T, dim> y(x.shape());
+  DeviceBuffer dy(y.size() * sizeof(T));
+  detail::standardize<T>(dx.get(), dy.get(), detail::widen(x.shape()), detail::contiguous_strides(x.shape()), axes,
+                         static_cast<float>(eps));
+  dy.download(y.data());
+  return y;
+}
+
+// yt::function::batchNorm without gamma / bias: every channel standardised over all other axes, batch included;
+// statistics of the tensor itself (include/function/normalization.hpp:199-205, src/function/normalization.inl:435-489)
+template <typename T, int dim>
+yt::YTensor<T, dim> batchNorm(const yt::YTensor<T, dim>& x, int channelAxis = 1, T eps = static_cast<T>(1e-5)) {
+  const int c = detail::channel_axis(x, channelAxis, "yt::function::batchNorm_");
+  std::vector<int> axes;
+  for (int a = 0; a < dim; ++a)
+    if (a != c) axes.push_back(a);
+  DeviceBuffer dx = detail::to_device(x);
+  yt::YTensor<T, dim> y(x.shape());
+  DeviceBuffer dy(y.size() * sizeof(T));
+  detail::standardize<T>(dx.get(), dy.get(), detail::widen(x.shape()), detail::contiguous_strides(x.shape()), axes,
+                         static_cast<float>(eps));
+  dy.download(y.data());
+  return y;
+}
+
+// yt::function::groupNorm without gamma / bias (include/function/normalization.hpp:232-239,
+// src/function/normalization.inl:491-577): every (sample, group of channels) standardised over the group's channels
+// and the remaining axes. The grouped tensor is a strided VIEW [n, groups, channels / groups, rest...] of x and of
+// the result: the channel axis is split and moved next to the batch axis in the shape / stride lists only.
+template <typename T, int dim>
+yt::YTensor<T, dim> groupNorm(const yt::YTensor<T, dim>& x, int groups, int channelAxis = 1,
+                              T eps = static_cast<T>(1e-5)) {
+  const int c = detail::channel_axis(x, channelAxis, "yt::function::groupNorm_");
+  if (groups <= 0) throw std::invalid_argument("yt::function::groupNorm: groups must be positive");
+  const int ch = x.shape(c);
+  if (ch % groups) throw std::invalid_argument("yt::function::groupNorm: channel count must be divisible by groups");
+  static_assert(dim + 1 <= 8, "groupNorm: at most 7 dims");
+  const auto st = detail::contiguous_strides(x.shape());
+  std::vector<int64_t> gshape = {x.shape(0), groups, ch / groups}, gstride = {st[0], st[c] * (ch / groups), st[c]};
+  for (int a = 1; a < dim; ++a)
+    if (a != c) {
+      gshape.push_back(x.shape(a));
+      gstride.push_back(st[a]);
+    }
+  std::vector<int> axes;
+  for (int a = 2; a < static_cast<int>(gshape.size()); ++a) axes.push_back(a);
+  DeviceBuffer dx = detail::to_device(x);
+  yt::YTensor<T, dim> y(x.shape());
+  DeviceBuffer dy(y.size() * sizeof(T));
+  detail::standardize<T>(dx.get(), dy.get(), gshape, gstride, axes, static_cast<float>(eps));
   dy.download(y.data());
   return y;
 }
