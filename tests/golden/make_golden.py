@@ -2,7 +2,7 @@
 oracle/ref_shim.cpp into oracle/_ref/libyt_ref.so) on small seeded inputs.
 
 Run from the repository root, where the reference sources are available:
-    make -C oracle ref && python tests/golden/make_golden.py
+    make -C oracle ref REF=<YTensor source tree> && python tests/golden/make_golden.py
 Inputs are stored next to outputs, so the fixtures do not depend on a random generator staying
 stable. Cases named doc_* use the literal inputs of the reference's documentation examples
 (doc/en/api/function/fused.mdx:69-73 matmul, :190-201 scaledDotProductAttention).

@@ -1,7 +1,7 @@
 """Generates tests/golden/golden_ext.npz by running the UNMODIFIED reference (oracle/_ref/libyt_ref.so) on seeded
 inputs, for the operators beyond the first golden file:
 
-    make -C oracle ref && python tests/golden/make_golden_ext.py
+    make -C oracle ref REF=<YTensor source tree> && python tests/golden/make_golden_ext.py
 
   norm_*    yt::function::normalize (p = 2 and 1.5, one and two axes, affine), instanceNorm, batchNorm, groupNorm
             (channel axis 1 and 2, plain and affine)                     src/function/normalization.inl:278-577

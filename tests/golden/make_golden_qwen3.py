@@ -1,7 +1,7 @@
 """Generates tests/golden/golden_qwen3.npz by running the UNMODIFIED reference example model
 (example/qwen3, compiled behind oracle/ref_shim.cpp) on seeded random weights.
 
-    make -C oracle ref && python tests/golden/make_golden_qwen3.py
+    make -C oracle ref REF=<YTensor source tree> && python tests/golden/make_golden_qwen3.py
 
 Two cases:
   small_* : a 2-layer toy configuration; full logits of the prefill and of 5 greedy steps, batch 1 and 2.

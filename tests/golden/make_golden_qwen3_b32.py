@@ -1,7 +1,7 @@
 """Generates tests/golden/golden_qwen3_b32.npz: the UNMODIFIED reference example model (example/qwen3, compiled behind
 oracle/ref_shim.cpp) at the Qwen3-0.6B shape with 32 sequences at once.
 
-    make -C oracle ref && python tests/golden/make_golden_qwen3_b32.py      (about five minutes on 8 cores)
+    make -C oracle ref REF=<YTensor source tree> && python tests/golden/make_golden_qwen3_b32.py      (about five minutes on 8 cores)
 
 32 distinct prompts of 16 token ids (uniform in [0, vocab), seed 32), 32 greedy steps; per step and sequence the token,
 the margin between the best and second-best logit, and the 4 largest logits with their indices. The prompt is short

@@ -2,7 +2,7 @@
 past the end of its KV cache, which is a ring buffer (example/qwen3/src/qwen3.cpp:70-126): a 9-token prompt and 19
 single-token steps with max_position_embeddings = 16, so the cache fills at step 7 and the later steps overwrite the
 oldest slots; and a second run that feeds SEVERAL tokens per call across the end of the ring (two sequences).
-Run from the repository root: make -C oracle ref && python tests/golden/make_golden_qwen3_wrap.py
+Run from the repository root: make -C oracle ref REF=<YTensor source tree> && python tests/golden/make_golden_qwen3_wrap.py
 """
 from __future__ import annotations
 

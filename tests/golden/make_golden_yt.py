@@ -3,7 +3,7 @@
 ytensor_b200.ytfile.write_yt are read back correctly by the reference.
 
 Run from the repository root, where the reference sources are available:
-    make -C oracle ref && python tests/golden/make_golden_yt.py
+    make -C oracle ref REF=<YTensor source tree> && python tests/golden/make_golden_yt.py
 """
 from __future__ import annotations
 
