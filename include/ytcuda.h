@@ -104,7 +104,11 @@ int ytcuda_gemm(int dtype_in, int dtype_out, const void* A, const void* B, void*
 int ytcuda_gemm_set_path(int path);
 /* fp32 products (sgemm, include/kernel/avx2/sgemm.hpp:51-63) on the tensor cores: each operand is split into three
  * bfloat16 planes (24 mantissa bits) and the six partial products that matter at fp32 precision are laid side by
- * side along k and accumulated in fp32 by one bf16 GEMM (finite inputs; an infinity gives NaN). 0 = automatic (m, n, k >= 256 with n and k multiples of 8), 1 = never (FFMA kernel), 2 = whenever n and k
+ * side along k and accumulated in fp32 by one bf16 GEMM. Every finite input is represented exactly (values next to
+ * the largest float included). One deviation from sgemm: an INFINITE operand gives NaN in the outputs it reaches
+ * (its top plane meets zero or opposite-signed lower planes of the other operand) where sgemm gives the infinity;
+ * NaN inputs give NaN in both. Callers that rely on infinities select mode 1.
+ * 0 = automatic (m, n, k >= 256 with n and k multiples of 8), 1 = never (FFMA kernel), 2 = whenever n and k
  * are multiples of 8. Process-wide, meant for tests; no counterpart in the reference. */
 int ytcuda_gemm_set_f32_mode(int mode);
 

@@ -243,6 +243,39 @@ def test_fp32_on_tensor_cores_vs_oracle(L, api, port, m, n, k, batch):
     status_ok(L)
 
 
+@pytest.mark.gpu
+def test_fp32_on_tensor_cores_extreme_values(L, api):
+    """Values next to the largest float go through the three-plane split exactly (rounding the top plane would
+    overflow: it is truncated instead). An infinite operand is the one documented deviation: the tensor-core form
+    answers NaN in the outputs it reaches, the FFMA kernel answers the infinity as the reference's sgemm does."""
+    rng = np.random.default_rng(5)
+    m = n = k = 256
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = np.zeros((k, n), dtype=np.float32)
+    b[np.arange(k), np.arange(n)] = 0.5  # C = 0.5 * A: no sums, so huge values stay finite
+    big = np.float32(3.4e38)             # above the largest bfloat16 after rounding (3.39e38)
+    a[3, 7] = big
+    a[200, 100] = -np.float32(np.finfo(np.float32).max)
+    L.ytcuda_gemm_set_f32_mode(2)
+    try:
+        got = api.matmul(dev(a), dev(b)).cpu().numpy()
+        assert np.isfinite(got).all()
+        assert got[3, 7] == np.float32(0.5) * big and got[200, 100] == -np.float32(np.finfo(np.float32).max) * np.float32(0.5)
+        assert normwise(got, 0.5 * a) < F32_TOL
+        a[5, 9] = np.inf
+        got = api.matmul(dev(a), dev(b)).cpu().numpy()
+        assert np.isnan(got[5]).any() and np.isfinite(np.delete(got, 5, axis=0)).all()  # the deviation, row 5 only
+    finally:
+        L.ytcuda_gemm_set_f32_mode(0)
+    L.ytcuda_gemm_set_f32_mode(1)
+    try:
+        got = api.matmul(dev(a), dev(b)).cpu().numpy()
+        assert got[5, 9] == np.inf  # as sgemm: inf * 0.5
+    finally:
+        L.ytcuda_gemm_set_f32_mode(0)
+    status_ok(L)
+
+
 def test_fp32_split_keeps_extreme_values(L, api):
     """Values far apart in magnitude and 24-bit integers: the three-plane split must not lose them. (Non-finite
     inputs are outside the contract of this path: an infinity times the zero low planes of the other operand gives

@@ -934,7 +934,8 @@ static int launch_simt(int dtype_in, int dtype_out, const void* A, const void* B
 // bf16 GEMM with k' = 6 k forms their sum in its fp32 accumulator:
 //   left operand  (is_b == 0, x is [rows = m][cols = k]): out[b][i][c k + j] = plane_a(c) of x[b][i][j]
 //   right operand (is_b == 1, x is [rows = k][cols = n]): out[b][c k + i][j] = plane_b(c) of x[b][i][j]
-// with plane_a = l m h m h h and plane_b = h m l h m h. Non-finite values keep m = l = 0.
+// with plane_a = l m h m h h and plane_b = h m l h m h. Non-finite values keep m = l = 0 (an infinite operand then
+// meets zero planes of the other operand and the sum becomes NaN where the FFMA kernel gives the infinity).
 __global__ void __launch_bounds__(256) gemm_split3_kernel(const float* x, int64_t rs, int64_t cs, int64_t bs, int rows,
                                                           int cols, int64_t batch, int is_b, __nv_bfloat16* out) {
   const int64_t per = static_cast<int64_t>(rows) * cols;
@@ -947,7 +948,13 @@ __global__ void __launch_bounds__(256) gemm_split3_kernel(const float* x, int64_
     __nv_bfloat16 p[3];  // h, m, l
     p[0] = __float2bfloat16_rn(v);
     p[1] = p[2] = __float2bfloat16_rn(0.f);
-    const float fh = __bfloat162float(p[0]);
+    float fh = __bfloat162float(p[0]);
+    if (!isfinite(fh) && isfinite(v)) {
+      // a finite value so close to the largest float that rounding its top plane overflows: truncate instead, the
+      // two lower planes still hold the remaining 16 mantissa bits exactly
+      fh = __uint_as_float(__float_as_uint(v) & 0xffff0000u);
+      p[0] = __float2bfloat16_rn(fh);
+    }
     if (isfinite(fh)) {
       const float r1 = v - fh;
       p[1] = __float2bfloat16_rn(r1);
