@@ -425,6 +425,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           float a0 = ident, a1 = ident, a2 = ident, a3 = ident;
 #pragma unroll 1
           for (int c0 = 0; c0 < FA_BN; c0 += 64) {
+            if (!full && __all_sync(0xffffffffu, cl < c0)) continue;  // no row of this warp sees these columns
             uint32_t r[64];
             tmem_ld_32x32b_x64(ts + c0, r);
             tmem_ld_wait();
@@ -521,29 +522,42 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         if (!elementwise_mask) {
 #pragma unroll 1
           for (int c0 = 0; c0 < FA_BN; c0 += 64) {
-            uint32_t r[64];
-            tmem_ld_32x32b_x64(ts + c0, r);
-            tmem_ld_wait();
             uint32_t pk[32];
-            if (full) {
+            // limited tiles: a 64-column half that no row of this warp sees (right of the causal diagonal, past
+            // the last key) is written as zeros without reading S or computing exponentials
+            const bool dead = !full && __all_sync(0xffffffffu, cl < c0);
+            if (dead) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) pk[e] = 0u;
+            } else {
+              uint32_t r[64];
+              tmem_ld_32x32b_x64(ts + c0, r);
+              tmem_ld_wait();
+              const int cc = cl - c0;  // limited tiles: columns 0..cc of this half are visible
               const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
               uint64_t lacc = f2_pack(0.f, 0.f), lacc2 = f2_pack(0.f, 0.f);
-              auto body = [&](auto is_bf) {
+              auto body = [&](auto is_bf, auto is_limited) {
 #pragma unroll
                 for (int e = 0; e < 64; e += 2) {
                   const uint64_t x2 =
                       f2_fma(f2_pack(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sc2, nm2);
                   float p0, p1;
-                  if (FA_EMU_EVERY > 0 && ((e >> 1) % (FA_EMU_EVERY > 0 ? FA_EMU_EVERY : 1)) == FA_EMU_EVERY - 1) {
+                  const bool emu =
+                      FA_EMU_EVERY > 0 && ((e >> 1) % (FA_EMU_EVERY > 0 ? FA_EMU_EVERY : 1)) == FA_EMU_EVERY - 1;
+                  if (emu) {
                     exp2_emu2(x2, p0, p1);
-                    lacc2 = f2_add(lacc2, f2_pack(p0, p1));
                   } else {
                     float t0, t1;
                     f2_unpack(x2, t0, t1);
                     p0 = fast_exp2(t0);
                     p1 = fast_exp2(t1);
-                    lacc = f2_add(lacc, f2_pack(p0, p1));
                   }
+                  if (decltype(is_limited)::value) {  // a hidden score may be anything, its P is exactly zero
+                    p0 = (e <= cc) ? p0 : 0.f;
+                    p1 = (e + 1 <= cc) ? p1 : 0.f;
+                  }
+                  if (emu) lacc2 = f2_add(lacc2, f2_pack(p0, p1));
+                  else lacc = f2_add(lacc, f2_pack(p0, p1));
                   if (decltype(is_bf)::value) {
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&h);
@@ -553,24 +567,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                   }
                 }
               };
-              if (p.is_bf16) body(std::true_type{});
-              else body(std::false_type{});
+              if (full) {
+                if (p.is_bf16) body(std::true_type{}, std::false_type{});
+                else body(std::false_type{}, std::false_type{});
+              } else {
+                if (p.is_bf16) body(std::true_type{}, std::true_type{});
+                else body(std::false_type{}, std::true_type{});
+              }
               float la, lb;
               f2_unpack(f2_add(lacc, lacc2), la, lb);
               l0 += la;
               l1 += lb;
-            } else {
-              const int cc = cl - c0;
-#pragma unroll
-              for (int e = 0; e < 64; e += 2) {
-                float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_m));
-                float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_m));
-                p0 = (e <= cc) ? p0 : 0.f;
-                p1 = (e + 1 <= cc) ? p1 : 0.f;
-                l0 += p0;
-                l1 += p1;
-                pk[e >> 1] = pack2(p0, p1);
-              }
             }
             tmem_st_32x32b_x32(ts + (c0 >> 1), pk);
             if (c0 == 0) publish_half();
