@@ -1002,14 +1002,14 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
     // barrier-free form never waits for a unit of its own CTA)
     const bool ll = m->tp_world == 1 && m->decode_path != 5 && (m->hidden + sm_count() - 1) / sm_count() + 1 <= LL_MAX_OWN &&
                     (p.chunks == 1 || B * m->l_kv_heads * p.chunks <= sm_count()) && p.chunks <= DS_MAX_CHUNKS_LL;
-    const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128) + (ll ? (DS_WARPS * 4 + 4 * LL_MAX_OWN) * 4 : 0);
+    const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128) + (ll ? (DS_WARPS * 4 + 4 * LL_MAX_OWN + LL_PART_FLOATS) * 4 : 0);
     int xs_bytes = mt * ll_row_floats(kmax) * static_cast<int>(sizeof(float));  // (rows padded to whole 256-column blocks)
     if (xs_bytes < att) xs_bytes = att;
     xs_bytes = (xs_bytes + 127) / 128 * 128;
     int nslot = (227 * 1024 - head - xs_bytes) / DW_CHUNK;
     if (nslot > DW_MAX_SLOTS) nslot = DW_MAX_SLOTS;
     const bool fits = nslot >= 2 && kmax * 2 <= DW_CHUNK && m->hidden * 4 <= DW_CHUNK && m->hidden % 8 == 0 &&
-                      m->l_inter % 8 == 0;
+                      m->l_inter % 8 == 0 && (!ll || (m->hidden % 64 == 0 && m->l_inter % 64 == 0));
     if (fits && ll) {
       const int qkv_w = (m->l_heads + 2 * m->l_kv_heads) * D;
       const size_t part_pairs = static_cast<size_t>(B) * m->l_kv_heads * DS_MAX_CHUNKS_LL * groups * (2 + D);
