@@ -216,7 +216,7 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
       bool ready = true;
 #pragma unroll
       for (int j = 0; j < LL_GROUP; ++j)
-        if (j < gc) ready &= mbar_try_wait(&S.full[slots[j]], pars[j]);
+        if (j < gc) ready &= mbar_test_wait(&S.full[slots[j]], pars[j]);
       if (!ready) {
 #pragma unroll
         for (int j = 0; j < LL_GROUP; ++j)
@@ -243,59 +243,42 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
       const int sl = jc == 0 ? slots[0] : jc == 1 ? slots[1] : jc == 2 ? slots[2] : slots[3];
       return ring + static_cast<size_t>(sl) * DW_CHUNK + (off + (up ? nrj : 0)) * row_bytes + q4 * 16;
     };
-    const char* wa[LL_GROUP];  // this lane's 16 bytes of row g of tile t
-    const char* wb[LL_GROUP];  // ... of row g + 8
-#pragma unroll
-    for (int t = 0; t < LL_GROUP; ++t) {
-      wa[t] = wb[t] = ring;
-      if (t < T) {
-        wa[t] = row_ptr(16 * t + gq);
-        wb[t] = row_ptr(16 * t + gq + 8);
-      }
-    }
-    // Chunk after chunk; a trip takes two neighbouring k blocks (128 bytes of every row) with accumulators of their
-    // own and issues all its loads before the first MMA. Weight rows lie a multiple of 128 bytes apart, so eight rows
+    // Tile after tile (a real loop: straight-line code runs at the speed of instruction fetch here, a loop body is
+    // fetched once); a trip takes two neighbouring k blocks (128 bytes of every row) with accumulators of their own
+    // and issues all its loads before the first MMA. Weight rows lie a multiple of 128 bytes apart, so eight rows
     // reading the same 64 bytes would meet in the same banks: rows with odd g read the two blocks in the opposite
     // order (each quarter warp then covers all 32 banks) and swap the registers afterwards.
-    float acc[LL_GROUP][4];
     const bool odd = (gq & 1) != 0;
     const int h1 = odd ? 64 : 0, h2 = 64 - h1;
-#pragma unroll
-    for (int j = 0; j < LL_GROUP; ++j) {
-      float a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
-      if (j < T) {
 #pragma unroll 1
-        for (int kp = warp; kp < nkp; kp += LL_WARPS) {
-          const int o = kp * 128;
-          uint4 bx = make_uint4(0u, 0u, 0u, 0u), bx2 = bx;
-          if (b_on) {
-            bx = *reinterpret_cast<const uint4*>(bsrc + o);
-            bx2 = *reinterpret_cast<const uint4*>(bsrc + o + 64);
-          }
-          const uint4 r1 = *reinterpret_cast<const uint4*>(wa[j] + o + h1);
-          const uint4 r2 = *reinterpret_cast<const uint4*>(wa[j] + o + h2);
-          const uint4 s1 = *reinterpret_cast<const uint4*>(wb[j] + o + h1);
-          const uint4 s2 = *reinterpret_cast<const uint4*>(wb[j] + o + h2);
-          const uint4 a_lo = odd ? r2 : r1, c_lo = odd ? r1 : r2;  // first / second block of rows g
-          const uint4 a_hi = odd ? s2 : s1, c_hi = odd ? s1 : s2;  // ... of rows g + 8
-          ds_mma_bf16(a1, a_lo.x, a_hi.x, a_lo.y, a_hi.y, bx.x, bx.y);
-          ds_mma_bf16(a2, c_lo.x, c_hi.x, c_lo.y, c_hi.y, bx2.x, bx2.y);
-          ds_mma_bf16(a1, a_lo.z, a_hi.z, a_lo.w, a_hi.w, bx.z, bx.w);
-          ds_mma_bf16(a2, c_lo.z, c_hi.z, c_lo.w, c_hi.w, bx2.z, bx2.w);
+    for (int t = 0; t < T; ++t) {
+      const char* wa = row_ptr(16 * t + gq);      // this lane's 16 bytes of row g of the tile
+      const char* wb = row_ptr(16 * t + gq + 8);  // ... of row g + 8
+      float a1[4] = {0.f, 0.f, 0.f, 0.f}, a2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+      for (int kp = warp; kp < nkp; kp += LL_WARPS) {
+        const int o = kp * 128;
+        uint4 bx = make_uint4(0u, 0u, 0u, 0u), bx2 = bx;
+        if (b_on) {
+          bx = *reinterpret_cast<const uint4*>(bsrc + o);
+          bx2 = *reinterpret_cast<const uint4*>(bsrc + o + 64);
         }
+        const uint4 r1 = *reinterpret_cast<const uint4*>(wa + o + h1);
+        const uint4 r2 = *reinterpret_cast<const uint4*>(wa + o + h2);
+        const uint4 s1 = *reinterpret_cast<const uint4*>(wb + o + h1);
+        const uint4 s2 = *reinterpret_cast<const uint4*>(wb + o + h2);
+        const uint4 a_lo = odd ? r2 : r1, c_lo = odd ? r1 : r2;  // first / second block of rows g
+        const uint4 a_hi = odd ? s2 : s1, c_hi = odd ? s1 : s2;  // ... of rows g + 8
+        ds_mma_bf16(a1, a_lo.x, a_hi.x, a_lo.y, a_hi.y, bx.x, bx.y);
+        ds_mma_bf16(a2, c_lo.x, c_hi.x, c_lo.y, c_hi.y, bx2.x, bx2.y);
+        ds_mma_bf16(a1, a_lo.z, a_hi.z, a_lo.w, a_hi.w, bx.z, bx.w);
+        ds_mma_bf16(a2, c_lo.z, c_hi.z, c_lo.w, c_hi.w, bx2.z, bx2.w);
       }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[j][e] = a1[e] + a2[e];
-    }
-    // accumulator columns 2 q and 2 q + 1 are the hi and lo products of sequence q: rows g and g + 8
-    if (q4 < B) {
-#pragma unroll
-      for (int j = 0; j < LL_GROUP; ++j) {
-        if (j < T) {
-          float* pj = part + ((warp * LL_GROUP + j) * 16) * MT;
-          pj[gq * MT + q4] = acc[j][0] + acc[j][1];
-          pj[(gq + 8) * MT + q4] = acc[j][2] + acc[j][3];
-        }
+      // accumulator columns 2 q and 2 q + 1 are the hi and lo products of sequence q: rows g and g + 8
+      if (q4 < B) {
+        float* pj = part + ((warp * LL_GROUP + t) * 16) * MT;
+        pj[gq * MT + q4] = (a1[0] + a2[0]) + (a1[1] + a2[1]);
+        pj[(gq + 8) * MT + q4] = (a1[2] + a2[2]) + (a1[3] + a2[3]);
       }
     }
 #ifdef LL_TRACE_FINE
@@ -677,6 +660,18 @@ __global__ void __launch_bounds__(LL_THREADS, 1) decode_ll_kernel(const DecodeSt
     S.nw[i][3] = W.norm2;
   }
   __syncthreads();  // (the only synchronisation of all nine warps)
+  // K / V rows of this CTA's first attention unit: the issuing lane asks for them into the L2 (one bulk prefetch each
+  // per layer) when it starts on the layer's weights, most of a layer ahead of the attention phase
+  uint32_t kv_bytes = 0;
+  int64_t kv_off = 0;
+  if (static_cast<int>(blockIdx.x) < B * p.kv_heads * p.chunks) {
+    const int chunk = blockIdx.x % p.chunks, bk = blockIdx.x / p.chunks;
+    const int k_begin = chunk * p.keys_per_chunk;
+    int k_end = k_begin + p.keys_per_chunk;
+    if (k_end > p.n_keys) k_end = p.n_keys;
+    kv_off = (static_cast<int64_t>(bk) * p.max_pos + k_begin) * D;
+    kv_bytes = k_end > k_begin ? static_cast<uint32_t>(k_end - k_begin) * D * 4u : 0u;
+  }
   if (threadIdx.x >= LL_WORKERS) {
     // The issuing warp: one lane keeps the ring full. Chunk number n may be issued once chunk n - nslot has been
     // consumed (the workers publish the count after the synchronisation that ends a group of chunks), so the copies
@@ -685,8 +680,16 @@ __global__ void __launch_bounds__(LL_THREADS, 1) decode_ll_kernel(const DecodeSt
       DwIssuer iss{0, 0, 0, 0};
       const long long t0 = clock64();
       long long last = t0;
+      int pf_layer = 0;  // next layer whose K / V rows have not been asked for
       while (iss.next < S.total) {
         if (*reinterpret_cast<volatile int*>(&S.abort_word)) break;
+        if (kv_bytes && pf_layer < p.layers && iss.next >= pf_layer * S.per_layer) {
+          const float* kr = p.k_cache + static_cast<size_t>(pf_layer) * p.cache_layer + kv_off;
+          const float* vr = p.v_cache + static_cast<size_t>(pf_layer) * p.cache_layer + kv_off;
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(kr), "r"(kv_bytes) : "memory");
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vr), "r"(kv_bytes) : "memory");
+          ++pf_layer;
+        }
         const int consumed = *reinterpret_cast<volatile int*>(&S.consumed);
         if (iss.next < consumed + S.nslot) {
           dw_issue_next(S, p, ring, iss);
@@ -735,18 +738,6 @@ __global__ void __launch_bounds__(LL_THREADS, 1) decode_ll_kernel(const DecodeSt
     ll_sync();
   }
 
-  // K / V rows of this CTA's first attention unit, requested into the L2 one phase ahead
-  int kv_lines = 0;
-  int64_t kv_off = 0;
-  if (static_cast<int>(blockIdx.x) < B * p.kv_heads * p.chunks) {
-    const int chunk = blockIdx.x % p.chunks, bk = blockIdx.x / p.chunks;
-    const int k_begin = chunk * p.keys_per_chunk;
-    int k_end = k_begin + p.keys_per_chunk;
-    if (k_end > p.n_keys) k_end = p.n_keys;
-    kv_off = (static_cast<int64_t>(bk) * p.max_pos + k_begin) * D;
-    kv_lines = k_end > k_begin ? (k_end - k_begin) * 4 : 0;
-  }
-
   // One loop body serves every phase (the functions are inlined exactly once: a call through the ABI with this
   // many live registers costs more than the phase's arithmetic).
   const int n_phases = 5 * p.layers + 1;
@@ -771,14 +762,6 @@ __global__ void __launch_bounds__(LL_THREADS, 1) decode_ll_kernel(const DecodeSt
         kind = 4; stage = 0; src = p.ll_x; st = t - 1; nw = p.final_norm; epi = 3; dst = nullptr; dt = 0u; ld = p.vocab_rows;
       } else if (sub == 0) {        // qkv = rmsNorm(x) . Wqkv^T (layer 0: x is the embedding staged above)
         kind = 0; stage = l == 0 ? 3 : 0; src = p.ll_x; st = t - 1; nw = S.nw[l][2]; epi = 0; dst = p.ll_qkv; dt = t; ld = qkv_w;
-        if (kv_lines > 0) {
-          const char* kr = reinterpret_cast<const char*>(p.k_cache + static_cast<size_t>(l) * p.cache_layer + kv_off);
-          const char* vr = reinterpret_cast<const char*>(p.v_cache + static_cast<size_t>(l) * p.cache_layer + kv_off);
-          for (int i = threadIdx.x; i < kv_lines; i += LL_WORKERS) {
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(kr + i * 128));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(vr + i * 128));
-          }
-        }
       } else if (sub == 2) {        // x += attn . Wo^T
         kind = 1; stage = 1; src = p.ll_att; st = t + 1; epi = 1; dst = p.ll_x; dt = t + 2; ld = H;
       } else if (sub == 3) {        // act = swish(gate) * up
