@@ -329,7 +329,8 @@ int ytcuda_qwen3_cache_len(void* handle);
  * 3 = as 2, with the FFMA form of the kernel's linear phases even where the tensor-core form (five or more
  * sequences, hidden <= 1024) applies. Up to four sequences the kernel streams its weights through a ring of
  * shared-memory slots filled by bulk async copies that run ahead of the phases and, on one GPU, has no grid barriers:
- * the activations that cross between phases are stored as {value, tag} pairs that the consumers poll; 4 = as 3 without
+ * the activations that cross between phases are stored as {value, tag} pairs that the consumers poll, and the linear
+ * phases run on mma.sync with the activations split into two bf16 planes (paths 0, 2 and 3 alike); 4 = as 3 without
  * the ring (every phase loads its weights after the barrier before it); 5 = the ring with grid barriers.
  * Both forms compute the operator sequence of Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has
  * no counterpart in the reference. */
