@@ -55,11 +55,13 @@ def test_small_model_logits_match_reference(Q, qwen3_golden, B):
     m.close()
 
 
-@pytest.mark.parametrize("B", [1, 2, 3, 5, 8, 13, 16, 32])
+@pytest.mark.parametrize("B", [1, 2, 3, 4, 5, 8, 13, 16, 32])
 def test_single_kernel_decode_step_matches_operator_path(Q, B):
     """The persistent step kernel (path 2: up to four sequences without grid barriers, activations exchanged as
-    tagged pairs and weights streamed through a shared-memory ring, tensor-core linear phases from five sequences on;
-    path 3: FFMA linear phases; path 4: the form without the weight ring; path 5: the ring with grid barriers)
+    tagged pairs, weights streamed through a shared-memory ring, linear phases on mma.sync from bf16 planes of the
+    activations; from five sequences on the kernel with grid barriers and tensor-core linear phases;
+    path 3: FFMA linear phases where the kernel with grid barriers runs; path 4: the form without the weight ring;
+    path 5: the ring with grid barriers)
     and the one-launch-per-operator forward compute the same logits and leave the same KV cache behind: 70 steps
     after a 40-token prompt (the attention of the step kernel goes from 2 to 4 key chunks), every model fed the
     tokens of the operator path."""

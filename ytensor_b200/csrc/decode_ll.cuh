@@ -315,6 +315,35 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
       if (epi == 2) {
         ll_st(dst + static_cast<int64_t>(m) * ld + n, ds_swish(y) * (y2 * inv[m]), dst_tag);
       } else if (epi == 1) {
+        if (p.tp_world > 1) {
+          // y is this rank's share of the sum over k: push it into every peer's pair area, then add the shares of
+          // all ranks in rank order (the same order everywhere: every rank holds bitwise the same x)
+          const size_t per_src = static_cast<size_t>(2) * 4 * p.hidden;
+          const size_t at = (static_cast<size_t>(kind == 3 ? 1 : 0) * 4 + m) * p.hidden + n;
+          for (int q = 0; q < p.tp_world; ++q) {
+            if (q == p.tp_rank) continue;
+            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p.ll_mail[q] + p.tp_rank * per_src + at),
+                         "r"(__float_as_uint(y)), "r"(dst_tag)
+                         : "memory");
+          }
+          float tot = 0.f;
+          const long long t0 = clock64();
+          for (int r = 0; r < p.tp_world; ++r) {
+            float v = y;
+            if (r != p.tp_rank) {
+              const uint2* src_pair = p.ll_mail[p.tp_rank] + r * per_src + at;
+              uint2 pr;
+              int spins = 0;
+              while (true) {
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(pr.x), "=r"(pr.y) : "l"(src_pair) : "memory");
+                if (pr.y == dst_tag || ll_expired(p, &S.abort_word, t0, spins++)) break;
+              }
+              v = __uint_as_float(pr.x);
+            }
+            tot += v;
+          }
+          y = tot;
+        }
         float* xo = x_own + m * LL_MAX_OWN + (n - ph.r0);
         const float y0 = xo[0] + y;
         xo[0] = y0;

@@ -94,6 +94,10 @@ struct DecodeStepParams {
   // this launch
   uint2 *ll_x, *ll_qkv, *ll_att, *ll_act, *ll_part;
   unsigned int ll_base;
+  // decode_ll_kernel under tensor parallelism: ll_mail[q] is rank q's pair area [source rank][2][4][hidden] (own
+  // memory or the peer's): a rank PUSHES its partial sums of the o and down projections as pairs into slot
+  // [its rank] of every peer's area and polls its own area for the peers' pairs
+  uint2* ll_mail[DS_MAX_TP];
 };
 
 __device__ __forceinline__ float ds_ldcg(const float* p) { return __ldcg(p); }

@@ -437,7 +437,11 @@ struct Qwen3Model {
 static size_t tp_flags_offset(int hidden) {
   return (static_cast<size_t>(2) * DS_MAX_B * hidden * sizeof(float) + 255) / 256 * 256;
 }
-static size_t tp_comm_bytes(int hidden) { return tp_flags_offset(hidden) + 256; }
+// Behind the flag words: the pair area of the barrier-free step kernel, [source rank][2][4][hidden] {bits, tag} pairs.
+static size_t tp_pairs_offset(int hidden) { return tp_flags_offset(hidden) + 256; }
+static size_t tp_comm_bytes(int hidden) {
+  return tp_pairs_offset(hidden) + static_cast<size_t>(DS_MAX_TP) * 2 * 4 * hidden * sizeof(uint2);
+}
 
 static int dev_alloc(Qwen3Model* m, void** p, size_t bytes) {
   YTC_CUDA(cudaMalloc(p, bytes));
@@ -731,8 +735,9 @@ int ytcuda_qwen3_tp_resync(void* handle) {
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m, "ytcuda_qwen3_tp_resync: null handle");
   YTC_CUDA(cudaDeviceSynchronize());
-  if (m->tp_comm) YTC_CUDA(cudaMemset(m->tp_comm + tp_flags_offset(m->hidden), 0, 256));
+  if (m->tp_comm) YTC_CUDA(cudaMemset(m->tp_comm, 0, tp_comm_bytes(m->hidden)));  // flags, mailboxes and pairs
   m->ar_seq = 0;
+  m->ll_base = 0xFFFFFFFFu;  // the barrier-free kernel starts again from clean pair buffers and tag 1
   m->cur_len = 0;
   m->total_written = 0;
   return YTC_OK;
@@ -971,6 +976,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
       char* base = r == m->tp_rank ? m->tp_comm : m->tp_peer[r];
       p.mail[r] = reinterpret_cast<float*>(base);
       p.flags[r] = reinterpret_cast<unsigned int*>(base + flags_at);
+      p.ll_mail[r] = reinterpret_cast<uint2*>(base + tp_pairs_offset(m->hidden));
     }
     p.go = reinterpret_cast<unsigned int*>(m->tp_comm + flags_at) + 16;
   }
@@ -980,7 +986,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   // Key chunks of 128 keys (8 per warp), fewer and longer ones when that would be more units than CTAs or more
   // than DS_MAX_CHUNKS chunks.
   // (The barrier-free form has seven worker warps of 16 keys each: chunks of 112 keys keep every warp at one pass.)
-  const bool ll_shape = !mma && mt <= 4 && m->tp_world == 1 && m->decode_path != 4 && m->decode_path != 5;
+  const bool ll_shape = !mma && mt <= 4 && m->decode_path != 4 && m->decode_path != 5;
   const int unit_keys = ll_shape ? LL_WARPS * DS_KB : 128;
   int n_chunks = (keys + unit_keys - 1) / unit_keys;
   const int fit = sm_count() / (B * m->l_kv_heads);
@@ -1000,7 +1006,7 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
   if (!mma && mt <= 4 && m->decode_path != 4 && m->layers <= DW_MAX_LAYERS) {
     // (a CTA holds at most one attention unit unless there is a single key chunk: the collecting unit of the
     // barrier-free form never waits for a unit of its own CTA)
-    const bool ll = m->tp_world == 1 && m->decode_path != 5 && (m->hidden + sm_count() - 1) / sm_count() + 1 <= LL_MAX_OWN &&
+    const bool ll = m->decode_path != 5 && (m->hidden + sm_count() - 1) / sm_count() + 1 <= LL_MAX_OWN &&
                     (p.chunks == 1 || B * m->l_kv_heads * p.chunks <= sm_count()) && p.chunks <= DS_MAX_CHUNKS_LL;
     const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128) + (ll ? (DS_WARPS * 4 + 4 * LL_MAX_OWN + LL_PART_FLOATS) * 4 : 0);
     int xs_bytes = mt * ll_row_floats(kmax) * static_cast<int>(sizeof(float));  // (rows padded to whole 256-column blocks)

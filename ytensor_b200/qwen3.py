@@ -207,8 +207,8 @@ class Qwen3ForCausalLM:
         if self.batch <= limit:
             if self.batch < 5:
                 return ("decode_ll_kernel (no grid barriers: tagged-pair activations, weights through a shared-memory "
-                        "ring, mma.sync linear phases)" if self.tp_world == 1
-                        else "decode_step_kernel (FFMA linear phases)")
+                        "ring, mma.sync linear phases" +
+                        (")" if self.tp_world == 1 else "; partial sums pushed to the peers as pairs over NVLink)"))
             return "decode_step_kernel (mma.sync linear phases)"
         return "gemm_tc_kernel (hi + lo planes, split-k pieces) + attn_decode_fast_kernel + fused glue kernels"
 
