@@ -343,8 +343,9 @@ int ytcuda_qwen3_set_trace(void* handle, int64_t* dev_buf, int slots_per_cta);
 /* Tensor-parallel decode steps without a host-side collective: every rank exports the CUDA IPC handle (64 bytes) of
  * its exchange buffer, the caller distributes the handles (one all-gather at start-up), and every rank imports its
  * peers'. From then on a forward of one token per sequence (batch <= 8) is ONE kernel per rank that all-reduces the
- * partial sums of the o and down projections itself, by loads from the peers' buffers over NVLink. All ranks must
- * call forward the same number of times. The all-reduce callback is still used for longer inputs. No counterpart in
+ * partial sums of the o and down projections itself over NVLink: up to four sequences by pushing {value, tag} pairs
+ * into the peers' buffers and polling its own, beyond that by loads from the peers' buffers behind a barrier. All
+ * ranks must call forward the same number of times. The all-reduce callback is still used for longer inputs. No counterpart in
  * the reference (single process). */
 int ytcuda_qwen3_tp_export(void* handle, void* ipc_handle_64);
 int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64);

@@ -1,4 +1,5 @@
-// One decode step (up to four sequences, one GPU) as ONE kernel WITHOUT grid barriers.
+// One decode step (up to four sequences; one GPU, or one rank of a tensor-parallel group) as ONE kernel WITHOUT grid
+// barriers.
 //
 // A decode step of the 0.6B shape is 141 dependent phases of a few microseconds; with a grid barrier between them
 // every phase pays three trips through the L2 (arrive, poll, then load what the others wrote) on top of its work. Here
@@ -20,6 +21,11 @@
 //             keeps them in shared memory for the whole step: x += y never reads x back from global memory.
 //   weights   stream through the shared-memory ring of decode_stream.cuh (bulk async copies that run ahead of the
 //             phases by the depth of the ring).
+//   ranks     tensor parallel (heads and FFN columns split): the thread that finishes a row of the o or down projection
+//             pushes its rank's share as a pair into slot [its rank] of every peer's pair area (NVLink stores), polls
+//             its own area for the peers' shares and adds all of them in rank order: every rank holds bitwise the same
+//             residual. A slot is rewritten one layer later, by when its reader has long passed (it has produced the
+//             next exchange's share, which needs every CTA of its GPU to have finished this one).
 //   rmsNorm   x * weight is staged while the sum of squares is reduced; 1 / sqrt(mean + eps) multiplies the finished
 //             dot products (one pass over the row, one block-wide synchronisation).
 //   attention (sequence, kv head, key chunk) units as in decode_step.cuh; the units of chunks 1, 2, ... store their
