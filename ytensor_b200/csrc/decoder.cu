@@ -177,6 +177,7 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float* part, in
 // the tensor-core products that together carry 16 mantissa bits of the activation.
 __global__ void __launch_bounds__(256) split_hi_lo_kernel(const float* x, int64_t x_rs, uint16_t* hi, uint16_t* lo,
                                                           int64_t rows, int K) {
+  dependent_trigger();  // the GEMM queued behind this kernel may be scheduled and set itself up meanwhile
   const int per_row = K / 4;
   const int64_t total = rows * per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -242,6 +243,7 @@ __device__ __forceinline__ float4 sum_pieces4(const float* part, int n_part, int
 __global__ void __launch_bounds__(1024) sum_norm_split_kernel(const float* part, int n_part, int64_t mn, float* x,
                                                               const float* w, float eps, uint16_t* hi, uint16_t* lo,
                                                               int hidden) {
+  dependent_trigger();  // the GEMM queued behind this kernel may be scheduled and set itself up meanwhile
   extern __shared__ float row_s[];  // [4][hidden]: the sums of the four thread groups, then (in [0]) the row
   __shared__ float red[32];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
@@ -297,6 +299,7 @@ __global__ void __launch_bounds__(1024) sum_norm_split_kernel(const float* part,
 // planes [rows][inter] for the down projection. Three launches (sum_partials, swiglu, split_hi_lo) as one.
 __global__ void __launch_bounds__(256) sum_swiglu_split_kernel(const float* part, int n_part, int64_t mn, uint16_t* hi,
                                                                uint16_t* lo, int64_t rows, int inter) {
+  dependent_trigger();  // the GEMM queued behind this kernel may be scheduled and set itself up meanwhile
   const int per_row = inter / 4;
   const int64_t total = rows * per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -1109,6 +1112,10 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
 // ids [batch, len] (device int32) -> logits [batch, this rank's vocab rows] (device fp32) of the LAST position;
 // appends `len` tokens to the KV caches (qwen3::Qwen3ForCausalLM::forward, reference qwen3.cpp:449-457).
 int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logits, void* stream) {
+  struct OverlapGuard {
+    OverlapGuard() { overlap_scope() = true; }
+    ~OverlapGuard() { overlap_scope() = false; }
+  } overlap_guard;  // the tile GEMMs of this forward are queued as programmatic dependent launches
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m && ids && logits, "ytcuda_qwen3_forward: null argument");
   YTC_REQUIRE(len > 0, "ytcuda_qwen3_forward: len must be positive");

@@ -169,6 +169,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched shared and tensor memory only: under a programmatic dependent launch it ran while the
+  // kernel before this one was finishing. From here on global memory is read and written.
+  dependent_wait();
+  dependent_trigger();
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
 
@@ -873,11 +877,11 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
   if (BN == 256) {
     const int s = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc_kernel<256>), TcSmem<256>::DYN_BYTES);
     if (s != YTC_OK) return s;
-    gemm_tc_kernel<256><<<grid, TC_THREADS, TcSmem<256>::DYN_BYTES, st>>>(tmA, tmB, p);
+    YTC_CUDA(launch_overlapped(gemm_tc_kernel<256>, dim3(grid), dim3(TC_THREADS), TcSmem<256>::DYN_BYTES, st, tmA, tmB, p));
   } else {
     const int s = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc_kernel<128>), TcSmem<128>::DYN_BYTES);
     if (s != YTC_OK) return s;
-    gemm_tc_kernel<128><<<grid, TC_THREADS, TcSmem<128>::DYN_BYTES, st>>>(tmA, tmB, p);
+    YTC_CUDA(launch_overlapped(gemm_tc_kernel<128>, dim3(grid), dim3(TC_THREADS), TcSmem<128>::DYN_BYTES, st, tmA, tmB, p));
   }
   count_launch();
   if (live) cudaFreeAsync(live, st);

@@ -17,6 +17,10 @@ static thread_local char g_err[512] = {0};
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<uint64_t> g_h2d{0}, g_d2h{0};
 void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+bool& overlap_scope() {
+  static thread_local bool on = false;
+  return on;
+}
 
 void set_last_error(const char* fmt, ...) {
   va_list ap;

@@ -266,6 +266,32 @@ int ensure_dynamic_smem(const void* fn, int bytes);
 // Cycle budget of bounded device-side waits (ytcuda_set_wait_limit).
 long long wait_cycle_limit();
 
+// Programmatic dependent launch. A kernel launched through launch_overlapped while overlap_scope() is on may start
+// (be scheduled, run its set-up) while the kernel before it in the stream is still running; it calls
+// dependent_wait() before it touches any global memory, which returns once that kernel has finished and its writes are
+// visible. A kernel that calls dependent_trigger() lets the next one be scheduled from that point on. Both calls do
+// nothing in a kernel launched the ordinary way.
+bool& overlap_scope();  // thread-local switch, set by callers that queue a chain of dependent launches
+#ifdef __CUDACC__
+__device__ __forceinline__ void dependent_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependent_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_scope() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup, so that
 // the library has no link-time dependency on libcuda.
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, uint32_t rank, const void* base,
