@@ -177,7 +177,8 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float* part, in
 // the tensor-core products that together carry 16 mantissa bits of the activation.
 __global__ void __launch_bounds__(256) split_hi_lo_kernel(const float* x, int64_t x_rs, uint16_t* hi, uint16_t* lo,
                                                           int64_t rows, int K) {
-  dependent_trigger();  // the GEMM queued behind this kernel may be scheduled and set itself up meanwhile
+  dependent_wait();     // (launched as a programmatic dependent of the kernel before it: that one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled and set itself up meanwhile
   const int per_row = K / 4;
   const int64_t total = rows * per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -243,7 +244,8 @@ __device__ __forceinline__ float4 sum_pieces4(const float* part, int n_part, int
 __global__ void __launch_bounds__(1024) sum_norm_split_kernel(const float* part, int n_part, int64_t mn, float* x,
                                                               const float* w, float eps, uint16_t* hi, uint16_t* lo,
                                                               int hidden) {
-  dependent_trigger();  // the GEMM queued behind this kernel may be scheduled and set itself up meanwhile
+  dependent_wait();     // (launched as a programmatic dependent of the kernel before it: that one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled and set itself up meanwhile
   extern __shared__ float row_s[];  // [4][hidden]: the sums of the four thread groups, then (in [0]) the row
   __shared__ float red[32];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
@@ -299,7 +301,8 @@ __global__ void __launch_bounds__(1024) sum_norm_split_kernel(const float* part,
 // planes [rows][inter] for the down projection. Three launches (sum_partials, swiglu, split_hi_lo) as one.
 __global__ void __launch_bounds__(256) sum_swiglu_split_kernel(const float* part, int n_part, int64_t mn, uint16_t* hi,
                                                                uint16_t* lo, int64_t rows, int inter) {
-  dependent_trigger();  // the GEMM queued behind this kernel may be scheduled and set itself up meanwhile
+  dependent_wait();     // (launched as a programmatic dependent of the kernel before it: that one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled and set itself up meanwhile
   const int per_row = inter / 4;
   const int64_t total = rows * per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -324,6 +327,8 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const float* qkv, float* 
                                                        const float* q_norm, const float* k_norm, const float* cos_t,
                                                        const float* sin_t, int B, int L, int H, int KVH, int max_len,
                                                        int pos0, int slot0, float eps, int n_part, int64_t mn) {
+  dependent_wait();
+  dependent_trigger();
   constexpr int D = 128;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_all = H + 2 * KVH;
@@ -459,8 +464,8 @@ static bool split_k_ok(int64_t M, int K) { return M <= 128 && K % 128 == 0 && K 
 static int split_planes(Qwen3Model* m, const float* x, int64_t x_rs, int64_t M, int K, cudaStream_t st) {
   const int64_t blocks = (M * (K / 4) + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-  split_hi_lo_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, x_rs, m->hi, m->hi + M * K,
-                                                                                         M, K);
+  YTC_CUDA(launch_overlapped(split_hi_lo_kernel, dim3(static_cast<unsigned>(blocks < cap ? blocks : cap)), dim3(256), 0, st,
+                             x, x_rs, m->hi, m->hi + M * K, M, K));
   count_launch();
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
@@ -498,8 +503,9 @@ static int gemm_pieces(Qwen3Model* m, const uint16_t* W, int64_t M, int N, int K
 
 static int sum_norm_split(Qwen3Model* m, const Pieces& pc, float* x, const float* w, int64_t rows, int hidden,
                           cudaStream_t st) {
-  sum_norm_split_kernel<<<static_cast<unsigned>(rows), 1024, 4 * hidden * sizeof(float), st>>>(
-      pc.part, pc.n, pc.mn, x, w, m->eps, m->hi, m->hi + rows * hidden, hidden);
+  YTC_CUDA(launch_overlapped(sum_norm_split_kernel, dim3(static_cast<unsigned>(rows)), dim3(1024),
+                             4 * hidden * sizeof(float), st, pc.part, pc.n, pc.mn, x, w, m->eps, m->hi,
+                             m->hi + rows * hidden, hidden));
   count_launch();
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
@@ -645,9 +651,9 @@ static int qkv_post_launch(const float* qkv, int n_part, int64_t mn, float* q_ou
   const int64_t vecs = static_cast<int64_t>(batch) * len * (heads + 2 * kv_heads);
   const int64_t blocks = (vecs + 3) / 4;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-  qkv_post_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      qkv, q_out, k_cache, v_cache, q_norm, k_norm, cos_table, sin_table, batch, len, heads, kv_heads, max_len, pos0,
-      slot0, eps, n_part, mn);
+  YTC_CUDA(launch_overlapped(qkv_post_kernel, dim3(static_cast<unsigned>(blocks < cap ? blocks : cap)), dim3(128), 0,
+                             static_cast<cudaStream_t>(stream), qkv, q_out, k_cache, v_cache, q_norm, k_norm, cos_table,
+                             sin_table, batch, len, heads, kv_heads, max_len, pos0, slot0, eps, n_part, mn));
   count_launch();
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
@@ -1218,8 +1224,9 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
       if ((s = gemm_pieces(m, W.gate_up, rows, 2 * m->l_inter, Hd, &pc, st)) != YTC_OK) return s;
       {
         const int64_t blocks = (rows * (m->l_inter / 4) + 127) / 128;
-        sum_swiglu_split_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 128, 0, st>>>(
-            pc.part, pc.n, pc.mn, m->hi, m->hi + rows * m->l_inter, rows, m->l_inter);
+        YTC_CUDA(launch_overlapped(sum_swiglu_split_kernel, dim3(static_cast<unsigned>(blocks < cap ? blocks : cap)),
+                                   dim3(128), 0, st, pc.part, pc.n, pc.mn, m->hi, m->hi + rows * m->l_inter, rows,
+                                   m->l_inter));
         count_launch();
         YTC_CUDA(cudaGetLastError());
       }

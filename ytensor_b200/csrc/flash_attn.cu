@@ -929,6 +929,8 @@ constexpr int DF_KB = 16;
 
 template <int G>
 __global__ void __launch_bounds__(DF_WARPS * 32) attn_decode_fast_kernel(const AttnDecodeParams dp) {
+  dependent_wait();     // (under a programmatic dependent launch: the kernel before this one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled meanwhile
   const AttnSimtParams& p = dp.a;
   constexpr int D = 128;
   __shared__ __align__(16) float qs[G * D];
@@ -1082,6 +1084,8 @@ __global__ void __launch_bounds__(DF_WARPS * 32) attn_decode_fast_kernel(const A
 
 // Combines the per-slice partials: O = sum_s O_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m); rows that saw no key -> 0.
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const AttnDecodeParams dp) {
+  dependent_wait();     // (under a programmatic dependent launch: the kernel before this one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled meanwhile
   const AttnSimtParams& p = dp.a;
   const int bk = blockIdx.x;
   const int b = bk / p.kv_heads, kvh = bk - b * p.kv_heads;
@@ -1593,13 +1597,13 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
                       (groups == 1 || groups == 2 || groups == 4) && q_strides[1] % 4 == 0 && q_strides[0] % 4 == 0 &&
                       (reinterpret_cast<uint64_t>(Q) & 15) == 0 && g_attn_path != 1;
     if (fast) {
-      if (groups == 1) attn_decode_fast_kernel<1><<<dim3(dp.splits, bk), DF_WARPS * 32, 0, st>>>(dp);
-      else if (groups == 2) attn_decode_fast_kernel<2><<<dim3(dp.splits, bk), DF_WARPS * 32, 0, st>>>(dp);
-      else attn_decode_fast_kernel<4><<<dim3(dp.splits, bk), DF_WARPS * 32, 0, st>>>(dp);
+      if (groups == 1) YTC_CUDA(launch_overlapped(attn_decode_fast_kernel<1>, dim3(dp.splits, bk), dim3(DF_WARPS * 32), 0, st, dp));
+      else if (groups == 2) YTC_CUDA(launch_overlapped(attn_decode_fast_kernel<2>, dim3(dp.splits, bk), dim3(DF_WARPS * 32), 0, st, dp));
+      else YTC_CUDA(launch_overlapped(attn_decode_fast_kernel<4>, dim3(dp.splits, bk), dim3(DF_WARPS * 32), 0, st, dp));
     } else {
       attn_decode_kernel<<<dim3(dp.splits, bk), DEC_WARPS * 32, 0, st>>>(dp);
     }
-    attn_decode_merge_kernel<<<bk, 128, 0, st>>>(dp);
+    YTC_CUDA(launch_overlapped(attn_decode_merge_kernel, dim3(bk), dim3(128), 0, st, dp));
     count_launch(2);
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;
