@@ -226,6 +226,8 @@ __global__ void __launch_bounds__(256) unary_nd_kernel(int op, const void* x, vo
 // (reference example/qwen3/src/qwen3.cpp:193-200 does swish_ on one slice, then *= the other).
 __global__ void __launch_bounds__(256) swiglu_kernel(const void* gu, void* out, int64_t rows, int inter, int64_t gu_rs,
                                                      int64_t out_rs, int dt_in, int dt_out) {
+  dependent_wait();     // (under a programmatic dependent launch: the kernel before this one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled meanwhile
   const int64_t per_row = inter / 4;
   const int64_t n4 = rows * per_row;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n4;
@@ -372,8 +374,9 @@ int ytcuda_swiglu(int dt_in, int dt_out, const void* gate_up, void* out, int64_t
     set_last_error("ytcuda_swiglu: the half width and the row strides must be multiples of 4 elements");
     return YTC_UNSUPPORTED;
   }
-  swiglu_kernel<<<grid_for(rows * (inter / 4)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      gate_up, out, rows, inter, gu_row_stride, out_row_stride, dt_in, dt_out);
+  YTC_CUDA(launch_overlapped(swiglu_kernel, dim3(grid_for(rows * (inter / 4))), dim3(256), 0,
+                             static_cast<cudaStream_t>(stream), gate_up, out, rows, inter, gu_row_stride, out_row_stride,
+                             dt_in, dt_out));
   count_launch();
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;

@@ -1279,6 +1279,8 @@ constexpr int T64_BM = 64, T64_BN = 64, T64_LD = 128 + 4, T64_PLD = 64 + 4;
 constexpr int T64_SMEM = (3 * 64 * T64_LD + T64_BN * T64_PLD) * 4;
 
 __global__ void __launch_bounds__(256, 1) attn_tile64_kernel(const AttnSimtParams p) {
+  dependent_wait();     // (under a programmatic dependent launch: the kernel before this one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled meanwhile
   extern __shared__ __align__(16) float t64_smem[];
   float(*Qs)[T64_LD] = reinterpret_cast<float(*)[T64_LD]>(t64_smem);
   float(*Ks)[T64_LD] = Qs + T64_BM;
@@ -1614,7 +1616,7 @@ int ytcuda_flash_attn_fwd(int dtype, const void* Q, const void* K, const void* V
     dim3 grid((q_len + T64_BM - 1) / T64_BM, heads, batch);
     const int sa = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_tile64_kernel), T64_SMEM);
     if (sa != YTC_OK) return sa;
-    attn_tile64_kernel<<<grid, 256, T64_SMEM, st>>>(p);
+    YTC_CUDA(launch_overlapped(attn_tile64_kernel, dim3(grid), dim3(256), T64_SMEM, st, p));
     count_launch();
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;

@@ -142,6 +142,8 @@ struct RowParams {
 
 template <int OP, int G>
 __global__ void __launch_bounds__(G < 256 ? 256 : G) row_kernel(const RowParams p) {
+  dependent_wait();     // (under a programmatic dependent launch: the kernel before this one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled meanwhile
   constexpr int THREADS = G < 256 ? 256 : G;
   constexpr int RPC = THREADS / G;  // rows per CTA
   constexpr int VPT = 4;
@@ -662,7 +664,7 @@ static void launch_row(const RowParams& p, cudaStream_t st) {
   const int64_t row_blocks = (p.rows + RPC - 1) / RPC;
   const int64_t cap = static_cast<int64_t>(sm_count()) * (2048 / THREADS) * 2;
   const int grid = static_cast<int>(row_blocks < cap ? row_blocks : cap);
-  row_kernel<OP, G><<<grid, THREADS, 0, st>>>(p);
+  (void)launch_overlapped(row_kernel<OP, G>, dim3(grid), dim3(THREADS), 0, st, p);
   count_launch();
 }
 template <int OP>
