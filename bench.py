@@ -632,7 +632,7 @@ def gemm32_arm(args) -> dict | None:
         "vs_baseline": None, "dtype": "f32 (three bf16 planes per operand, fp32 accumulate)", "data": "synthetic",
         "config": {"workload": "configs[0]: fp32 GEMM 1024 x 1024 x 1024", "l2": "flushed between steps (192 MB write)"},
         "roofline": {"bound": "tensor", "achieved": val, "peak": peak, "unit": "TFLOP/s", "frac": val / peak,
-                     "traffic": None, "kernel": "gemm_split3_kernel (two launches) + gemm_tc_kernel over k' = 6 k",
+                     "traffic": None, "kernel": "gemm_split3_kernel (one launch for both operands) + gemm_tc kernel over k' = 6 k, queued as dependent launches",
                      "peak_source": f"{peaks['source']} (burst cuBLAS bf16 / 6 partial products)",
                      "algorithmic_flops_per_launch": flops},
         "ffma_kernel": {"ms_per_step": res["ffma"][0], "tflops": flops / (res["ffma"][0] * 1e-3) / 1e12},

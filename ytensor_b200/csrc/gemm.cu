@@ -434,6 +434,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
   cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // (set-up done in shared and tensor memory only; under a programmatic dependent launch global memory may be touched
+  // from here on)
+  dependent_wait();
+  dependent_trigger();
 
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -862,7 +866,7 @@ static int launch_tc(int dtype_in, int dtype_out, const void* A, const void* B, 
       const int s = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tc2_kernel), Tc2Smem::DYN_BYTES);
       if (s != YTC_OK) return s;
     }
-    gemm_tc2_kernel<<<clusters * 2, TC_THREADS, Tc2Smem::DYN_BYTES, st>>>(tmA, tmB, p);
+    YTC_CUDA(launch_overlapped(gemm_tc2_kernel, dim3(clusters * 2), dim3(TC_THREADS), Tc2Smem::DYN_BYTES, st, tmA, tmB, p));
     count_launch();
     YTC_CUDA(cudaGetLastError());
     return YTC_OK;
@@ -940,12 +944,31 @@ static int launch_simt(int dtype_in, int dtype_out, const void* A, const void* B
 //   right operand (is_b == 1, x is [rows = k][cols = n]): out[b][c k + i][j] = plane_b(c) of x[b][i][j]
 // with plane_a = l m h m h h and plane_b = h m l h m h. Non-finite values keep m = l = 0 (an infinite operand then
 // meets zero planes of the other operand and the sum becomes NaN where the FFMA kernel gives the infinity).
-__global__ void __launch_bounds__(256) gemm_split3_kernel(const float* x, int64_t rs, int64_t cs, int64_t bs, int rows,
-                                                          int cols, int64_t batch, int is_b, __nv_bfloat16* out) {
+// One operand of the split; `blocks` CTAs of the launch work on it.
+struct SplitOp {
+  const float* x;
+  int64_t rs, cs, bs;
+  int rows, cols;
+  int64_t batch;
+  int is_b;
+  __nv_bfloat16* out;
+  int blocks;
+};
+// One launch splits both operands (or one: b.blocks == 0): CTAs [0, a.blocks) take a, the rest b.
+__global__ void __launch_bounds__(256) gemm_split3_kernel(const SplitOp oa, const SplitOp ob) {
+  dependent_wait();     // (under a programmatic dependent launch: the kernel before this one has finished)
+  dependent_trigger();  // the kernel queued behind this one may be scheduled and set itself up meanwhile
+  const bool second = static_cast<int>(blockIdx.x) >= oa.blocks;
+  const SplitOp& op = second ? ob : oa;
+  const float* x = op.x;
+  const int64_t rs = op.rs, cs = op.cs, bs = op.bs, batch = op.batch;
+  const int rows = op.rows, cols = op.cols, is_b = op.is_b;
+  __nv_bfloat16* out = op.out;
+  const int64_t block = static_cast<int64_t>(blockIdx.x) - (second ? oa.blocks : 0);
   const int64_t per = static_cast<int64_t>(rows) * cols;
   const int64_t total = per * batch;
-  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
-       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  for (int64_t t = block * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<int64_t>(op.blocks) * blockDim.x) {
     const int64_t b = t / per, r = t - b * per;
     const int i = static_cast<int>(r / cols), j = static_cast<int>(r - static_cast<int64_t>(i) * cols);
     const float v = x[b * bs + i * rs + j * cs];
@@ -1022,6 +1045,13 @@ static bool f32_split_ok(int m, int n, int k, int64_t rsc, int64_t csc, int64_t 
 static int launch_f32_split(const float* A, const float* B, float* C, int m, int n, int k, float alpha, float beta,
                             int64_t rsa, int64_t csa, int64_t rsb, int64_t csb, int64_t rsc, int64_t csc, int64_t batch,
                             int64_t bsa, int64_t bsb, int64_t bsc, cudaStream_t st) {
+  // the split launches and the product are one chain of dependent kernels: each is scheduled while the one before it
+  // still runs (programmatic dependent launches)
+  struct Scope {
+    bool was = overlap_scope();
+    Scope() { overlap_scope() = true; }
+    ~Scope() { overlap_scope() = was; }
+  } scope;
   const bool b_shared = batch > 1 && bsb == 0;
   const int64_t a_per = static_cast<int64_t>(m) * k * 6, b_per = static_cast<int64_t>(k) * n * 6;  // bf16 elements
   // batch items per pass so that the expanded operands stay below about 2 GiB
@@ -1039,18 +1069,21 @@ static int launch_f32_split(const float* A, const float* B, float* C, int m, int
   __nv_bfloat16* a6 = reinterpret_cast<__nv_bfloat16*>(ws);
   __nv_bfloat16* b6 = reinterpret_cast<__nv_bfloat16*>(ws + a_bytes);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-  auto split = [&](const float* x, int64_t rs, int64_t cs, int64_t bs, int rows, int cols, int64_t nb, int is_b,
+  auto op_of = [&](const float* x, int64_t rs, int64_t cs, int64_t bs, int rows, int cols, int64_t nb, int is_b,
                    __nv_bfloat16* out) {
     const int64_t blocks = (static_cast<int64_t>(rows) * cols * nb + 255) / 256;
-    gemm_split3_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(x, rs, cs, bs, rows, cols, nb,
-                                                                                            is_b, out);
+    return SplitOp{x, rs, cs, bs, rows, cols, nb, is_b, out, static_cast<int>(blocks < cap ? blocks : cap)};
+  };
+  auto split = [&](const SplitOp& a, const SplitOp& b) {  // b.blocks == 0: one operand only
+    (void)launch_overlapped(gemm_split3_kernel, dim3(static_cast<unsigned>(a.blocks + b.blocks)), dim3(256), 0, st, a, b);
     count_launch();
   };
-  if (b_shared) split(B, rsb, csb, 0, k, n, 1, 1, b6);
+  const SplitOp none{nullptr, 0, 0, 0, 0, 0, 0, 0, nullptr, 0};
+  if (b_shared) split(op_of(B, rsb, csb, 0, k, n, 1, 1, b6), none);
   for (int64_t b0 = 0; b0 < batch; b0 += chunk) {
     const int64_t nb = batch - b0 < chunk ? batch - b0 : chunk;
-    split(A + b0 * bsa, rsa, csa, bsa, m, k, nb, 0, a6);
-    if (!b_shared) split(B + b0 * bsb, rsb, csb, bsb, k, n, nb, 1, b6);
+    split(op_of(A + b0 * bsa, rsa, csa, bsa, m, k, nb, 0, a6),
+          b_shared ? none : op_of(B + b0 * bsb, rsb, csb, bsb, k, n, nb, 1, b6));
     YTC_CUDA(cudaGetLastError());
     const int s = launch_tc(YTC_BF16, YTC_F32, a6, b6, C + b0 * bsc, m, n, 6 * k, alpha, beta, /*a_mn=*/0, 6 * k,
                             /*b_mn=*/1, n, rsc, csc, nb, a_per, b_shared ? 0 : b_per, bsc, st);
