@@ -331,7 +331,10 @@ int ytcuda_qwen3_cache_len(void* handle);
  * shared-memory slots filled by bulk async copies that run ahead of the phases and, on one GPU, has no grid barriers:
  * the activations that cross between phases are stored as {value, tag} pairs that the consumers poll, and the linear
  * phases run on mma.sync with the activations split into two bf16 planes (paths 0, 2 and 3 alike); 4 = as 3 without
- * the ring (every phase loads its weights after the barrier before it); 5 = the ring with grid barriers.
+ * the ring (every phase loads its weights after the barrier before it); 5 = the ring with grid barriers;
+ * 6 = as 1, and under tensor parallelism every sum over ranks goes through the all-reduce callback (otherwise inputs
+ * of 5 to 128 rows exchange the ranks' shares inside the kernel that adds a projection to the residual stream: each
+ * rank pushes its row sums as {value, tag} pairs into the peers' buffers and polls its own).
  * Both forms compute the operator sequence of Qwen3ForCausalLM::forward (qwen3.cpp:365-457); the switch itself has
  * no counterpart in the reference. */
 int ytcuda_qwen3_set_decode_path(void* handle, int path);

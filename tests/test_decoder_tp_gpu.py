@@ -60,27 +60,35 @@ def _worker(rank, world, port, ret):
                             num_attention_heads=4 if world == 2 else 16, num_key_value_heads=2 if world == 2 else 8,
                             head_dim=128, max_position_embeddings=128)
         w = Q.random_weights(cfg, seed=11, std=0.05)
-        ids = torch.from_numpy(np.random.default_rng(6).integers(0, cfg.vocab_size, (6, 20)).astype(np.int32)).cuda()
-        ms = []
-        for path in (1, 2):
-            m = Q.Qwen3ForCausalLM(cfg, batch=6, tp_rank=rank, tp_world=world)
-            m.load_weights(w)
-            m.set_decode_path(path)
-            ms.append(m)
-        la, lb = ms[0].forward(ids), ms[1].forward(ids)
-        assert torch.equal(la, lb)
-        for step in range(12):
-            tok, _ = ms[0].argmax(la)
-            tok = tok.reshape(6, 1).contiguous()
-            la = ms[0].forward(tok)
-            n0 = Q._lib.lib().ytcuda_launch_count()
-            lb = ms[1].forward(tok)
-            assert Q._lib.lib().ytcuda_launch_count() - n0 == 1
-            a, b = la.cpu().numpy(), lb.cpu().numpy()
-            assert np.linalg.norm(b - a) / np.linalg.norm(a) < 2e-5, (step, np.linalg.norm(b - a) / np.linalg.norm(a))
-        assert Q._lib.lib().ytcuda_device_status(None) == 0
-        for m in ms:
-            m.close()
+        # path 6: one launch per operator, sums over ranks by the NCCL callback; path 1: the same launches with the
+        # ranks' shares pushed to the peers inside the kernels that add a projection to the residual stream;
+        # path 2: the step kernel. All fed the tokens of path 6.
+        for nseq in (6, 16):
+            ids = torch.from_numpy(np.random.default_rng(nseq).integers(0, cfg.vocab_size, (nseq, 20)).astype(np.int32)).cuda()
+            ms = []
+            for path in (6, 1, 2):
+                m = Q.Qwen3ForCausalLM(cfg, batch=nseq, tp_rank=rank, tp_world=world)
+                m.load_weights(w)
+                m.set_decode_path(path)
+                ms.append(m)
+            la = ms[0].forward(ids)
+            for m in ms[1:]:
+                b, a = m.forward(ids).cpu().numpy(), la.cpu().numpy()
+                assert np.linalg.norm(b - a) / np.linalg.norm(a) < 2e-5, (nseq, "prefill")
+            for step in range(12):
+                tok, _ = ms[0].argmax(la)
+                tok = tok.reshape(nseq, 1).contiguous()
+                la = ms[0].forward(tok)
+                a = la.cpu().numpy()
+                for m, launches in ((ms[1], None), (ms[2], 1)):
+                    n0 = Q._lib.lib().ytcuda_launch_count()
+                    b = m.forward(tok).cpu().numpy()
+                    if launches:
+                        assert Q._lib.lib().ytcuda_launch_count() - n0 == launches
+                    assert np.linalg.norm(b - a) / np.linalg.norm(a) < 2e-5, (nseq, step, np.linalg.norm(b - a) / np.linalg.norm(a))
+            assert Q._lib.lib().ytcuda_device_status(None) == 0
+            for m in ms:
+                m.close()
         # Qwen3-0.6B shape: the first 16 greedy tokens of the reference
         cfg = Q.Qwen3Config(max_position_embeddings=768)
         m = Q.Qwen3ForCausalLM(cfg, batch=1, tp_rank=rank, tp_world=world)

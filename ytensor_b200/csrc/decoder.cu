@@ -241,9 +241,63 @@ __device__ __forceinline__ float4 sum_pieces4(const float* part, int n_part, int
 //   y = rmsNorm(x[r]) * w   (reference src/function/normalization.inl:234-277),
 //   y -> hi + lo bf16 planes, the left operand of the projection that follows.
 // Three launches (sum_partials, the row kernel, split_hi_lo) as one.
+// Tensor parallelism: the pieces above are this rank's share of the sum over k. RowExchange describes where the ranks
+// meet: area[q] is rank q's pair area (its own memory or the peer's), [source rank][2 slots][TP_PUSH_ROWS][hidden]
+// {bits, tag} pairs. A thread pushes its four sums as pairs into slot [its rank] of every peer's area (8-byte
+// system-scope stores over NVLink), polls its own area for the peers' pairs (bounded), and adds all ranks' shares in
+// rank order, so that every rank holds bitwise the same residual stream. world == 1: no exchange.
+constexpr int TP_PUSH_ROWS = 128;
+struct RowExchange {
+  uint2* area[DS_MAX_TP];
+  int rank, world, slot;
+  unsigned int tag;
+  long long wait_cycles;
+  int* status;
+};
+__device__ __forceinline__ float4 exchange_row_sums(const RowExchange& ex, int row, int hidden, int c, float4 mine) {
+  const size_t per_src = static_cast<size_t>(2) * TP_PUSH_ROWS * hidden;
+  const size_t at = (static_cast<size_t>(ex.slot) * TP_PUSH_ROWS + row) * hidden + c;
+  const float mv[4] = {mine.x, mine.y, mine.z, mine.w};
+  for (int q = 0; q < ex.world; ++q) {
+    if (q == ex.rank) continue;
+    uint2* dst = ex.area[q] + ex.rank * per_src + at;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + e), "r"(__float_as_uint(mv[e])), "r"(ex.tag)
+                   : "memory");
+  }
+  float tot[4] = {0.f, 0.f, 0.f, 0.f};
+  const long long t0 = clock64();
+  for (int r = 0; r < ex.world; ++r) {
+    if (r == ex.rank) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) tot[e] += mv[e];
+      continue;
+    }
+    const uint2* src = ex.area[ex.rank] + r * per_src + at;
+    uint4 a, b;  // pairs 0, 1 and 2, 3
+    int spins = 0;
+    while (true) {
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 2) : "memory");
+      if (a.y == ex.tag && a.w == ex.tag && b.y == ex.tag && b.w == ex.tag) break;
+      if ((++spins & 63) == 0 && clock64() - t0 > ex.wait_cycles) {  // a peer never arrived: report, carry on
+        atomicExch(ex.status, YTC_TIMEOUT);
+        break;
+      }
+    }
+    tot[0] += __uint_as_float(a.x);
+    tot[1] += __uint_as_float(a.z);
+    tot[2] += __uint_as_float(b.x);
+    tot[3] += __uint_as_float(b.z);
+  }
+  return make_float4(tot[0], tot[1], tot[2], tot[3]);
+}
+
+// w == nullptr: only the sum (and the exchange) into x, no norm and no planes (after the last layer).
 __global__ void __launch_bounds__(1024) sum_norm_split_kernel(const float* part, int n_part, int64_t mn, float* x,
                                                               const float* w, float eps, uint16_t* hi, uint16_t* lo,
-                                                              int hidden) {
+                                                              int hidden, const RowExchange ex) {
   dependent_wait();     // (launched as a programmatic dependent of the kernel before it: that one has finished)
   dependent_trigger();  // the kernel queued behind this one may be scheduled and set itself up meanwhile
   extern __shared__ float row_s[];  // [4][hidden]: the sums of the four thread groups, then (in [0]) the row
@@ -272,15 +326,22 @@ __global__ void __launch_bounds__(1024) sum_norm_split_kernel(const float* part,
       const float4 s1 = *reinterpret_cast<const float4*>(row_s + hidden + c);
       const float4 s2 = *reinterpret_cast<const float4*>(row_s + 2 * hidden + c);
       const float4 s3 = *reinterpret_cast<const float4*>(row_s + 3 * hidden + c);
-      v.x += (s0.x + s1.x) + (s2.x + s3.x);  // a fixed order: the result does not depend on timing
-      v.y += (s0.y + s1.y) + (s2.y + s3.y);
-      v.z += (s0.z + s1.z) + (s2.z + s3.z);
-      v.w += (s0.w + s1.w) + (s2.w + s3.w);
+      float4 y;  // a fixed order: the result does not depend on timing
+      y.x = (s0.x + s1.x) + (s2.x + s3.x);
+      y.y = (s0.y + s1.y) + (s2.y + s3.y);
+      y.z = (s0.z + s1.z) + (s2.z + s3.z);
+      y.w = (s0.w + s1.w) + (s2.w + s3.w);
+      if (ex.world > 1) y = exchange_row_sums(ex, static_cast<int>(blockIdx.x), hidden, c, y);
+      v.x += y.x;
+      v.y += y.y;
+      v.z += y.z;
+      v.w += y.w;
       *reinterpret_cast<float4*>(x + base + c) = v;
     }
     *reinterpret_cast<float4*>(row_s + c) = v;  // (read back by this thread only)
     ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
   }
+  if (!w) return;  // (uniform: the sum was all that was asked for)
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -437,6 +498,7 @@ struct Qwen3Model {
   char* tp_peer[DS_MAX_TP] = {};
   bool tp_ready = false;
   unsigned int ar_seq = 0;  // exchanges completed so far (the same on every rank)
+  unsigned int push_seq = 0;  // exchanges of the operator path's pushed row sums so far (the same on every rank)
   std::vector<void*> owned;
 };
 
@@ -447,8 +509,12 @@ static size_t tp_flags_offset(int hidden) {
 }
 // Behind the flag words: the pair area of the barrier-free step kernel, [source rank][2][4][hidden] {bits, tag} pairs.
 static size_t tp_pairs_offset(int hidden) { return tp_flags_offset(hidden) + 256; }
-static size_t tp_comm_bytes(int hidden) {
+// ... and behind that the pair area of the operator path (5 .. TP_PUSH_ROWS rows): [source rank][2][TP_PUSH_ROWS][hidden].
+static size_t tp_rows_offset(int hidden) {
   return tp_pairs_offset(hidden) + static_cast<size_t>(DS_MAX_TP) * 2 * 4 * hidden * sizeof(uint2);
+}
+static size_t tp_comm_bytes(int hidden) {
+  return tp_rows_offset(hidden) + static_cast<size_t>(DS_MAX_TP) * 2 * TP_PUSH_ROWS * hidden * sizeof(uint2);
 }
 
 static int dev_alloc(Qwen3Model* m, void** p, size_t bytes) {
@@ -501,11 +567,25 @@ static int gemm_pieces(Qwen3Model* m, const uint16_t* W, int64_t M, int N, int K
                      kc, kc, 2 * out->mn, st);
 }
 
+// exchange: the pieces are this rank's share of a sum over k that is split over the tensor-parallel ranks (the o and
+// down projections): the ranks' shares are exchanged inside the kernel.
 static int sum_norm_split(Qwen3Model* m, const Pieces& pc, float* x, const float* w, int64_t rows, int hidden,
-                          cudaStream_t st) {
+                          cudaStream_t st, bool exchange = false) {
+  RowExchange ex{};
+  ex.world = 1;
+  if (exchange && m->tp_world > 1 && pc.n > 0) {
+    for (int r = 0; r < m->tp_world; ++r)
+      ex.area[r] = reinterpret_cast<uint2*>((r == m->tp_rank ? m->tp_comm : m->tp_peer[r]) + tp_rows_offset(m->hidden));
+    ex.rank = m->tp_rank;
+    ex.world = m->tp_world;
+    ex.slot = static_cast<int>(m->push_seq & 1u);
+    ex.tag = ++m->push_seq;  // (never 0: the areas start zeroed)
+    ex.wait_cycles = wait_cycle_limit();
+    ex.status = device_status_word();
+  }
   YTC_CUDA(launch_overlapped(sum_norm_split_kernel, dim3(static_cast<unsigned>(rows)), dim3(1024),
                              4 * hidden * sizeof(float), st, pc.part, pc.n, pc.mn, x, w, m->eps, m->hi,
-                             m->hi + rows * hidden, hidden));
+                             m->hi + rows * hidden, hidden, ex));
   count_launch();
   YTC_CUDA(cudaGetLastError());
   return YTC_OK;
@@ -746,6 +826,7 @@ int ytcuda_qwen3_tp_resync(void* handle) {
   YTC_CUDA(cudaDeviceSynchronize());
   if (m->tp_comm) YTC_CUDA(cudaMemset(m->tp_comm, 0, tp_comm_bytes(m->hidden)));  // flags, mailboxes and pairs
   m->ar_seq = 0;
+  m->push_seq = 0;
   m->ll_base = 0xFFFFFFFFu;  // the barrier-free kernel starts again from clean pair buffers and tag 1
   m->cur_len = 0;
   m->total_written = 0;
@@ -853,7 +934,7 @@ int ytcuda_qwen3_tp_import(void* handle, int rank, const void* ipc_handle_64) {
 int ytcuda_qwen3_set_decode_path(void* handle, int path) {
   auto* m = static_cast<Qwen3Model*>(handle);
   YTC_REQUIRE(m, "ytcuda_qwen3_set_decode_path: null handle");
-  YTC_REQUIRE(path >= 0 && path <= 5, "ytcuda_qwen3_set_decode_path: path must be 0 .. 5");
+  YTC_REQUIRE(path >= 0 && path <= 6, "ytcuda_qwen3_set_decode_path: path must be 0 .. 6");
   m->decode_path = path;
   return YTC_OK;
 }
@@ -1142,7 +1223,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
     YTC_REQUIRE(L.qkv && L.o && L.gate_up && L.down && L.q_norm && L.k_norm && L.norm1 && L.norm2,
                 "ytcuda_qwen3_forward: a layer weight is not set");
   YTC_REQUIRE(m->tp_world == 1 || m->allreduce ||
-                  (len == 1 && m->tp_ready && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= ds_auto_b(m)))),
+                  (len == 1 && m->tp_ready && ((m->decode_path >= 2 && m->decode_path <= 5) || (m->decode_path == 0 && m->batch <= ds_auto_b(m)))),
               "ytcuda_qwen3_forward: tensor parallel needs an all-reduce callback");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int B = m->batch, D = m->head_dim, Hd = m->hidden;
@@ -1178,12 +1259,13 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   };
   // Automatic choice: the step kernel up to ds_auto_b() sequences. Beyond that its linear phases lose against the
   // tensor-core linears of the operator path (measured at 16 and 32 sequences), so it runs only when asked for.
-  if (len == 1 && (m->decode_path >= 2 || (m->decode_path == 0 && m->batch <= ds_auto_b(m))) && decode_step_supported(m)) {
+  const bool want_step = m->decode_path >= 2 && m->decode_path <= 5;  // (6: operator path, sums over ranks by callback)
+  if (len == 1 && (want_step || (m->decode_path == 0 && m->batch <= ds_auto_b(m))) && decode_step_supported(m)) {
     if ((s = decode_step_launch(m, ids, logits, st)) != YTC_OK) return s;
     advance();
     return YTC_OK;
   }
-  if (len == 1 && m->decode_path >= 2) {
+  if (len == 1 && want_step) {
     set_last_error("ytcuda_qwen3_forward: the single-kernel decode step needs batch <= %d, 1, 2 or %d query heads "
                    "per kv head and, under tensor parallelism, connected exchange buffers", DS_MAX_B, DS_MAX_G);
     return YTC_UNSUPPORTED;
@@ -1197,8 +1279,11 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
   // 5 .. 128 rows on one GPU: every projection runs as k pieces on the tensor cores, and the kernels between two
   // projections (sum of the pieces, residual, rmsNorm or SwiGLU or the per-head norm + RoPE, the split into bf16
   // planes) are one launch each: 11 launches per layer instead of 18.
-  const bool fused_glue = m->tp_world == 1 && rows > SK_MAX_ROWS && split_k_ok(rows, Hd) &&
-                          split_k_ok(rows, m->l_heads * D) && split_k_ok(rows, m->l_inter) && Hd <= 3072;
+  // Tensor parallel (exchange buffers connected, up to TP_PUSH_ROWS rows): the same launches; the kernel that adds the
+  // pieces of the o or down projection to the residual stream also exchanges the ranks' shares (no collective call).
+  const bool fused_glue = (m->tp_world == 1 || (m->tp_ready && rows <= TP_PUSH_ROWS && m->decode_path != 6)) &&
+                          rows > SK_MAX_ROWS && split_k_ok(rows, Hd) && split_k_ok(rows, m->l_heads * D) &&
+                          split_k_ok(rows, m->l_inter) && Hd <= 3072;
   if (fused_glue) {
     Pieces pc;  // the projection whose pieces still have to be added to the residual stream
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
@@ -1206,7 +1291,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
       const LayerW& W = m->lw[l];
       float* kc = m->k_cache + l * cache_layer;
       float* vc = m->v_cache + l * cache_layer;
-      if ((s = sum_norm_split(m, pc, m->x, W.norm1, rows, Hd, st)) != YTC_OK) return s;
+      if ((s = sum_norm_split(m, pc, m->x, W.norm1, rows, Hd, st, true)) != YTC_OK) return s;
       if ((s = gemm_pieces(m, W.qkv, rows, qkv_w, Hd, &pc, st)) != YTC_OK) return s;
       if ((s = qkv_post_launch(pc.part, pc.n, pc.mn, m->q, kc, vc, W.q_norm, W.k_norm, m->cos_t, m->sin_t, B, len,
                                m->l_heads, m->l_kv_heads, D, m->max_pos, pos0, slot0, m->eps, st)) != YTC_OK)
@@ -1220,7 +1305,7 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
         return s;
       if ((s = split_planes(m, m->attn, m->l_heads * D, rows, m->l_heads * D, st)) != YTC_OK) return s;
       if ((s = gemm_pieces(m, W.o, rows, Hd, m->l_heads * D, &pc, st)) != YTC_OK) return s;
-      if ((s = sum_norm_split(m, pc, m->x, W.norm2, rows, Hd, st)) != YTC_OK) return s;
+      if ((s = sum_norm_split(m, pc, m->x, W.norm2, rows, Hd, st, true)) != YTC_OK) return s;
       if ((s = gemm_pieces(m, W.gate_up, rows, 2 * m->l_inter, Hd, &pc, st)) != YTC_OK) return s;
       {
         const int64_t blocks = (rows * (m->l_inter / 4) + 127) / 128;
@@ -1232,11 +1317,15 @@ int ytcuda_qwen3_forward(void* handle, const int32_t* ids, int len, float* logit
       }
       if ((s = gemm_pieces(m, W.down, rows, Hd, m->l_inter, &pc, st)) != YTC_OK) return s;
     }
-    const int64_t blocks = (pc.mn + 255) / 256;  // the last down projection joins the residual stream
-    sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(pc.part, pc.n, pc.mn, m->x,
-                                                                                             Hd, Hd, 1);
-    count_launch();
-    YTC_CUDA(cudaGetLastError());
+    if (m->tp_world > 1) {  // the last down projection joins the residual stream (sum and exchange only)
+      if ((s = sum_norm_split(m, pc, m->x, nullptr, rows, Hd, st, true)) != YTC_OK) return s;
+    } else {
+      const int64_t blocks = (pc.mn + 255) / 256;
+      sum_partials_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, st>>>(pc.part, pc.n, pc.mn,
+                                                                                               m->x, Hd, Hd, 1);
+      count_launch();
+      YTC_CUDA(cudaGetLastError());
+    }
   }
   for (int l = fused_glue ? m->layers : 0; l < m->layers; ++l) {
     const LayerW& W = m->lw[l];

@@ -193,7 +193,9 @@ class Qwen3ForCausalLM:
     def set_decode_path(self, path: int) -> None:
         """0: automatic, 1: one launch per operator, 2: the single persistent kernel per decode step (or an error),
         3: as 2 with FFMA linear phases at every batch size, 4: as 3 without the shared-memory weight ring, 5: the
-        ring with grid barriers (2 on one GPU with up to four sequences has neither barriers nor a cold ring)."""
+        ring with grid barriers (2 on one GPU with up to four sequences has neither barriers nor a cold ring), 6: as 1
+        with every tensor-parallel sum through the all-reduce callback (1 exchanges the ranks' shares of inputs of
+        5 to 128 rows inside its own kernels)."""
         check(self.L.ytcuda_qwen3_set_decode_path(self.h, int(path)))
 
     def get_kv_cache_len(self) -> int:
