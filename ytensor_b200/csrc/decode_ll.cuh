@@ -332,19 +332,30 @@ __device__ __forceinline__ bool ll_linear(const DecodeStepParams& p, DwShared& S
                          "r"(__float_as_uint(y)), "r"(dst_tag)
                          : "memory");
           }
+          // the peers' pairs are requested together (one trip to the L2 for all of them), then taken in rank order
+          uint2 pr[DS_MAX_TP];
+#pragma unroll
+          for (int r = 0; r < DS_MAX_TP; ++r) {
+            pr[r] = make_uint2(0u, dst_tag);
+            if (r < p.tp_world && r != p.tp_rank) {
+              const uint2* src_pair = p.ll_mail[p.tp_rank] + r * per_src + at;
+              asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(pr[r].x), "=r"(pr[r].y) : "l"(src_pair) : "memory");
+            }
+          }
           float tot = 0.f;
           const long long t0 = clock64();
-          for (int r = 0; r < p.tp_world; ++r) {
+#pragma unroll
+          for (int r = 0; r < DS_MAX_TP; ++r) {
+            if (r >= p.tp_world) break;
             float v = y;
             if (r != p.tp_rank) {
               const uint2* src_pair = p.ll_mail[p.tp_rank] + r * per_src + at;
-              uint2 pr;
               int spins = 0;
-              while (true) {
-                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(pr.x), "=r"(pr.y) : "l"(src_pair) : "memory");
-                if (pr.y == dst_tag || ll_expired(p, &S.abort_word, t0, spins++)) break;
+              while (pr[r].y != dst_tag) {
+                if (ll_expired(p, &S.abort_word, t0, spins++)) break;
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(pr[r].x), "=r"(pr[r].y) : "l"(src_pair) : "memory");
               }
-              v = __uint_as_float(pr.x);
+              v = __uint_as_float(pr[r].x);
             }
             tot += v;
           }

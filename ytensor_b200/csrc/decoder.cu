@@ -266,30 +266,41 @@ __device__ __forceinline__ float4 exchange_row_sums(const RowExchange& ex, int r
       asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + e), "r"(__float_as_uint(mv[e])), "r"(ex.tag)
                    : "memory");
   }
+  // the peers' pairs are requested together (one trip to the L2 for all of them), then taken in rank order
+  uint4 pa[DS_MAX_TP], pb[DS_MAX_TP];  // pairs 0, 1 and 2, 3 of every rank
+#pragma unroll
+  for (int r = 0; r < DS_MAX_TP; ++r) {
+    pa[r] = pb[r] = make_uint4(0u, ex.tag, 0u, ex.tag);
+    if (r < ex.world && r != ex.rank) {
+      const uint2* src = ex.area[ex.rank] + r * per_src + at;
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pa[r].x), "=r"(pa[r].y), "=r"(pa[r].z), "=r"(pa[r].w) : "l"(src) : "memory");
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pb[r].x), "=r"(pb[r].y), "=r"(pb[r].z), "=r"(pb[r].w) : "l"(src + 2) : "memory");
+    }
+  }
   float tot[4] = {0.f, 0.f, 0.f, 0.f};
   const long long t0 = clock64();
-  for (int r = 0; r < ex.world; ++r) {
+#pragma unroll
+  for (int r = 0; r < DS_MAX_TP; ++r) {
+    if (r >= ex.world) break;
     if (r == ex.rank) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) tot[e] += mv[e];
       continue;
     }
     const uint2* src = ex.area[ex.rank] + r * per_src + at;
-    uint4 a, b;  // pairs 0, 1 and 2, 3
     int spins = 0;
-    while (true) {
-      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
-      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(src + 2) : "memory");
-      if (a.y == ex.tag && a.w == ex.tag && b.y == ex.tag && b.w == ex.tag) break;
+    while (!(pa[r].y == ex.tag && pa[r].w == ex.tag && pb[r].y == ex.tag && pb[r].w == ex.tag)) {
       if ((++spins & 63) == 0 && clock64() - t0 > ex.wait_cycles) {  // a peer never arrived: report, carry on
         atomicExch(ex.status, YTC_TIMEOUT);
         break;
       }
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pa[r].x), "=r"(pa[r].y), "=r"(pa[r].z), "=r"(pa[r].w) : "l"(src) : "memory");
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pb[r].x), "=r"(pb[r].y), "=r"(pb[r].z), "=r"(pb[r].w) : "l"(src + 2) : "memory");
     }
-    tot[0] += __uint_as_float(a.x);
-    tot[1] += __uint_as_float(a.z);
-    tot[2] += __uint_as_float(b.x);
-    tot[3] += __uint_as_float(b.z);
+    tot[0] += __uint_as_float(pa[r].x);
+    tot[1] += __uint_as_float(pa[r].z);
+    tot[2] += __uint_as_float(pb[r].x);
+    tot[3] += __uint_as_float(pb[r].z);
   }
   return make_float4(tot[0], tot[1], tot[2], tot[3]);
 }
