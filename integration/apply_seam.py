@@ -6,7 +6,7 @@
 The reference tree is never edited: `ytensor.hpp`, `include/` and `src/` are copied to the output directory and
 the copy gets the branches a maintainer of YTensor would add for the device backend. Every edit is an insertion next
 to an anchor line (a signature or a `case` label of the reference, quoted below only as far as needed to find the
-place); nothing is deleted. Compile the result with `-DYT_USE_CUDA=1 -I<repo>/include -I<repo>/ytensor_b200/cpp`
+place); nothing is deleted (one enumerator gains the comma that lets another follow it). Compile the result with `-DYT_USE_CUDA=1 -I<repo>/include -I<repo>/ytensor_b200/cpp`
 and link `-lytensor_cuda`. With `-DYT_USE_CUDA=0` (the default of the patched tree) it builds as before.
 
 What is added:
