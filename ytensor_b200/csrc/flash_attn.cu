@@ -18,6 +18,7 @@
 // (reference src/function/ops.inl:109-234,368-425, src/kernel/avx2/flash_attention.inl:202-443).
 #include <math_constants.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "ptx_sm100.cuh"
@@ -1433,7 +1434,7 @@ __global__ void __launch_bounds__(256, 1) attn_tile64_kernel(const AttnSimtParam
   }
 }
 
-static int g_attn_path = 0;  // 0 automatic, 1 always the one-warp-per-row kernel, 2 tensor-core kernel or fail
+static std::atomic<int> g_attn_path{0};  // 0 automatic, 1 always the one-warp-per-row kernel, 2 tensor-core kernel or fail
 
 static int make_qkv_map(CUtensorMap* map, const void* base, int d, int64_t len, int64_t heads, int64_t batch,
                         int64_t s_row, int64_t s_head, int64_t s_batch) {

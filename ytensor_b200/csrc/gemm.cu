@@ -10,6 +10,8 @@
 //
 // Replaces yt::kernel::avx2::sgemm / matmul / hgemm (reference src/kernel/avx2/sgemm.inl:586-806,
 // src/kernel/avx2/hgemm.inl:139-288) behind ytcuda_gemm.
+#include <atomic>
+
 #include "ptx_sm100.cuh"
 #include "ytc_common.cuh"
 
@@ -732,11 +734,11 @@ static bool tc_operand_ok(const void* ptr, int64_t rs, int64_t cs, int64_t bs, i
 }
 
 // L2 prefetch distance of the A operand in k-blocks (see GemmTcParams::a_prefetch).
-static int g_tc_a_prefetch = 0;
+static std::atomic<int> g_tc_a_prefetch{0};
 // 1 = fetch K-major operand tiles as 64-row boxes instead of one tall box.
-static int g_tc_split_loads = 0;
+static std::atomic<int> g_tc_split_loads{0};
 // CTA-pair kernel: 0 = automatic, 1 = whenever the layout allows, 2 = never.
-static int g_tc_pair = 0;
+static std::atomic<int> g_tc_pair{0};
 
 // Masked products (YTensor::masked_matmul): what the entry point asked for, seen by the launchers below.
 // kind 0: no mask; 1: bool matrix [m, n]; 2: the causal predicate j <= i + offset, evaluated on the device.
@@ -1029,11 +1031,11 @@ __global__ void __launch_bounds__(256) gemm_apply_mask_kernel(void* C, int dt, i
 }
 
 // Which kernel ytcuda_gemm picks: 0 = automatic, 1 = force FFMA, 2 = require tcgen05.
-static int g_gemm_path = 0;
+static std::atomic<int> g_gemm_path{0};
 
 // fp32 GEMM on the tensor cores (see gemm_split3_kernel): 0 = automatic (large problems), 1 = never,
 // 2 = whenever the shapes allow.
-static int g_f32_split = 0;
+static std::atomic<int> g_f32_split{0};
 
 static bool f32_split_ok(int m, int n, int k, int64_t rsc, int64_t csc, int64_t bsc) {
   if (g_f32_split == 1) return false;
