@@ -196,8 +196,9 @@ int ytcuda_reduce(int op, int dt_in, int dt_out, const void* x, void* y, int32_t
  * into the library (8192 value/index pairs; each GPU that loads the library holds it until the process ends) instead
  * of the library's grown-on-demand workspace, and the call makes no cudaMalloc / cudaFree of its own.
  * A request whose partials do not fit the array is refused with YTC_INVALID_ARG and a message naming both sizes.
- * The very first call on each device looks up the array's device address (cudaGetSymbolAddress); make that call once,
- * with the device current, before starting any stream capture. All calls share the one array and do not clear
+ * The very first call on each device looks up the array's device address (cudaGetSymbolAddress), which may load the
+ * library's device code on that device; make that call once, with the device current, before starting any stream
+ * capture. All calls share the one array and do not clear
  * it (every slot a call reads it has written first): two calls that overlap on the GPU, on different streams or
  * from different threads, race on it - serialise them. */
 int ytcuda_reduce_noalloc(int op, int dt_in, int dt_out, const void* x, void* y, int32_t* index, const int64_t* shape,
