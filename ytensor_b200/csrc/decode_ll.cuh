@@ -49,7 +49,10 @@ constexpr int LL_THREADS = LL_WORKERS + 32;  // the eighth warp only issues the 
 constexpr int LL_MAX_OWN = 64;  // rows of x one CTA may own (hidden / CTAs, rounded up)
 constexpr int DS_MAX_CHUNKS_LL = 64;  // key chunks per (sequence, kv head) the partial-result buffer holds
 constexpr int LL_GROUP = 4;     // chunks of the weight ring a linear phase takes at a time
-constexpr int LL_PART_FLOATS = LL_WARPS * LL_GROUP * 16 * 4;  // partial sums of the warps (up to 4 sequences)
+// partial sums of the warps [LL_WARPS][LL_GROUP][16][sequences], and the attention phase's scratch (query heads,
+// the warps' maxima, sums and outputs): sized for the kernel instance at hand, every KB not spent here is ring depth
+__host__ __device__ constexpr int ll_part_floats(int mt) { return LL_WARPS * LL_GROUP * 16 * mt; }
+__host__ __device__ constexpr int ll_att_floats(int g) { return g * 128 + 2 * LL_WARPS * g + LL_WARPS * g * 128; }
 
 // Synchronises the worker threads (named barrier 1); the issuing warp never takes part.
 __device__ __forceinline__ void ll_sync() { asm volatile("bar.sync 1, %0;" ::"n"(LL_WORKERS) : "memory"); }
@@ -655,7 +658,7 @@ __global__ void __launch_bounds__(LL_THREADS, 1) decode_ll_kernel(const DecodeSt
   float* red = reinterpret_cast<float*>(dw_smem + ((sizeof(DwShared) + 127) / 128) * 128);
   float* x_own = red + 32;  // (red holds up to 8 warps x 4 sequences)
   float* part = x_own + 4 * LL_MAX_OWN;  // partial sums of the warps [LL_WARPS][LL_GROUP][16][MT]
-  float* xs = part + LL_PART_FLOATS;
+  float* xs = part + ll_part_floats(MT);
   char* ring = reinterpret_cast<char*>(xs) + p.dw_xs_bytes;
   constexpr int D = 128;
   const int B = p.B, H = p.hidden;

@@ -1109,9 +1109,12 @@ static int decode_step_launch(Qwen3Model* m, const int32_t* ids, float* logits, 
     // barrier-free form never waits for a unit of its own CTA)
     const bool ll = m->decode_path != 5 && (m->hidden + sm_count() - 1) / sm_count() + 1 <= LL_MAX_OWN &&
                     (p.chunks == 1 || B * m->l_kv_heads * p.chunks <= sm_count()) && p.chunks <= DS_MAX_CHUNKS_LL;
-    const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128) + (ll ? (DS_WARPS * 4 + 4 * LL_MAX_OWN + LL_PART_FLOATS) * 4 : 0);
+    const int head = static_cast<int>((sizeof(DwShared) + 127) / 128 * 128) +
+                     (ll ? (DS_WARPS * 4 + 4 * LL_MAX_OWN + ll_part_floats(mt)) * 4 : 0);
     int xs_bytes = mt * ll_row_floats(kmax) * static_cast<int>(sizeof(float));  // (rows padded to whole 256-column blocks)
-    if (xs_bytes < att) xs_bytes = att;
+    // the attention phase's scratch: the barrier-free form has seven warps and this model's group size
+    const int att_here = ll ? ll_att_floats(groups) * static_cast<int>(sizeof(float)) : att;
+    if (xs_bytes < att_here) xs_bytes = att_here;
     xs_bytes = (xs_bytes + 127) / 128 * 128;
     int nslot = (227 * 1024 - head - xs_bytes) / DW_CHUNK;
     if (nslot > DW_MAX_SLOTS) nslot = DW_MAX_SLOTS;
